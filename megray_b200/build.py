@@ -1,0 +1,146 @@
+"""In-tree native build of ``libmegray.so`` (and the C++ test / benchmark binaries).
+
+The library is plain C++17 + CUDA for sm_100a with no dependency on PyTorch: the
+Python layer talks to it through its ``extern "C"`` interface with ctypes.  The
+build is driven by ninja from a generated ``build/build.ninja`` so that repeated
+calls only recompile what changed.  NCCL is not linked: the NCCL engine opens
+``libnccl.so.2`` at run time.
+
+    python -m megray_b200.build            # library only
+    python -m megray_b200.build --all      # + megray_test, megray_bench binaries
+"""
+from __future__ import annotations
+
+import argparse
+import glob
+import os
+import shutil
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BUILD_DIR = os.path.join(ROOT, "build")
+LIB_DIR = os.path.join(ROOT, "megray_b200", "lib")
+LIB_PATH = os.path.join(LIB_DIR, "libmegray.so")
+
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
+GENCODE = "-gencode arch=compute_100a,code=sm_100a"
+
+
+def _sources():
+    cpp = sorted(glob.glob(os.path.join(ROOT, "src", "**", "*.cpp"), recursive=True))
+    cu = sorted(glob.glob(os.path.join(ROOT, "src", "**", "*.cu"), recursive=True))
+    return cpp, cu
+
+
+def _nccl_include():
+    """Directory holding nccl.h (only the header is needed at build time)."""
+    for cand in ("/usr/include",):
+        if os.path.exists(os.path.join(cand, "nccl.h")):
+            return cand
+    try:
+        import nvidia.nccl  # type: ignore
+
+        d = os.path.join(os.path.dirname(nvidia.nccl.__file__), "include")
+        if os.path.exists(os.path.join(d, "nccl.h")):
+            return d
+    except Exception:
+        pass
+    return None
+
+
+def write_ninja(with_bins: bool) -> str:
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    os.makedirs(LIB_DIR, exist_ok=True)
+    cpp, cu = _sources()
+    inc = f"-I{ROOT}/include -I{ROOT}/src -I{CUDA_HOME}/include"
+    nccl_inc = _nccl_include()
+    defs = "-DMEGRAY_WITH_CUDA -DMEGRAY_WITH_NVL -DMEGRAY_WITH_SHM"
+    if nccl_inc:
+        defs += " -DMEGRAY_WITH_NCCL"
+        if nccl_inc != "/usr/include":
+            inc += f" -I{nccl_inc}"
+    lines = [
+        "ninja_required_version = 1.3",
+        f"cxxflags = -std=c++17 -O2 -g -fPIC -Wall -Wno-unused-function {defs} {inc}",
+        f"nvccflags = -std=c++17 -O3 {GENCODE} -lineinfo -Xcompiler -fPIC "
+        f"--expt-relaxed-constexpr {defs} {inc}",
+        "rule cxx",
+        "  command = g++ -MMD -MF $out.d $cxxflags -c $in -o $out",
+        "  depfile = $out.d",
+        "  deps = gcc",
+        "  description = CXX $in",
+        "rule nvcc",
+        f"  command = {NVCC} -MD -MF $out.d $nvccflags -c $in -o $out",
+        "  depfile = $out.d",
+        "  deps = gcc",
+        "  description = NVCC $in",
+        "rule link_so",
+        f"  command = {NVCC} -shared {GENCODE} -o $out $in -lpthread -ldl -lrt",
+        "  description = LINK $out",
+        "rule link_bin",
+        f"  command = g++ -o $out $in -L{LIB_DIR} -lmegray -Wl,-rpath,{LIB_DIR} "
+        f"-Wl,-rpath,$$ORIGIN/../megray_b200/lib -L{CUDA_HOME}/lib64 -lcudart -lpthread -ldl",
+        "  description = LINK $out",
+        "",
+    ]
+    objs = []
+    for src in cpp + cu:
+        rel = os.path.relpath(src, ROOT).replace(os.sep, "_")
+        obj = os.path.join(BUILD_DIR, rel + ".o")
+        rule = "nvcc" if src.endswith(".cu") else "cxx"
+        lines.append(f"build {obj}: {rule} {src}")
+        objs.append(obj)
+    lines.append(f"build {LIB_PATH}: link_so {' '.join(objs)}")
+    targets = [LIB_PATH]
+    if with_bins:
+        for name, srcs in (
+            ("megray_test", sorted(glob.glob(os.path.join(ROOT, "tests", "cpp", "*.cpp")))),
+            ("megray_bench", sorted(glob.glob(os.path.join(ROOT, "bench", "*.cpp")))),
+        ):
+            if not srcs:
+                continue
+            bobjs = []
+            for src in srcs:
+                rel = os.path.relpath(src, ROOT).replace(os.sep, "_")
+                obj = os.path.join(BUILD_DIR, rel + ".o")
+                lines.append(f"build {obj}: cxx {src}")
+                bobjs.append(obj)
+            out = os.path.join(BUILD_DIR, name)
+            lines.append(f"build {out}: link_bin {' '.join(bobjs)} | {LIB_PATH}")
+            targets.append(out)
+    lines.append("default " + " ".join(targets))
+    path = os.path.join(BUILD_DIR, "build.ninja")
+    text = "\n".join(lines) + "\n"
+    old = open(path).read() if os.path.exists(path) else None
+    if old != text:
+        with open(path, "w") as f:
+            f.write(text)
+    return path
+
+
+def build(with_bins: bool = False, verbose: bool = False) -> str:
+    """Compile everything that is stale; returns the path of libmegray.so."""
+    ninja = shutil.which("ninja")
+    if ninja is None:
+        raise RuntimeError("ninja not found on PATH")
+    path = write_ninja(with_bins)
+    cmd = [ninja, "-f", path, "-C", BUILD_DIR]
+    if verbose:
+        cmd.append("-v")
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout)
+        raise RuntimeError("native build failed")
+    if verbose:
+        print(res.stdout)
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--all", action="store_true", help="also build megray_test and megray_bench")
+    ap.add_argument("-v", "--verbose", action="store_true")
+    a = ap.parse_args()
+    print(build(with_bins=a.all, verbose=a.verbose))

@@ -1,0 +1,45 @@
+// C entry points for the GEMM family (see include/megray/c_api.h).
+#include "kernels/gemm_tcgen05.cuh"
+#include "kernels/launch_count.h"
+#include "megray/c_api.h"
+
+extern "C" int megray_gemm_bf16(const megray_gemm_args* a, void* stream) {
+    if (a == nullptr)
+        return 6;
+    megray::gemm::GemmArgs g{};
+    g.A = a->A;
+    g.B = a->B;
+    g.D = a->D;
+    g.D2 = a->D2;
+    g.aux = a->aux;
+    g.M = a->M;
+    g.N = a->N;
+    g.K = a->K;
+    g.lda = a->lda;
+    g.ldb = a->ldb;
+    g.ldd = a->ldd;
+    g.ldd2 = a->ldd2;
+    g.ldaux = a->ldaux;
+    g.a_mn = a->a_mn != 0;
+    g.b_mn = a->b_mn != 0;
+    g.epilogue = a->epilogue;
+    g.aux_off = a->aux_off;
+    g.m_rot = a->m_rot;
+    g.sm_limit = a->sm_limit;
+    g.a_ready = a->a_ready;
+    g.rows_per_flag = a->rows_per_flag;
+    g.a_ready_target = a->a_ready_target;
+    g.peer_out = a->peer_out;
+    g.rows_per_peer = a->rows_per_peer;
+    g.grouped.m_block_group = a->m_block_group;
+    g.grouped.group_rows_b = a->group_rows_b;
+    g.grouped.k_begin = a->k_begin;
+    g.grouped.k_end = a->k_end;
+    g.grouped.groups = a->groups;
+    g.error_flag = a->error_flag;
+    g.wait_limit_ns = a->wait_limit_ns;
+    cudaError_t e = megray::gemm::launch_gemm_bf16(g, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+extern "C" uint64_t megray_launch_count(void) { return megray::launch_count(); }

@@ -1,0 +1,671 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a on tcgen05 tensor cores.
+//
+//   warp 0      : TMA producer   (cp.async.bulk.tensor 2D tiles -> 128B-swizzled smem ring)
+//   warp 1      : UMMA issuer    (tcgen05.mma cta_group::1, 128x256x16, accumulators in TMEM)
+//   warps 2..5  : epilogue       (tcgen05.ld TMEM -> registers -> fused epilogue -> global)
+//
+// Tile 128 x 256 x 64 per stage, 4-stage ring (48 KB per stage), two TMEM
+// accumulators (2 x 256 columns) so the epilogue of tile i overlaps the main
+// loop of tile i+1.  Every wait is bounded: a wait that runs out sets the
+// kernel's error word, all roles leave their loops, TMEM is freed and the
+// kernel returns normally.
+//
+// The reference library (MegRay) contains no GEMM; this kernel exists for the
+// fused tensor-parallel and expert-parallel entry points.
+#include "gemm_tcgen05.cuh"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_bf16.h>
+
+#include <atomic>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "launch_count.h"
+#include "ptx_sm100.cuh"
+
+namespace megray {
+namespace gemm {
+
+using namespace megray::ptx;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int TMEM_COLS = 512;
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int MN_CHUNK_BYTES = 64 * BK * 2;  // one 64(mn) x 64(k) box of an MN-major operand
+
+struct KParams {
+    int M, N, K;
+    int m_blocks, n_blocks, num_tiles;
+    int group_m;
+    int m_rot;
+    int n_tile_stride;  // 256, or 128 for the SwiGLU pairing
+    int b_half_off;     // row offset of the second 128 rows of a K-major B tile
+    __nv_bfloat16* D;
+    long ldd;
+    __nv_bfloat16* D2;
+    long ldd2;
+    const __nv_bfloat16* aux;
+    long ldaux;
+    int aux_off;
+    const uint32_t* a_ready;
+    int rows_per_flag;
+    uint32_t a_ready_target;
+    void* const* peer_out;
+    int rows_per_peer;
+    const int* m_block_group;
+    int group_rows_b;
+    const int* k_begin;
+    const int* k_end;
+    int* error_flag;
+    uint64_t wait_limit_ns;
+};
+
+struct Tile {
+    int m0;        // first row of A / D (within the group for grouped-K)
+    int n0;        // first output column
+    int b_row;     // K-major B: first row; MN-major B: added to the k coordinate
+    int k0;        // first k
+    int k_blocks;  // 64-wide k steps; 0 = write zeros
+    long d_row0;   // first output row
+    bool skip;     // nothing to do (padding block of a grouped problem)
+};
+
+__device__ __forceinline__ Tile decode_tile(const KParams& p, int t) {
+    Tile tl;
+    tl.skip = false;
+    tl.b_row = 0;
+    tl.k0 = 0;
+    tl.k_blocks = (p.K + BK - 1) / BK;
+    int grp = 0;
+    if (p.k_begin != nullptr) {  // grouped-K: one dense [M,N] problem per group
+        int per = p.m_blocks * p.n_blocks;
+        grp = t / per;
+        t -= grp * per;
+    }
+    int per_group = p.group_m * p.n_blocks;
+    int g = t / per_group;
+    int first_m = g * p.group_m;
+    int gsz = min(p.group_m, p.m_blocks - first_m);
+    int r = t - g * per_group;
+    int mb = first_m + r % gsz;
+    int nb = r / gsz;
+    mb += p.m_rot;
+    if (mb >= p.m_blocks)
+        mb -= p.m_blocks;
+    tl.m0 = mb * BM;
+    tl.n0 = nb * p.n_tile_stride;
+    tl.d_row0 = tl.m0;
+    if (p.k_begin != nullptr) {
+        int kb = p.k_begin[grp], ke = p.k_end[grp];
+        tl.k0 = kb;
+        tl.k_blocks = (ke - kb + BK - 1) / BK;
+        tl.d_row0 = static_cast<long>(grp) * p.M + tl.m0;
+    } else if (p.m_block_group != nullptr) {
+        int e = p.m_block_group[mb];
+        if (e < 0)
+            tl.skip = true;
+        else
+            tl.b_row = e * p.group_rows_b;
+    }
+    return tl;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+// Store 32 consecutive fp32 values of one row as bf16.
+__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const float (&v)[32], int ncols_ok) {
+    if (ncols_ok >= 32) {
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint4 o;
+            o.x = pack_bf16x2(v[i * 8 + 0], v[i * 8 + 1]);
+            o.y = pack_bf16x2(v[i * 8 + 2], v[i * 8 + 3]);
+            o.z = pack_bf16x2(v[i * 8 + 4], v[i * 8 + 5]);
+            o.w = pack_bf16x2(v[i * 8 + 6], v[i * 8 + 7]);
+            d4[i] = o;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < ncols_ok)
+                dst[i] = __float2bfloat16_rn(v[i]);
+    }
+}
+__device__ __forceinline__ void load_row32(const __nv_bfloat16* src, float (&v)[32], int ncols_ok) {
+    if (ncols_ok >= 32) {
+        const uint4* s4 = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint4 o = s4[i];
+            v[i * 8 + 0] = bf16_lo(o.x);
+            v[i * 8 + 1] = bf16_hi(o.x);
+            v[i * 8 + 2] = bf16_lo(o.y);
+            v[i * 8 + 3] = bf16_hi(o.y);
+            v[i * 8 + 4] = bf16_lo(o.z);
+            v[i * 8 + 5] = bf16_hi(o.z);
+            v[i * 8 + 6] = bf16_lo(o.w);
+            v[i * 8 + 7] = bf16_hi(o.w);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            v[i] = (i < ncols_ok) ? __bfloat162float(src[i]) : 0.f;
+    }
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+        gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
+                         const __grid_constant__ CUtensorMap tma_b, const KParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
+    const int lane = threadIdx.x & 31;
+
+    const uint32_t full0 = smem_u32(bars);
+    const uint32_t empty0 = smem_u32(bars + STAGES);
+    const uint32_t tfull0 = smem_u32(bars + 2 * STAGES);
+    const uint32_t tempty0 = smem_u32(bars + 2 * STAGES + 2);
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        prefetch_tensormap(&tma_a);
+        prefetch_tensormap(&tma_b);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull0 + 8 * a, 1);
+            mbar_init(tempty0 + 8 * a, 4);
+        }
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+        tmem_alloc_cg1(smem_u32(tmem_slot), TMEM_COLS);
+        tmem_relinquish_cg1();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    WaitCtx wc{abort_flag, p.wait_limit_ns};
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool alive = true;
+            for (int t = blockIdx.x; t < p.num_tiles && alive; t += gridDim.x) {
+                Tile tl = decode_tile(p, t);
+                if (tl.skip || tl.k_blocks == 0)
+                    continue;
+                if (p.a_ready != nullptr) {
+                    // all_gather fusion: rows of this m-block arrive from another GPU;
+                    // wait (bounded) for the shard's ready counter.
+                    const uint32_t* f = p.a_ready + tl.m0 / p.rows_per_flag;
+                    uint32_t spins = 0;
+                    uint64_t t0 = 0;
+                    while (ld_acquire_gpu(f) < p.a_ready_target) {
+                        if ((++spins & 0x3f) == 0) {
+                            uint64_t now = globaltimer_ns();
+                            if (t0 == 0)
+                                t0 = now;
+                            if (*abort_flag || now - t0 > p.wait_limit_ns) {
+                                *abort_flag = 1;
+                                alive = false;
+                                break;
+                            }
+                        }
+                    }
+                    if (!alive)
+                        break;
+                    fence_proxy_async();  // data written by generic-proxy stores, read by TMA
+                }
+                for (int kb = 0; kb < tl.k_blocks; ++kb) {
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1, wc)) {
+                        alive = false;
+                        break;
+                    }
+                    const uint32_t fb = full0 + 8 * s;
+                    mbar_expect_tx(fb, STAGE_BYTES);
+                    const int k = tl.k0 + kb * BK;
+                    const uint32_t sa = smem_u32(smem_a + s * A_STAGE_BYTES);
+                    const uint32_t sb = smem_u32(smem_b + s * B_STAGE_BYTES);
+                    if (!A_MN) {
+                        tma_load_2d(sa, &tma_a, fb, k, tl.m0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BM / 64; ++j)
+                            tma_load_2d(sa + j * MN_CHUNK_BYTES, &tma_a, fb, tl.m0 + 64 * j, k);
+                    }
+                    if (!B_MN) {
+                        tma_load_2d(sb, &tma_b, fb, k, tl.b_row + tl.n0);
+                        tma_load_2d(sb + B_STAGE_BYTES / 2, &tma_b, fb, k,
+                                    tl.b_row + tl.n0 + p.b_half_off);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_2d(sb + j * MN_CHUNK_BYTES, &tma_b, fb, tl.n0 + 64 * j,
+                                        tl.b_row + k);
+                    }
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------ UMMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN, A_MN, B_MN);
+            int s = 0;
+            uint32_t ph = 0;
+            int acc = 0;
+            uint32_t acc_ph = 0;
+            bool alive = true;
+            for (int t = blockIdx.x; t < p.num_tiles && alive; t += gridDim.x) {
+                Tile tl = decode_tile(p, t);
+                if (tl.skip || tl.k_blocks == 0)
+                    continue;
+                if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1, wc))
+                    break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < tl.k_blocks; ++kb) {
+                    if (!mbar_wait(full0 + 8 * s, ph, wc)) {
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem_a + s * A_STAGE_BYTES);
+                    const uint32_t sb = smem_u32(smem_b + s * B_STAGE_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        // K-major: 16 k = 32 bytes inside the 128 B row.
+                        // MN-major: 16 k = 16 rows of 128 B.
+                        const uint64_t ad =
+                                A_MN ? umma_smem_desc_sw128(sa + kk * (UMMA_K * 128), MN_CHUNK_BYTES,
+                                                            1024)
+                                     : umma_smem_desc_sw128(sa + kk * (UMMA_K * 2), 16, 1024);
+                        const uint64_t bd =
+                                B_MN ? umma_smem_desc_sw128(sb + kk * (UMMA_K * 128), MN_CHUNK_BYTES,
+                                                            1024)
+                                     : umma_smem_desc_sw128(sb + kk * (UMMA_K * 2), 16, 1024);
+                        umma_f16_cg1(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit_cg1(empty0 + 8 * s);  // frees the smem stage when the MMAs retire
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (!alive)
+                    break;
+                umma_commit_cg1(tfull0 + 8 * acc);  // accumulator complete
+                acc ^= 1;
+                if (acc == 0)
+                    acc_ph ^= 1;
+            }
+        }
+    } else {
+        // ------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        bool alive = true;
+        for (int t = blockIdx.x; t < p.num_tiles && alive; t += gridDim.x) {
+            Tile tl = decode_tile(p, t);
+            if (tl.skip)
+                continue;
+            const int row_in_tile = q * 32 + lane;
+            const int m = tl.m0 + row_in_tile;
+            const bool row_ok = m < p.M;
+            const long drow = tl.d_row0 + row_in_tile;
+            const bool zero_tile = tl.k_blocks == 0;
+            if (!zero_tile) {
+                // the whole warp must agree before the .sync.aligned TMEM loads
+                const bool got = mbar_wait(tfull0 + 8 * acc, acc_ph, wc);
+                if (!__all_sync(0xffffffffu, got))
+                    break;
+                tc_fence_after();
+            }
+            const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+
+            if (EPI == EPI_SWIGLU) {
+                // columns [0,128) = gate, [128,256) = up of output columns n0..n0+127
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t rg[32], ru[32];
+                    tmem_ld_32x32b_x32(t_addr + c * 32, rg);
+                    tmem_ld_32x32b_x32(t_addr + 128 + c * 32, ru);
+                    tmem_ld_wait();
+                    const int col = tl.n0 + c * 32;
+                    const int ok = p.N - col;
+                    if (row_ok && ok > 0) {
+                        float g[32], u[32], h[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            g[i] = __uint_as_float(rg[i]);
+                            u[i] = __uint_as_float(ru[i]);
+                            h[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+                        }
+                        store_row32(p.D + drow * p.ldd + col, g, ok);
+                        store_row32(p.D + drow * p.ldd + p.aux_off + col, u, ok);
+                        store_row32(p.D2 + drow * p.ldd2 + col, h, ok);
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    if (!zero_tile) {
+                        tmem_ld_32x32b_x32(t_addr + c * 32, r);
+                        tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            r[i] = 0u;
+                    }
+                    const int col = tl.n0 + c * 32;
+                    const int ok = p.N - col;
+                    if (!row_ok || ok <= 0)
+                        continue;
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        v[i] = __uint_as_float(r[i]);
+                    if (EPI == EPI_STORE) {
+                        store_row32(p.D + drow * p.ldd + col, v, ok);
+                    } else if (EPI == EPI_ACCUM) {
+                        float o[32];
+                        load_row32(p.D + drow * p.ldd + col, o, ok);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            v[i] += o[i];
+                        store_row32(p.D + drow * p.ldd + col, v, ok);
+                    } else if (EPI == EPI_DSWIGLU) {
+                        float g[32], u[32];
+                        load_row32(p.aux + drow * p.ldaux + col, g, ok);
+                        load_row32(p.aux + drow * p.ldaux + p.aux_off + col, u, ok);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float sg = 1.f / (1.f + __expf(-g[i]));
+                            const float dh = v[i];
+                            const float silu = g[i] * sg;
+                            u[i] = dh * u[i] * (sg + silu * (1.f - sg));  // dG
+                            g[i] = dh * silu;                              // dU
+                        }
+                        store_row32(p.D + drow * p.ldd + col, u, ok);
+                        store_row32(p.D + drow * p.ldd + p.aux_off + col, g, ok);
+                    } else if (EPI == EPI_PUSH) {
+                        // output rows are sharded over GPUs: a whole m-block has one owner
+                        const int peer = static_cast<int>(drow / p.rows_per_peer);
+                        const long prow = drow - static_cast<long>(peer) * p.rows_per_peer;
+                        __nv_bfloat16* base = static_cast<__nv_bfloat16*>(p.peer_out[peer]);
+                        store_row32(base + prow * p.ldd + col, v, ok);
+                    }
+                }
+            }
+            if (!zero_tile) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(tempty0 + 8 * acc);
+                acc ^= 1;
+                if (acc == 0)
+                    acc_ph ^= 1;
+            }
+        }
+    }
+
+    // ---------------------------------------------------------- teardown
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // A wait ran out.  TMA copies already issued complete on their own within
+        // microseconds (their source is local memory); give them that time before
+        // shared memory is released, then report.
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000) {
+        }
+        if (threadIdx.x == 0 && p.error_flag != nullptr)
+            atomicExch(p.error_flag, 1);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_cg1(tmem_base, TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) ==
+                    cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(f);
+    });
+    return fn;
+}
+
+// bf16 matrix, `inner` contiguous elements per row, `outer` rows `ld` elements apart;
+// box = 64 inner elements (128 B, the swizzle span) x `box_rows`.
+bool make_map(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
+              uint32_t box_rows) {
+    auto fn = get_encode_fn();
+    if (fn == nullptr)
+        return false;
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+std::atomic<uint64_t> g_launches{0};
+
+template <bool A_MN, bool B_MN, int EPI>
+cudaError_t launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const KParams& kp, int grid,
+                     cudaStream_t stream) {
+    auto kern = gemm_bf16_kernel<A_MN, B_MN, EPI>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    // one attribute set per device would be needed for multi-device processes; set every call
+    // when more than one device is visible to this process
+    int dev = 0;
+    cudaGetDevice(&dev);
+    static std::mutex mu;
+    static std::map<int, bool> done;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!done[dev]) {
+            attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            SMEM_BYTES);
+            if (attr_err != cudaSuccess)
+                return attr_err;
+            done[dev] = true;
+        }
+    }
+    (void)once;
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, kp);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    count_launch();
+    return cudaGetLastError();
+}
+
+template <bool A_MN, bool B_MN>
+cudaError_t launch_e(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const KParams& kp,
+                     int grid, cudaStream_t stream) {
+    switch (epi) {
+        case EPI_STORE:
+            return launch_t<A_MN, B_MN, EPI_STORE>(ma, mb, kp, grid, stream);
+        case EPI_ACCUM:
+            return launch_t<A_MN, B_MN, EPI_ACCUM>(ma, mb, kp, grid, stream);
+        case EPI_PUSH:
+            return launch_t<A_MN, B_MN, EPI_PUSH>(ma, mb, kp, grid, stream);
+        case EPI_DSWIGLU:
+            return launch_t<A_MN, B_MN, EPI_DSWIGLU>(ma, mb, kp, grid, stream);
+        case EPI_SWIGLU:
+            if (B_MN)
+                return cudaErrorInvalidValue;
+            return launch_t<A_MN, false, EPI_SWIGLU>(ma, mb, kp, grid, stream);
+        default:
+            return cudaErrorInvalidValue;
+    }
+}
+
+int sm_count() {
+    static std::mutex mu;
+    static std::map<int, int> cache;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(dev);
+    if (it != cache.end())
+        return it->second;
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cache[dev] = n;
+    return n;
+}
+
+}  // namespace
+
+uint64_t gemm_launch_count() { return g_launches.load(std::memory_order_relaxed); }
+
+cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
+    if (a.M <= 0 || a.N <= 0 || a.K <= 0)
+        return cudaErrorInvalidValue;
+    if ((a.lda % 8) || (a.ldb % 8) || (a.ldd % 8))
+        return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.B) |
+         reinterpret_cast<uintptr_t>(a.D)) & 15)
+        return cudaErrorInvalidValue;
+    const bool grouped_m = a.grouped.m_block_group != nullptr;
+    const bool grouped_k = a.grouped.k_begin != nullptr;
+
+    KParams kp{};
+    kp.M = a.M;
+    kp.N = a.N;
+    kp.K = a.K;
+    kp.m_blocks = (a.M + BM - 1) / BM;
+    kp.n_tile_stride = (a.epilogue == EPI_SWIGLU) ? 128 : BN;
+    kp.b_half_off = (a.epilogue == EPI_SWIGLU) ? a.aux_off : 128;
+    kp.n_blocks = (a.N + kp.n_tile_stride - 1) / kp.n_tile_stride;
+    kp.num_tiles = kp.m_blocks * kp.n_blocks * (grouped_k ? a.grouped.groups : 1);
+    kp.group_m = 8;
+    kp.m_rot = (a.m_rot % kp.m_blocks + kp.m_blocks) % kp.m_blocks;
+    kp.D = static_cast<__nv_bfloat16*>(a.D);
+    kp.ldd = a.ldd;
+    kp.D2 = static_cast<__nv_bfloat16*>(a.D2);
+    kp.ldd2 = a.ldd2;
+    kp.aux = static_cast<const __nv_bfloat16*>(a.aux);
+    kp.ldaux = a.ldaux;
+    kp.aux_off = a.aux_off;
+    kp.a_ready = a.a_ready;
+    kp.rows_per_flag = a.rows_per_flag > 0 ? a.rows_per_flag : BM;
+    kp.a_ready_target = a.a_ready_target;
+    kp.peer_out = a.peer_out;
+    kp.rows_per_peer = a.rows_per_peer > 0 ? a.rows_per_peer : a.M;
+    kp.m_block_group = a.grouped.m_block_group;
+    kp.group_rows_b = a.grouped.group_rows_b;
+    kp.k_begin = a.grouped.k_begin;
+    kp.k_end = a.grouped.k_end;
+    kp.error_flag = a.error_flag;
+    kp.wait_limit_ns = a.wait_limit_ns ? a.wait_limit_ns : 4000000000ull;
+
+    if (a.epilogue == EPI_SWIGLU && (a.D2 == nullptr || (a.ldd2 % 8)))
+        return cudaErrorInvalidValue;
+    if (a.epilogue == EPI_DSWIGLU && (a.aux == nullptr || (a.ldaux % 8)))
+        return cudaErrorInvalidValue;
+    if (a.epilogue == EPI_PUSH && (a.peer_out == nullptr || (kp.rows_per_peer % BM)))
+        return cudaErrorInvalidValue;
+
+    // Extents the tensor maps cover.  Grouped problems stack the groups along the
+    // outer dimension of B (and of A for grouped-K).
+    const uint64_t groups = (grouped_m || grouped_k) ? static_cast<uint64_t>(a.grouped.groups) : 1;
+    CUtensorMap ma, mb;
+    bool ok;
+    if (!a.a_mn) {
+        ok = make_map(&ma, a.A, a.K, a.M, a.lda, BM);
+    } else {
+        // stored [K, M]; for grouped-K, K counts the rows of all groups together
+        ok = make_map(&ma, a.A, a.M, a.K, a.lda, BK);
+    }
+    if (!ok)
+        return cudaErrorInvalidValue;
+    if (!a.b_mn) {
+        // SwiGLU pairing reads rows n and n+aux_off: the map spans both halves.
+        uint64_t rows = (a.epilogue == EPI_SWIGLU) ? static_cast<uint64_t>(a.aux_off) + a.N
+                                                   : static_cast<uint64_t>(a.N);
+        if (grouped_m)
+            rows = groups * static_cast<uint64_t>(a.grouped.group_rows_b);
+        ok = make_map(&mb, a.B, a.K, rows, a.ldb, 128);
+    } else {
+        uint64_t krows = static_cast<uint64_t>(a.K);
+        if (grouped_m)
+            krows = groups * static_cast<uint64_t>(a.grouped.group_rows_b);
+        ok = make_map(&mb, a.B, a.N, krows, a.ldb, BK);
+    }
+    if (!ok)
+        return cudaErrorInvalidValue;
+
+    int grid = sm_count();
+    if (a.sm_limit > 0 && a.sm_limit < grid)
+        grid = a.sm_limit;
+    if (grid > kp.num_tiles)
+        grid = kp.num_tiles;
+
+    if (!a.a_mn && !a.b_mn)
+        return launch_e<false, false>(a.epilogue, ma, mb, kp, grid, stream);
+    if (!a.a_mn && a.b_mn)
+        return launch_e<false, true>(a.epilogue, ma, mb, kp, grid, stream);
+    if (a.a_mn && !a.b_mn)
+        return launch_e<true, false>(a.epilogue, ma, mb, kp, grid, stream);
+    return launch_e<true, true>(a.epilogue, ma, mb, kp, grid, stream);
+}
+
+}  // namespace gemm
+}  // namespace megray
