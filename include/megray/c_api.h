@@ -43,6 +43,77 @@ typedef struct {
 
 int megray_gemm_bf16(const megray_gemm_args* args, void* stream);
 
+
+/* ---- rendezvous ------------------------------------------------------------- */
+int megray_get_host_ip(char* buf, size_t buflen);           /* 0 ok, 1 none */
+int megray_get_free_port(void);                             /* port or -1 */
+int megray_create_server(uint32_t nranks, int port);        /* free-function server */
+void* megray_server_new(uint32_t nranks, int port);         /* RAII server; NULL on failure */
+int megray_server_port(void* server);
+int megray_server_running(void* server);
+int megray_server_status(void* server);
+uint64_t megray_server_requests(void* server);
+void megray_server_stop(void* server);
+void megray_server_delete(void* server);
+
+void* megray_client_new(uint32_t nranks, uint32_t rank);
+void megray_client_set_timeout_ms(void* client, int64_t ms);
+int megray_client_connect(void* client, const char* ip, int port);
+int megray_client_barrier(void* client);
+int megray_client_broadcast(void* client, const void* send, void* recv, size_t len, uint32_t root);
+int megray_client_allgather(void* client, const void* send, void* recv, size_t len);
+void megray_client_delete(void* client);
+
+/* ---- communicators ---------------------------------------------------------- */
+/* ctx_type: 0 = host buffers (HostContext), 1 = CUDA stream (CudaContext, `stream` is the
+ * cudaStream_t value).  dtype / op / backend take the MegRay enum values. */
+void* megray_comm_new(uint32_t nranks, uint32_t rank, int backend); /* NULL: unknown backend */
+void megray_comm_delete(void* comm);
+int megray_comm_init(void* comm, const char* ip, int port);
+int megray_comm_backend(void* comm);
+int megray_comm_status(void* comm);
+void megray_comm_abort(void* comm);
+/* out[0..8) = calls, bytes, kernels, timeouts, oneshot, twoshot, nvls, copy */
+void megray_comm_stats(void* comm, uint64_t* out);
+
+int megray_send(void* comm, const void* buf, size_t len, int dtype, uint32_t peer, int ctx_type, void* stream);
+int megray_recv(void* comm, void* buf, size_t len, int dtype, uint32_t peer, int ctx_type, void* stream);
+int megray_scatter(void* comm, const void* send, void* recv, size_t recvlen, int dtype, uint32_t root, int ctx_type, void* stream);
+int megray_gather(void* comm, const void* send, void* recv, size_t sendlen, int dtype, uint32_t root, int ctx_type, void* stream);
+int megray_all_to_all(void* comm, const void* send, void* recv, size_t len, int dtype, int ctx_type, void* stream);
+int megray_all_gather(void* comm, const void* send, void* recv, size_t sendlen, int dtype, int ctx_type, void* stream);
+int megray_all_reduce(void* comm, const void* send, void* recv, size_t len, int dtype, int op, int ctx_type, void* stream);
+int megray_reduce_scatter(void* comm, const void* send, void* recv, size_t recvlen, int dtype, int op, int ctx_type, void* stream);
+int megray_broadcast(void* comm, const void* send, void* recv, size_t len, int dtype, uint32_t root, int ctx_type, void* stream);
+int megray_reduce(void* comm, const void* send, void* recv, size_t len, int dtype, int op, uint32_t root, int ctx_type, void* stream);
+int megray_group_start(void* comm);
+int megray_group_end(void* comm);
+int megray_host_barrier(void* comm);              /* host backend only */
+void megray_host_set_timeout_ms(void* comm, int64_t ms);
+
+/* ---- native NVLink backend extras (return 7 = INVALID_USAGE on other backends) ------- */
+void* megray_nvl_alloc(void* comm, size_t bytes, size_t* offset_out);
+int megray_nvl_free(void* comm, void* ptr);
+void* megray_nvl_peer_ptr(void* comm, void* ptr, uint32_t peer);
+void* megray_nvl_heap_base(void* comm, uint32_t peer);
+size_t megray_nvl_heap_bytes(void* comm);
+int megray_nvl_all_reduce_scaled(void* comm, const void* send, void* recv, size_t len, int in_dtype,
+                                 int out_dtype, float scale, int op, void* stream);
+int megray_nvl_stream_barrier(void* comm, void* stream);
+void megray_nvl_set_device_timeout_ms(void* comm, int64_t ms);
+
+/* ---- host arithmetic (the oracle) and stand-alone device reduction ----------------------- */
+int megray_cpu_reduce_n(const void* const* in, int n_in, void* out, size_t len, int dtype, int op);
+int megray_cpu_reduce_scale_cast(const void* const* in, int n_in, int in_dtype, void* out,
+                                 int out_dtype, size_t len, int op, double scale);
+int megray_reduce_n(const void* const* in, int n_in, void* out, size_t len, int in_dtype,
+                    int out_dtype, int op, float scale, void* stream);
+
+size_t megray_dtype_size(int dtype);   /* 0 for an unknown dtype */
+void megray_set_log_level(int level);
+void megray_trace_enable(const char* path);
+size_t megray_trace_dump(void);
+
 /* Kernels launched by this library since it was loaded (all modules). */
 uint64_t megray_launch_count(void);
 

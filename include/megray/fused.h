@@ -1,0 +1,68 @@
+/**
+ * Entry points of the native NVLink backend that go beyond the MegRay
+ * interface: symmetric memory, the fused scale/cast all_reduce, and (declared
+ * in the headers named below) the GEMM-fused and MoE collectives.  None of
+ * these has a counterpart in the reference, whose interface ends at
+ * include/megray/communicator.h:60-109.
+ *
+ * Obtain the interface from a communicator made with MEGRAY_NVL:
+ *     auto comm = MegRay::get_communicator(n, r, MegRay::MEGRAY_NVL);
+ *     auto* nvl = MegRay::as_nvl(comm.get());
+ */
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#include <memory>
+
+#include "megray/communicator.h"
+
+namespace MegRay {
+
+class NvlInterface {
+public:
+    virtual ~NvlInterface() = default;
+
+    /** Symmetric allocation: every rank must call with the same size in the same order.
+     *  The returned pointer is device memory of this rank; peers reach it with peer_ptr().
+     *  `offset_out` (optional) receives the offset inside the heap, equal on all ranks. */
+    virtual void* sym_alloc(size_t bytes, size_t* offset_out = nullptr) = 0;
+    /** Release the most recent allocations down to (and including) `ptr`: the allocator is a
+     *  stack, which keeps offsets identical on all ranks without any communication. */
+    virtual Status sym_free(void* ptr) = 0;
+    /** Address, in this rank's address space, of `ptr`'s twin on rank `peer`. */
+    virtual void* peer_ptr(void* ptr, uint32_t peer) = 0;
+    /** True if [ptr, ptr+bytes) lies inside this rank's symmetric heap. */
+    virtual bool in_heap(const void* ptr, size_t bytes) = 0;
+    virtual size_t heap_bytes() = 0;
+    /** Base address of rank `peer`'s heap as mapped here. */
+    virtual void* heap_base(uint32_t peer) = 0;
+
+    /**
+     * out = cast<out_dtype>(scale * reduce_op(in over ranks)): the gradient-bucket path.
+     * Floating dtypes (fp16, bf16, fp32; fp64 with out_dtype == in_dtype); scale applies to SUM.
+     */
+    virtual Status all_reduce_scaled(const void* sendbuff, void* recvbuff, size_t len,
+                                     DType in_dtype, DType out_dtype, float scale, ReduceOp op,
+                                     std::shared_ptr<Context> ctx) = 0;
+
+    /** Barrier on the stream: later work of every rank starts after earlier work of all ranks. */
+    virtual Status stream_barrier(std::shared_ptr<Context> ctx) = 0;
+
+    /** Next flag epoch for kernels of other modules that synchronise through the pad
+     *  (`count` consecutive values are reserved). */
+    virtual uint32_t reserve_epochs(uint32_t count) = 0;
+    /** Byte offset, inside every heap, of a flag area reserved for fused kernels. */
+    virtual size_t fused_flag_offset() = 0;
+    /** Device-visible status word of this communicator (0 = ok). */
+    virtual int* status_word() = 0;
+    /** Limit of one in-kernel wait, in nanoseconds. */
+    virtual uint64_t device_timeout_ns() = 0;
+    /** Override it (tests of the timeout path use a short limit). */
+    virtual void set_device_timeout_ms(int64_t ms) = 0;
+};
+
+/** The NVL interface of `comm`, or nullptr if it is another backend. */
+NvlInterface* as_nvl(Communicator* comm);
+
+}  // namespace MegRay

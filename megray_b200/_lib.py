@@ -50,6 +50,71 @@ class GemmArgs(C.Structure):
     ]
 
 
+def _declare(lib) -> None:
+    """argtypes / restype of the C interface (include/megray/c_api.h)."""
+    vp, u32, u64, i32, i64, sz = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int, C.c_int64, C.c_size_t
+    P = C.POINTER
+
+    def d(name, res, *args):
+        f = getattr(lib, name)
+        f.restype = res
+        f.argtypes = list(args)
+
+    d("megray_get_host_ip", i32, C.c_char_p, sz)
+    d("megray_get_free_port", i32)
+    d("megray_create_server", i32, u32, i32)
+    d("megray_server_new", vp, u32, i32)
+    d("megray_server_port", i32, vp)
+    d("megray_server_running", i32, vp)
+    d("megray_server_status", i32, vp)
+    d("megray_server_requests", u64, vp)
+    d("megray_server_stop", None, vp)
+    d("megray_server_delete", None, vp)
+    d("megray_client_new", vp, u32, u32)
+    d("megray_client_set_timeout_ms", None, vp, i64)
+    d("megray_client_connect", i32, vp, C.c_char_p, i32)
+    d("megray_client_barrier", i32, vp)
+    d("megray_client_broadcast", i32, vp, vp, vp, sz, u32)
+    d("megray_client_allgather", i32, vp, vp, vp, sz)
+    d("megray_client_delete", None, vp)
+    d("megray_comm_new", vp, u32, u32, i32)
+    d("megray_comm_delete", None, vp)
+    d("megray_comm_init", i32, vp, C.c_char_p, i32)
+    d("megray_comm_backend", i32, vp)
+    d("megray_comm_status", i32, vp)
+    d("megray_comm_abort", None, vp)
+    d("megray_comm_stats", None, vp, P(u64))
+    d("megray_send", i32, vp, vp, sz, i32, u32, i32, vp)
+    d("megray_recv", i32, vp, vp, sz, i32, u32, i32, vp)
+    d("megray_scatter", i32, vp, vp, vp, sz, i32, u32, i32, vp)
+    d("megray_gather", i32, vp, vp, vp, sz, i32, u32, i32, vp)
+    d("megray_all_to_all", i32, vp, vp, vp, sz, i32, i32, vp)
+    d("megray_all_gather", i32, vp, vp, vp, sz, i32, i32, vp)
+    d("megray_all_reduce", i32, vp, vp, vp, sz, i32, i32, i32, vp)
+    d("megray_reduce_scatter", i32, vp, vp, vp, sz, i32, i32, i32, vp)
+    d("megray_broadcast", i32, vp, vp, vp, sz, i32, u32, i32, vp)
+    d("megray_reduce", i32, vp, vp, vp, sz, i32, i32, u32, i32, vp)
+    d("megray_group_start", i32, vp)
+    d("megray_group_end", i32, vp)
+    d("megray_host_barrier", i32, vp)
+    d("megray_host_set_timeout_ms", None, vp, i64)
+    d("megray_nvl_alloc", vp, vp, sz, P(sz))
+    d("megray_nvl_free", i32, vp, vp)
+    d("megray_nvl_peer_ptr", vp, vp, vp, u32)
+    d("megray_nvl_heap_base", vp, vp, u32)
+    d("megray_nvl_heap_bytes", sz, vp)
+    d("megray_nvl_all_reduce_scaled", i32, vp, vp, vp, sz, i32, i32, C.c_float, i32, vp)
+    d("megray_nvl_stream_barrier", i32, vp, vp)
+    d("megray_nvl_set_device_timeout_ms", None, vp, i64)
+    d("megray_cpu_reduce_n", i32, P(vp), i32, vp, sz, i32, i32)
+    d("megray_cpu_reduce_scale_cast", i32, P(vp), i32, i32, vp, i32, sz, i32, C.c_double)
+    d("megray_reduce_n", i32, P(vp), i32, vp, sz, i32, i32, i32, C.c_float, vp)
+    d("megray_dtype_size", sz, i32)
+    d("megray_set_log_level", None, i32)
+    d("megray_trace_enable", None, C.c_char_p)
+    d("megray_trace_dump", sz)
+
+
 def load(build_if_missing: bool = True) -> C.CDLL:
     """Load the native library (building it first when it is absent)."""
     global _lib
@@ -67,5 +132,6 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         lib.megray_gemm_bf16.restype = C.c_int
         lib.megray_launch_count.argtypes = []
         lib.megray_launch_count.restype = C.c_uint64
+        _declare(lib)
         _lib = lib
         return lib

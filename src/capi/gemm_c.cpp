@@ -6,7 +6,7 @@
 extern "C" int megray_gemm_bf16(const megray_gemm_args* a, void* stream) {
     if (a == nullptr)
         return 6;
-    megray::gemm::GemmArgs g{};
+    mgk::gemm::GemmArgs g{};
     g.A = a->A;
     g.B = a->B;
     g.D = a->D;
@@ -38,8 +38,8 @@ extern "C" int megray_gemm_bf16(const megray_gemm_args* a, void* stream) {
     g.grouped.groups = a->groups;
     g.error_flag = a->error_flag;
     g.wait_limit_ns = a->wait_limit_ns;
-    cudaError_t e = megray::gemm::launch_gemm_bf16(g, static_cast<cudaStream_t>(stream));
+    cudaError_t e = mgk::gemm::launch_gemm_bf16(g, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }
 
-extern "C" uint64_t megray_launch_count(void) { return megray::launch_count(); }
+extern "C" uint64_t megray_launch_count(void) { return mgk::launch_count(); }

@@ -26,10 +26,10 @@
 #include "launch_count.h"
 #include "ptx_sm100.cuh"
 
-namespace megray {
+namespace mgk {
 namespace gemm {
 
-using namespace megray::ptx;
+using namespace mgk::ptx;
 
 namespace {
 
@@ -668,4 +668,4 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace gemm
-}  // namespace megray
+}  // namespace mgk

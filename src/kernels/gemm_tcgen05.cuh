@@ -10,7 +10,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-namespace megray {
+namespace mgk {
 namespace gemm {
 
 enum Epilogue : int {
@@ -68,4 +68,4 @@ cudaError_t launch_gemm_bf16(const GemmArgs& args, cudaStream_t stream);
 uint64_t gemm_launch_count();
 
 }  // namespace gemm
-}  // namespace megray
+}  // namespace mgk

@@ -4,11 +4,11 @@
 #include <atomic>
 #include <stdint.h>
 
-namespace megray {
+namespace mgk {
 inline std::atomic<uint64_t>& launch_counter() {
     static std::atomic<uint64_t> c{0};
     return c;
 }
 inline void count_launch(uint64_t n = 1) { launch_counter().fetch_add(n, std::memory_order_relaxed); }
 inline uint64_t launch_count() { return launch_counter().load(std::memory_order_relaxed); }
-}  // namespace megray
+}  // namespace mgk

@@ -8,7 +8,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-namespace megray {
+namespace mgk {
 namespace ptx {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -281,4 +281,4 @@ __device__ __forceinline__ void red_release_gpu_add(uint32_t* p, uint32_t v) {
 }
 
 }  // namespace ptx
-}  // namespace megray
+}  // namespace mgk

@@ -1,0 +1,705 @@
+#include "nvl/nvl_communicator.h"
+
+#include <string.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <random>
+
+#include "megray/cuda_context.h"
+#include "megray/options.h"
+#include "megray/trace.h"
+
+#ifdef MEGRAY_WITH_NCCL
+#include "nccl/nccl_communicator.h"
+#endif
+
+namespace MegRay {
+
+using mgk::coll::CommonArgs;
+using mgk::coll::ExchangeArgs;
+using mgk::coll::kMaxCtas;
+using mgk::coll::kMaxRanks;
+using mgk::coll::ReduceArgs;
+
+namespace {
+
+size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+size_t round_down(size_t v, size_t a) { return v / a * a; }
+
+int64_t env_i64(const char* name, int64_t dflt) {
+    const char* e = getenv(name);
+    if (e == nullptr || *e == 0)
+        return dflt;
+    return atoll(e);
+}
+
+bool is_float(DType t) {
+    return t == MEGRAY_FLOAT16 || t == MEGRAY_BFLOAT16 || t == MEGRAY_FLOAT32 ||
+           t == MEGRAY_FLOAT64;
+}
+
+}  // namespace
+
+NvlInterface* as_nvl(Communicator* comm) { return dynamic_cast<NvlInterface*>(comm); }
+
+NvlCommunicator::NvlCommunicator(uint32_t nranks, uint32_t rank) : Communicator(nranks, rank) {
+    const Options& o = global_options();
+    m_timeout_ns = static_cast<uint64_t>(o.device_timeout_ms) * 1000000ull;
+    m_max_ctas = o.max_ctas > 0 ? std::min(o.max_ctas, kMaxCtas) : 64;
+    m_oneshot_bytes = static_cast<size_t>(env_i64("MEGRAY_ONESHOT_BYTES", 256 * 1024));
+    if (o.algo == "oneshot")
+        m_oneshot_bytes = ~static_cast<size_t>(0);
+    else if (o.algo == "twoshot")
+        m_oneshot_bytes = 0;
+}
+
+NvlCommunicator::~NvlCommunicator() {
+    if (m_ready) {
+        cudaSetDevice(m_heap.device());
+        cudaDeviceSynchronize();
+    }
+    m_p2p.reset();
+    if (m_last_event != nullptr)
+        cudaEventDestroy(m_last_event);
+    if (m_status_host != nullptr)
+        cudaFreeHost(m_status_host);
+    // peers may still be inside their last kernel reading this rank's heap: meet first
+    if (m_ready && m_client && m_client->connected() && !m_aborted.load())
+        m_client->barrier();
+    m_heap.destroy();
+}
+
+Status NvlCommunicator::check_cuda(cudaError_t e) {
+    if (e == cudaSuccess)
+        return MEGRAY_OK;
+    MEGRAY_ERROR("cuda error [%d]: %s", e, cudaGetErrorString(e));
+    if (m_error == MEGRAY_OK)
+        m_error = MEGRAY_CUDA_ERR;
+    return MEGRAY_CUDA_ERR;
+}
+
+Status NvlCommunicator::do_init(BcastCallback cb) {
+    // No server was given: rank 0 starts a private one and publishes its address
+    // through the caller's broadcast.
+    struct {
+        char ip[64];
+        int32_t port;
+    } where;
+    memset(&where, 0, sizeof(where));
+    if (m_rank == 0) {
+        m_own_server.reset(new Server(m_nranks, 0));
+        char* ip = get_host_ip();
+        snprintf(where.ip, sizeof(where.ip), "%s", ip != nullptr ? ip : "127.0.0.1");
+        delete[] ip;
+        where.port = m_own_server->port();
+    }
+    cb(reinterpret_cast<char*>(&where), sizeof(where));
+    where.ip[sizeof(where.ip) - 1] = 0;
+    m_client = std::make_shared<Client>(m_nranks, m_rank);
+    Status s = m_client->connect(where.ip, where.port);
+    if (s != MEGRAY_OK && strcmp(where.ip, "127.0.0.1") != 0)
+        s = m_client->connect("127.0.0.1", where.port);
+    MEGRAY_CHECK(s);
+    return do_init();
+}
+
+Status NvlCommunicator::do_init() {
+    if (m_nranks > static_cast<uint32_t>(kMaxRanks)) {
+        MEGRAY_ERROR("NVL backend supports up to %d ranks", kMaxRanks);
+        return MEGRAY_INVALID_ARGUMENT;
+    }
+    const Options& o = global_options();
+    // a name for this group on this machine
+    uint64_t gid = 0;
+    if (m_rank == 0) {
+        std::random_device rd;
+        gid = (static_cast<uint64_t>(rd()) << 32) ^ rd() ^ (static_cast<uint64_t>(getpid()) << 20);
+    }
+    MEGRAY_CHECK(m_client->broadcast(&gid, &gid, sizeof(gid), 0));
+    char group[32];
+    snprintf(group, sizeof(group), "%016llx", static_cast<unsigned long long>(gid));
+
+    const size_t heap_bytes = static_cast<size_t>(o.heap_mb) << 20;
+    MEGRAY_CHECK(m_heap.create(m_client.get(), m_nranks, m_rank, heap_bytes, group, o.nvls));
+
+    m_ws_bytes = static_cast<size_t>(env_i64("MEGRAY_WORKSPACE_MB", 0)) << 20;
+    if (m_ws_bytes == 0)
+        m_ws_bytes = std::min<size_t>(192ull << 20, m_heap.bytes() / 8);
+    m_ws_bytes = round_down(m_ws_bytes, 4096);
+    m_user_off = round_up(kWorkspaceOff + 2 * m_ws_bytes, 1 << 20);
+    if (m_user_off >= m_heap.bytes()) {
+        MEGRAY_ERROR("heap of %zu bytes is too small for two %zu-byte workspaces", m_heap.bytes(),
+                     m_ws_bytes);
+        return MEGRAY_INVALID_ARGUMENT;
+    }
+    m_user_top = m_user_off;
+
+    CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&m_status_host), 64, cudaHostAllocMapped));
+    memset(m_status_host, 0, 64);
+    CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&m_status_dev), m_status_host, 0));
+    CUDA_CHECK(cudaEventCreateWithFlags(&m_last_event, cudaEventDisableTiming));
+
+#ifdef MEGRAY_WITH_NCCL
+    // point-to-point engine
+    if (m_nranks > 1 && env_i64("MEGRAY_NVL_P2P", 1) != 0) {
+        m_p2p.reset(new NcclCommunicator(m_nranks, m_rank));
+        std::shared_ptr<Client> client = m_client;
+        Status s = m_p2p->init([client](char* buf, size_t len) { client->broadcast(buf, buf, len, 0); });
+        if (s != MEGRAY_OK) {
+            MEGRAY_WARN("NCCL point-to-point engine unavailable (status %d): send/recv disabled", s);
+            m_p2p.reset();
+        }
+    }
+#endif
+    m_ready = true;
+    return m_client->barrier();
+}
+
+Status NvlCommunicator::begin(const std::shared_ptr<Context>& ctx, cudaStream_t* stream) {
+    if (!m_ready) {
+        MEGRAY_ERROR("communicator used before init");
+        return MEGRAY_INVALID_USAGE;
+    }
+    if (m_aborted.load())
+        return MEGRAY_ABORTED;
+    if (!ctx || ctx->type() != MEGRAY_CTX_CUDA) {
+        MEGRAY_ERROR("NVL backend needs a CudaContext");
+        return MEGRAY_INVALID_ARGUMENT;
+    }
+    if (*m_status_host != 0) {  // an earlier kernel gave up waiting
+        if (m_error == MEGRAY_OK) {
+            m_error = static_cast<Status>(*m_status_host);
+            m_stats.timeouts++;
+        }
+        return m_error;
+    }
+    if (m_error != MEGRAY_OK)
+        return m_error;
+    *stream = static_cast<CudaContext*>(ctx.get())->get_stream();
+    // Launches of one communicator share staging memory and flag epochs: they must
+    // run in issue order even when the caller switches streams.
+    if (m_has_last && m_last_stream != *stream) {
+        CUDA_CHECK(cudaEventRecord(m_last_event, m_last_stream));
+        CUDA_CHECK(cudaStreamWaitEvent(*stream, m_last_event, 0));
+    }
+    m_stats.calls++;
+    return MEGRAY_OK;
+}
+
+void NvlCommunicator::after_launch(cudaStream_t stream) {
+    m_stats.kernels++;
+    m_last_stream = stream;
+    m_has_last = true;
+}
+
+CommonArgs NvlCommunicator::common_args() {
+    CommonArgs c;
+    memset(&c, 0, sizeof(c));
+    for (uint32_t q = 0; q < m_nranks; ++q)
+        c.peers.heap[q] = m_heap.base(q);
+    c.nranks = static_cast<int>(m_nranks);
+    c.rank = static_cast<int>(m_rank);
+    c.epoch = m_epoch;
+    m_epoch += 2;  // a launch uses at most two barriers
+    c.timeout_ns = m_timeout_ns;
+    c.status = m_status_dev;
+    c.flag_off = kFlagOff;
+    return c;
+}
+
+uint32_t NvlCommunicator::reserve_epochs(uint32_t count) {
+    const uint32_t e = m_epoch;
+    m_epoch += count;
+    return e;
+}
+
+size_t NvlCommunicator::workspace_off() {
+    const size_t off = kWorkspaceOff + static_cast<size_t>(m_parity) * m_ws_bytes;
+    m_parity ^= 1;
+    return off;
+}
+
+int NvlCommunicator::pick_ctas(size_t bytes) const {
+    // enough CTAs to keep the links busy, few enough that flag traffic stays small
+    size_t want = (bytes + (128u << 10) - 1) / (128u << 10);
+    if (want < 1)
+        want = 1;
+    return static_cast<int>(std::min<size_t>(want, static_cast<size_t>(m_max_ctas)));
+}
+
+// ------------------------------------------------------------------ reduce family
+
+Status NvlCommunicator::reduce_impl(ReduceKind kind, const void* in, void* out, size_t len,
+                                    DType in_dtype, DType out_dtype, float scale, ReduceOp op,
+                                    uint32_t root, cudaStream_t stream) {
+    const size_t ein = get_dtype_size(in_dtype), eout = get_dtype_size(out_dtype);
+    const uint32_t n = m_nranks;
+    m_stats.bytes += len * ein;
+    if (len == 0)
+        return MEGRAY_OK;
+    const bool wants_out = kind != ReduceKind::Reduce || m_rank == root;
+    if (in == nullptr || (wants_out && out == nullptr))
+        return MEGRAY_INVALID_ARGUMENT;
+
+    // Largest slice (elements) whose n staging slots plus reduced slice fit one workspace.
+    const size_t se_max = round_down((m_ws_bytes - 16 * (n + 1)) / (n * ein + eout), 16);
+    if (se_max == 0)
+        return MEGRAY_INVALID_ARGUMENT;
+
+    ReduceArgs a;
+    memset(&a, 0, sizeof(a));
+    a.scale = scale;
+    a.in_dtype = in_dtype;
+    a.out_dtype = out_dtype;
+    a.op = op;
+    a.do_gather = wants_out ? 1 : 0;
+
+    const char* inb = static_cast<const char*>(in);
+    char* outb = static_cast<char*>(out);
+
+    if (kind == ReduceKind::ReduceScatter) {
+        // `len` is the per-rank result length; slice j of the input starts at j*len
+        for (size_t off = 0; off < len; off += se_max) {
+            const size_t se = std::min(se_max, len - off);
+            a.c = common_args();
+            const size_t ws = workspace_off();
+            a.in = inb + off * ein;
+            a.out = outb + off * eout;
+            a.slice_elems = se;
+            a.len = se * n;
+            a.in_pitch_elems = len;
+            a.stage_off = ws;
+            a.red_off = ws + n * round_up(se * ein, 16);
+            a.one_shot = 0;
+            a.out_is_slice = 1;
+            MEGRAY_CHECK(check_cuda(mgk::coll::launch_reduce(a, pick_ctas(se * ein * n), 512, stream)));
+            after_launch(stream);
+            m_stats.algo_twoshot++;
+        }
+        return MEGRAY_OK;
+    }
+
+    // all_reduce / reduce: small messages in one shot, larger ones in two
+    const size_t bytes = len * ein;
+    const bool fits_oneshot = n * round_up(bytes, 16) + round_up(len * eout, 16) <= m_ws_bytes;
+    if (kind == ReduceKind::AllReduce && bytes <= m_oneshot_bytes && fits_oneshot) {
+        a.c = common_args();
+        const size_t ws = workspace_off();
+        a.in = in;
+        a.out = out;
+        a.len = len;
+        a.slice_elems = len;
+        a.in_pitch_elems = len;
+        a.stage_off = ws;
+        a.red_off = ws + n * round_up(bytes, 16);
+        a.one_shot = 1;
+        MEGRAY_CHECK(check_cuda(mgk::coll::launch_reduce(a, pick_ctas(bytes * n), 512, stream)));
+        after_launch(stream);
+        m_stats.algo_oneshot++;
+        return MEGRAY_OK;
+    }
+    const size_t piece = se_max * n;
+    for (size_t off = 0; off < len; off += piece) {
+        const size_t this_len = std::min(piece, len - off);
+        const size_t se = round_up((this_len + n - 1) / n, 16);
+        a.c = common_args();
+        const size_t ws = workspace_off();
+        a.in = inb + off * ein;
+        a.out = wants_out ? outb + off * eout : nullptr;
+        a.len = this_len;
+        a.slice_elems = se;
+        a.in_pitch_elems = se;
+        a.stage_off = ws;
+        a.red_off = ws + n * round_up(se * ein, 16);
+        a.one_shot = 0;
+        a.out_is_slice = 0;
+        MEGRAY_CHECK(check_cuda(mgk::coll::launch_reduce(a, pick_ctas(this_len * ein), 512, stream)));
+        after_launch(stream);
+        m_stats.algo_twoshot++;
+    }
+    return MEGRAY_OK;
+}
+
+Status NvlCommunicator::all_reduce(const void* sendbuff, void* recvbuff, size_t len, DType dtype,
+                                   ReduceOp op, std::shared_ptr<Context> ctx) {
+    if (dtype == MEGRAY_CHAR || dtype >= MEGRAY_DTYPE_COUNT || op >= MEGRAY_REDUCEOP_COUNT)
+        return MEGRAY_INVALID_ARGUMENT;
+    cudaStream_t stream;
+    MEGRAY_CHECK(begin(ctx, &stream));
+    TraceScope trace("all_reduce", len * get_dtype_size(dtype), m_rank);
+    return reduce_impl(ReduceKind::AllReduce, sendbuff, recvbuff, len, dtype, dtype, 1.0f, op, 0,
+                       stream);
+}
+
+Status NvlCommunicator::all_reduce_scaled(const void* sendbuff, void* recvbuff, size_t len,
+                                          DType in_dtype, DType out_dtype, float scale,
+                                          ReduceOp op, std::shared_ptr<Context> ctx) {
+    if (!is_float(in_dtype) || !is_float(out_dtype) || op >= MEGRAY_REDUCEOP_COUNT)
+        return MEGRAY_INVALID_ARGUMENT;
+    if ((in_dtype == MEGRAY_FLOAT64) != (out_dtype == MEGRAY_FLOAT64))
+        return MEGRAY_INVALID_ARGUMENT;
+    cudaStream_t stream;
+    MEGRAY_CHECK(begin(ctx, &stream));
+    TraceScope trace("all_reduce_scaled", len * get_dtype_size(in_dtype), m_rank);
+    return reduce_impl(ReduceKind::AllReduce, sendbuff, recvbuff, len, in_dtype, out_dtype, scale,
+                       op, 0, stream);
+}
+
+Status NvlCommunicator::reduce_scatter(const void* sendbuff, void* recvbuff, size_t recvlen,
+                                       DType dtype, ReduceOp op, std::shared_ptr<Context> ctx) {
+    if (dtype == MEGRAY_CHAR || dtype >= MEGRAY_DTYPE_COUNT || op >= MEGRAY_REDUCEOP_COUNT)
+        return MEGRAY_INVALID_ARGUMENT;
+    cudaStream_t stream;
+    MEGRAY_CHECK(begin(ctx, &stream));
+    TraceScope trace("reduce_scatter", recvlen * get_dtype_size(dtype), m_rank);
+    return reduce_impl(ReduceKind::ReduceScatter, sendbuff, recvbuff, recvlen, dtype, dtype, 1.0f,
+                       op, 0, stream);
+}
+
+Status NvlCommunicator::reduce(const void* sendbuff, void* recvbuff, size_t len, DType dtype,
+                               ReduceOp op, uint32_t root, std::shared_ptr<Context> ctx) {
+    if (dtype == MEGRAY_CHAR || dtype >= MEGRAY_DTYPE_COUNT || op >= MEGRAY_REDUCEOP_COUNT ||
+        root >= m_nranks)
+        return MEGRAY_INVALID_ARGUMENT;
+    cudaStream_t stream;
+    MEGRAY_CHECK(begin(ctx, &stream));
+    TraceScope trace("reduce", len * get_dtype_size(dtype), m_rank);
+    return reduce_impl(ReduceKind::Reduce, sendbuff, recvbuff, len, dtype, dtype, 1.0f, op, root,
+                       stream);
+}
+
+// ------------------------------------------------------------------ exchange family
+
+Status NvlCommunicator::all_gather(const void* sendbuff, void* recvbuff, size_t sendlen,
+                                   DType dtype, std::shared_ptr<Context> ctx) {
+    cudaStream_t stream;
+    MEGRAY_CHECK(begin(ctx, &stream));
+    const size_t bytes = sendlen * get_dtype_size(dtype);
+    TraceScope trace("all_gather", bytes, m_rank);
+    m_stats.bytes += bytes;
+    if (bytes == 0)
+        return MEGRAY_OK;
+    const size_t cap = round_down(m_ws_bytes - 16, 16);
+    for (size_t off = 0; off < bytes; off += cap) {
+        const size_t piece = std::min(cap, bytes - off);
+        ExchangeArgs a;
+        memset(&a, 0, sizeof(a));
+        a.c = common_args();
+        a.pub_off = workspace_off();
+        a.in = static_cast<const char*>(sendbuff) + off;
+        a.out = static_cast<char*>(recvbuff) + off;
+        a.chunk_bytes = piece;
+        a.in_pitch = bytes;
+        a.out_pitch = bytes;
+        a.publish_chunks = 1;
+        a.push_root = -1;
+        a.pull_mask = (1u << m_nranks) - 1;
+        for (uint32_t q = 0; q < m_nranks; ++q) {
+            a.src_chunk[q] = 0;
+            a.dst_chunk[q] = static_cast<int>(q);
+            a.pull_bytes[q] = piece;
+        }
+        MEGRAY_CHECK(check_cuda(mgk::coll::launch_exchange(a, pick_ctas(piece * m_nranks), 512, stream)));
+        after_launch(stream);
+        m_stats.algo_copy++;
+    }
+    return MEGRAY_OK;
+}
+
+Status NvlCommunicator::all_to_all(const void* sendbuff, void* recvbuff, size_t len, DType dtype,
+                                   std::shared_ptr<Context> ctx) {
+    cudaStream_t stream;
+    MEGRAY_CHECK(begin(ctx, &stream));
+    const size_t bytes = len * get_dtype_size(dtype);
+    TraceScope trace("all_to_all", bytes, m_rank);
+    m_stats.bytes += bytes;
+    if (bytes == 0)
+        return MEGRAY_OK;
+    const size_t cap = round_down(m_ws_bytes / m_nranks - 16, 16);
+    for (size_t off = 0; off < bytes; off += cap) {
+        const size_t piece = std::min(cap, bytes - off);
+        ExchangeArgs a;
+        memset(&a, 0, sizeof(a));
+        a.c = common_args();
+        a.pub_off = workspace_off();
+        a.in = static_cast<const char*>(sendbuff) + off;
+        a.out = static_cast<char*>(recvbuff) + off;
+        a.chunk_bytes = piece;
+        a.in_pitch = bytes;
+        a.out_pitch = bytes;
+        a.publish_chunks = static_cast<int>(m_nranks);
+        a.push_root = -1;
+        a.pull_mask = (1u << m_nranks) - 1;
+        for (uint32_t q = 0; q < m_nranks; ++q) {
+            a.src_chunk[q] = static_cast<int>(m_rank);
+            a.dst_chunk[q] = static_cast<int>(q);
+            a.pull_bytes[q] = piece;
+        }
+        MEGRAY_CHECK(check_cuda(mgk::coll::launch_exchange(a, pick_ctas(piece * m_nranks), 512, stream)));
+        after_launch(stream);
+        m_stats.algo_copy++;
+    }
+    return MEGRAY_OK;
+}
+
+Status NvlCommunicator::broadcast(const void* sendbuff, void* recvbuff, size_t len, DType dtype,
+                                  uint32_t root, std::shared_ptr<Context> ctx) {
+    if (root >= m_nranks)
+        return MEGRAY_INVALID_ARGUMENT;
+    cudaStream_t stream;
+    MEGRAY_CHECK(begin(ctx, &stream));
+    const size_t bytes = len * get_dtype_size(dtype);
+    TraceScope trace("broadcast", bytes, m_rank);
+    m_stats.bytes += bytes;
+    if (bytes == 0)
+        return MEGRAY_OK;
+    const uint32_t n = m_nranks;
+    const bool two_step = bytes > m_oneshot_bytes && n > 2;
+    // one step: everyone loads the whole piece from the root's pub buffer
+    // two steps: the root pushes slice j to peer j, then everyone loads all slices
+    const size_t cap = two_step ? round_down(m_ws_bytes - 16, 16) * n : round_down(m_ws_bytes - 16, 16);
+    for (size_t off = 0; off < bytes; off += cap) {
+        const size_t piece = std::min(cap, bytes - off);
+        ExchangeArgs a;
+        memset(&a, 0, sizeof(a));
+        a.c = common_args();
+        a.pub_off = workspace_off();
+        a.in = m_rank == root ? static_cast<const char*>(sendbuff) + off : nullptr;
+        a.out = static_cast<char*>(recvbuff) + off;
+        if (two_step) {
+            const size_t sb = round_up((piece + n - 1) / n, 16);
+            a.chunk_bytes = sb;
+            a.in_pitch = sb;
+            a.out_pitch = sb;
+            a.push_root = static_cast<int>(root);
+            a.pull_mask = (1u << n) - 1;
+            for (uint32_t q = 0; q < n; ++q) {
+                const size_t s0 = static_cast<size_t>(q) * sb;
+                a.src_chunk[q] = 0;
+                a.dst_chunk[q] = static_cast<int>(q);
+                a.pull_bytes[q] = s0 >= piece ? 0 : std::min(sb, piece - s0);
+            }
+        } else {
+            a.chunk_bytes = piece;
+            a.in_pitch = piece;
+            a.out_pitch = piece;
+            a.publish_chunks = m_rank == root ? 1 : 0;
+            a.push_root = -1;
+            a.pull_mask = 1u << root;
+            a.pull_bytes[root] = piece;
+        }
+        MEGRAY_CHECK(check_cuda(mgk::coll::launch_exchange(a, pick_ctas(piece), 512, stream)));
+        after_launch(stream);
+        m_stats.algo_copy++;
+    }
+    return MEGRAY_OK;
+}
+
+Status NvlCommunicator::gather(const void* sendbuff, void* recvbuff, size_t sendlen, DType dtype,
+                               uint32_t root, std::shared_ptr<Context> ctx) {
+    if (root >= m_nranks)
+        return MEGRAY_INVALID_ARGUMENT;
+    cudaStream_t stream;
+    MEGRAY_CHECK(begin(ctx, &stream));
+    const size_t bytes = sendlen * get_dtype_size(dtype);
+    TraceScope trace("gather", bytes, m_rank);
+    m_stats.bytes += bytes;
+    if (bytes == 0)
+        return MEGRAY_OK;
+    if (m_rank == root && recvbuff == nullptr)
+        return MEGRAY_INVALID_ARGUMENT;
+    const size_t cap = round_down(m_ws_bytes - 16, 16);
+    for (size_t off = 0; off < bytes; off += cap) {
+        const size_t piece = std::min(cap, bytes - off);
+        ExchangeArgs a;
+        memset(&a, 0, sizeof(a));
+        a.c = common_args();
+        a.pub_off = workspace_off();
+        a.in = static_cast<const char*>(sendbuff) + off;
+        a.out = m_rank == root ? static_cast<char*>(recvbuff) + off : nullptr;
+        a.chunk_bytes = piece;
+        a.in_pitch = bytes;
+        a.out_pitch = bytes;
+        a.publish_chunks = 1;
+        a.push_root = -1;
+        a.pull_mask = m_rank == root ? (1u << m_nranks) - 1 : 0;
+        for (uint32_t q = 0; q < m_nranks; ++q) {
+            a.src_chunk[q] = 0;
+            a.dst_chunk[q] = static_cast<int>(q);
+            a.pull_bytes[q] = piece;
+        }
+        MEGRAY_CHECK(check_cuda(mgk::coll::launch_exchange(a, pick_ctas(piece * m_nranks), 512, stream)));
+        after_launch(stream);
+        m_stats.algo_copy++;
+    }
+    return MEGRAY_OK;
+}
+
+Status NvlCommunicator::scatter(const void* sendbuff, void* recvbuff, size_t recvlen, DType dtype,
+                                uint32_t root, std::shared_ptr<Context> ctx) {
+    if (root >= m_nranks)
+        return MEGRAY_INVALID_ARGUMENT;
+    cudaStream_t stream;
+    MEGRAY_CHECK(begin(ctx, &stream));
+    const size_t bytes = recvlen * get_dtype_size(dtype);
+    TraceScope trace("scatter", bytes, m_rank);
+    m_stats.bytes += bytes;
+    if (bytes == 0)
+        return MEGRAY_OK;
+    if (m_rank == root && sendbuff == nullptr)
+        return MEGRAY_INVALID_ARGUMENT;
+    const size_t cap = round_down(m_ws_bytes / m_nranks - 16, 16);
+    for (size_t off = 0; off < bytes; off += cap) {
+        const size_t piece = std::min(cap, bytes - off);
+        ExchangeArgs a;
+        memset(&a, 0, sizeof(a));
+        a.c = common_args();
+        a.pub_off = workspace_off();
+        a.in = m_rank == root ? static_cast<const char*>(sendbuff) + off : nullptr;
+        a.out = static_cast<char*>(recvbuff) + off;
+        a.chunk_bytes = piece;
+        a.in_pitch = bytes;
+        a.out_pitch = bytes;
+        a.publish_chunks = m_rank == root ? static_cast<int>(m_nranks) : 0;
+        a.push_root = -1;
+        a.pull_mask = 1u << root;
+        a.src_chunk[root] = static_cast<int>(m_rank);
+        a.dst_chunk[root] = 0;
+        a.pull_bytes[root] = piece;
+        MEGRAY_CHECK(check_cuda(mgk::coll::launch_exchange(a, pick_ctas(piece * m_nranks), 512, stream)));
+        after_launch(stream);
+        m_stats.algo_copy++;
+    }
+    return MEGRAY_OK;
+}
+
+Status NvlCommunicator::stream_barrier(std::shared_ptr<Context> ctx) {
+    cudaStream_t stream;
+    MEGRAY_CHECK(begin(ctx, &stream));
+    ExchangeArgs a;
+    memset(&a, 0, sizeof(a));
+    a.c = common_args();
+    a.pub_off = workspace_off();
+    a.push_root = -1;
+    MEGRAY_CHECK(check_cuda(mgk::coll::launch_exchange(a, 1, 32, stream)));
+    after_launch(stream);
+    return MEGRAY_OK;
+}
+
+// ------------------------------------------------------------------ point to point (NCCL)
+
+Status NvlCommunicator::_send(const void* sendbuff, size_t size, uint32_t rank,
+                              std::shared_ptr<Context> ctx) {
+#ifdef MEGRAY_WITH_NCCL
+    if (!m_p2p)
+        return MEGRAY_NOT_IMPLEMENTED;
+    m_stats.calls++;
+    m_stats.bytes += size;
+    return m_p2p->send(sendbuff, size, MEGRAY_CHAR, rank, ctx);
+#else
+    return MEGRAY_NOT_IMPLEMENTED;
+#endif
+}
+
+Status NvlCommunicator::_recv(void* recvbuf, size_t size, uint32_t rank,
+                              std::shared_ptr<Context> ctx) {
+#ifdef MEGRAY_WITH_NCCL
+    if (!m_p2p)
+        return MEGRAY_NOT_IMPLEMENTED;
+    m_stats.calls++;
+    m_stats.bytes += size;
+    return m_p2p->recv(recvbuf, size, MEGRAY_CHAR, rank, ctx);
+#else
+    return MEGRAY_NOT_IMPLEMENTED;
+#endif
+}
+
+Status NvlCommunicator::group_start() {
+#ifdef MEGRAY_WITH_NCCL
+    // native collectives are single launches and ignore grouping; p2p is batched by NCCL
+    return m_p2p ? m_p2p->group_start() : MEGRAY_OK;
+#else
+    return MEGRAY_OK;
+#endif
+}
+
+Status NvlCommunicator::group_end() {
+#ifdef MEGRAY_WITH_NCCL
+    return m_p2p ? m_p2p->group_end() : MEGRAY_OK;
+#else
+    return MEGRAY_OK;
+#endif
+}
+
+// ------------------------------------------------------------------ state
+
+void NvlCommunicator::abort() {
+    Communicator::abort();
+#ifdef MEGRAY_WITH_NCCL
+    if (m_p2p)
+        m_p2p->abort();
+#endif
+}
+
+Status NvlCommunicator::status() {
+    if (m_aborted.load())
+        return MEGRAY_ABORTED;
+    if (m_status_host != nullptr && *m_status_host != 0 && m_error == MEGRAY_OK) {
+        m_error = static_cast<Status>(*m_status_host);
+        m_stats.timeouts++;
+    }
+    return m_error;
+}
+
+CommStats NvlCommunicator::stats() { return m_stats; }
+
+// ------------------------------------------------------------------ symmetric allocator
+
+void* NvlCommunicator::sym_alloc(size_t bytes, size_t* offset_out) {
+    if (!m_ready || bytes == 0)
+        return nullptr;
+    const size_t at = round_up(m_user_top, 1024);
+    if (at + bytes > m_heap.bytes()) {
+        MEGRAY_ERROR("symmetric heap exhausted: %zu bytes wanted, %zu free (MEGRAY_HEAP_MB=%lld)", bytes,
+                     m_heap.bytes() - at, static_cast<long long>(global_options().heap_mb));
+        return nullptr;
+    }
+    m_allocs.push_back(m_user_top);
+    m_user_top = at + bytes;
+    if (offset_out != nullptr)
+        *offset_out = at;
+    return m_heap.local() + at;
+}
+
+Status NvlCommunicator::sym_free(void* ptr) {
+    if (!in_heap(ptr, 1))
+        return MEGRAY_INVALID_ARGUMENT;
+    const size_t off = static_cast<size_t>(static_cast<char*>(ptr) - m_heap.local());
+    while (!m_allocs.empty()) {
+        const size_t prev_top = m_allocs.back();
+        m_allocs.pop_back();
+        const size_t at = round_up(prev_top, 1024);
+        m_user_top = prev_top;
+        if (at == off)
+            return MEGRAY_OK;
+        if (at < off)
+            break;
+    }
+    return MEGRAY_INVALID_ARGUMENT;
+}
+
+void* NvlCommunicator::peer_ptr(void* ptr, uint32_t peer) {
+    if (peer >= m_nranks || !in_heap(ptr, 1))
+        return nullptr;
+    return m_heap.base(peer) + (static_cast<char*>(ptr) - m_heap.local());
+}
+
+bool NvlCommunicator::in_heap(const void* ptr, size_t bytes) {
+    if (!m_ready || ptr == nullptr)
+        return false;
+    const char* p = static_cast<const char*>(ptr);
+    return p >= m_heap.local() && p + bytes <= m_heap.local() + m_heap.bytes();
+}
+
+}  // namespace MegRay

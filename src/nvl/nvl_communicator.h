@@ -1,0 +1,121 @@
+// Native NVLink 5 / NVSwitch backend (Backend MEGRAY_NVL).
+//
+// Every collective is one kernel launch per rank on the caller's stream: the
+// kernels in kernels/collectives.cu move data through a symmetric heap that all
+// ranks map, synchronise through flag words in that heap, and fuse the
+// reduction, scale and cast into the transfer.  User buffers need no
+// registration: inputs are pushed into peers' staging slots (or published in
+// the local heap) and results are loaded from peers' heaps straight into the
+// output.  send/recv and group_start/group_end go to NCCL point-to-point.
+//
+// Replaces, behind the same interface, what the reference does through
+// ncclAllReduce & co. (src/nccl/communicator.cpp:90-228).
+#pragma once
+#include <cuda_runtime_api.h>
+
+#include <memory>
+#include <vector>
+
+#include "kernels/collectives.cuh"
+#include "megray/communicator.h"
+#include "megray/fused.h"
+#include "megray/server.h"
+#include "nvl/sym_heap.h"
+
+namespace MegRay {
+
+class NcclCommunicator;
+
+class NvlCommunicator : public Communicator, public NvlInterface {
+public:
+    NvlCommunicator(uint32_t nranks, uint32_t rank);
+    ~NvlCommunicator() override;
+
+    Status do_init() override;
+    Status do_init(BcastCallback cb) override;
+
+    Status scatter(const void* sendbuff, void* recvbuff, size_t recvlen, DType dtype, uint32_t root,
+                   std::shared_ptr<Context> ctx) override;
+    Status gather(const void* sendbuff, void* recvbuff, size_t sendlen, DType dtype, uint32_t root,
+                  std::shared_ptr<Context> ctx) override;
+    Status all_to_all(const void* sendbuff, void* recvbuff, size_t len, DType dtype,
+                      std::shared_ptr<Context> ctx) override;
+    Status all_gather(const void* sendbuff, void* recvbuff, size_t sendlen, DType dtype,
+                      std::shared_ptr<Context> ctx) override;
+    Status all_reduce(const void* sendbuff, void* recvbuff, size_t len, DType dtype, ReduceOp op,
+                      std::shared_ptr<Context> ctx) override;
+    Status reduce_scatter(const void* sendbuff, void* recvbuff, size_t recvlen, DType dtype,
+                          ReduceOp op, std::shared_ptr<Context> ctx) override;
+    Status broadcast(const void* sendbuff, void* recvbuff, size_t len, DType dtype, uint32_t root,
+                     std::shared_ptr<Context> ctx) override;
+    Status reduce(const void* sendbuff, void* recvbuff, size_t len, DType dtype, ReduceOp op,
+                  uint32_t root, std::shared_ptr<Context> ctx) override;
+    Status group_start() override;
+    Status group_end() override;
+
+    Backend backend() const override { return MEGRAY_NVL; }
+    void abort() override;
+    Status status() override;
+    CommStats stats() override;
+
+    // NvlInterface
+    void* sym_alloc(size_t bytes, size_t* offset_out) override;
+    Status sym_free(void* ptr) override;
+    void* peer_ptr(void* ptr, uint32_t peer) override;
+    bool in_heap(const void* ptr, size_t bytes) override;
+    size_t heap_bytes() override { return m_heap.bytes(); }
+    void* heap_base(uint32_t peer) override { return m_heap.base(peer); }
+    Status all_reduce_scaled(const void* sendbuff, void* recvbuff, size_t len, DType in_dtype,
+                             DType out_dtype, float scale, ReduceOp op,
+                             std::shared_ptr<Context> ctx) override;
+    Status stream_barrier(std::shared_ptr<Context> ctx) override;
+    uint32_t reserve_epochs(uint32_t count) override;
+    size_t fused_flag_offset() override { return kFusedFlagOff; }
+    int* status_word() override { return m_status_dev; }
+    uint64_t device_timeout_ns() override { return m_timeout_ns; }
+    void set_device_timeout_ms(int64_t ms) override { m_timeout_ns = static_cast<uint64_t>(ms) * 1000000ull; }
+
+    // heap layout (byte offsets, identical on every rank)
+    static constexpr size_t kFlagOff = 0;               // collectives: kMaxCtas x kMaxRanks words
+    static constexpr size_t kFusedFlagOff = 16 * 1024;  // fused kernels: 48 KiB of flags/counters
+    static constexpr size_t kWorkspaceOff = 64 * 1024;  // two staging workspaces follow
+
+protected:
+    Status _send(const void* sendbuff, size_t size, uint32_t rank,
+                 std::shared_ptr<Context> ctx) override;
+    Status _recv(void* recvbuf, size_t size, uint32_t rank, std::shared_ptr<Context> ctx) override;
+
+private:
+    enum class ReduceKind { AllReduce, Reduce, ReduceScatter };
+    Status begin(const std::shared_ptr<Context>& ctx, cudaStream_t* stream);
+    Status reduce_impl(ReduceKind kind, const void* in, void* out, size_t len, DType in_dtype,
+                       DType out_dtype, float scale, ReduceOp op, uint32_t root,
+                       cudaStream_t stream);
+    mgk::coll::CommonArgs common_args();
+    size_t workspace_off();  // offset of the workspace this launch uses; flips the parity
+    void after_launch(cudaStream_t stream);
+    int pick_ctas(size_t bytes) const;
+    Status check_cuda(cudaError_t e);
+
+    SymmetricHeap m_heap;
+    std::unique_ptr<Server> m_own_server;  // init(BcastCallback): private rendezvous
+    std::unique_ptr<NcclCommunicator> m_p2p;
+    bool m_ready = false;
+    size_t m_ws_bytes = 0;   // bytes of one staging workspace
+    size_t m_user_off = 0;   // first byte of the symmetric allocator's area
+    size_t m_user_top = 0;   // bump pointer
+    std::vector<size_t> m_allocs;
+    uint32_t m_epoch = 0;
+    int m_parity = 0;
+    uint64_t m_timeout_ns;
+    int m_max_ctas;
+    size_t m_oneshot_bytes;
+    int* m_status_host = nullptr;  // pinned, mapped
+    int* m_status_dev = nullptr;
+    cudaStream_t m_last_stream = nullptr;
+    cudaEvent_t m_last_event = nullptr;
+    bool m_has_last = false;
+    Status m_error = MEGRAY_OK;
+};
+
+}  // namespace MegRay
