@@ -27,6 +27,7 @@ typedef struct {
     int aux_off;
     int m_rot;
     int sm_limit;
+    int variant;     /* 0 automatic, 1 force the single-CTA tile */
     const uint32_t* a_ready;
     int rows_per_flag;
     uint32_t a_ready_target;
@@ -113,6 +114,17 @@ size_t megray_dtype_size(int dtype);   /* 0 for an unknown dtype */
 void megray_set_log_level(int level);
 void megray_trace_enable(const char* path);
 size_t megray_trace_dump(void);
+
+/* ---- training-harness kernels ---------------------------------------------------------------- */
+int megray_sgd_bf16(void* w, const void* g, float* momentum, uint64_t n, float lr, float mu,
+                    float weight_decay, void* stream);
+int megray_mse_bf16(const void* y, const void* target, void* dy, float* loss_out, uint64_t n,
+                    float scale, void* stream);
+
+int megray_add_rmsnorm_bf16(const void* x, const void* y, void* x_out, void* n_out, float* inv_rms,
+                            int rows, int cols, float eps, void* stream);
+int megray_rmsnorm_bwd_bf16(const void* dn, const void* n, const float* inv_rms, const void* dres,
+                            void* dx, int rows, int cols, void* stream);
 
 /* Kernels launched by this library since it was loaded (all modules). */
 uint64_t megray_launch_count(void);

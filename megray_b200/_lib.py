@@ -35,6 +35,7 @@ class GemmArgs(C.Structure):
         ("aux_off", C.c_int),
         ("m_rot", C.c_int),
         ("sm_limit", C.c_int),
+        ("variant", C.c_int),
         ("a_ready", C.c_void_p),
         ("rows_per_flag", C.c_int),
         ("a_ready_target", C.c_uint32),
@@ -109,6 +110,10 @@ def _declare(lib) -> None:
     d("megray_cpu_reduce_n", i32, P(vp), i32, vp, sz, i32, i32)
     d("megray_cpu_reduce_scale_cast", i32, P(vp), i32, i32, vp, i32, sz, i32, C.c_double)
     d("megray_reduce_n", i32, P(vp), i32, vp, sz, i32, i32, i32, C.c_float, vp)
+    d("megray_sgd_bf16", i32, vp, vp, vp, u64, C.c_float, C.c_float, C.c_float, vp)
+    d("megray_mse_bf16", i32, vp, vp, vp, vp, u64, C.c_float, vp)
+    d("megray_add_rmsnorm_bf16", i32, vp, vp, vp, vp, vp, i32, i32, C.c_float, vp)
+    d("megray_rmsnorm_bwd_bf16", i32, vp, vp, vp, vp, vp, i32, i32, vp)
     d("megray_dtype_size", sz, i32)
     d("megray_set_log_level", None, i32)
     d("megray_trace_enable", None, C.c_char_p)

@@ -1,0 +1,2 @@
+"""Model families used by the benchmarks and harnesses."""
+from .tp_mlp import TPMLPConfig, TPMLPStack  # noqa: F401

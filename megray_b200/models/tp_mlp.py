@@ -1,0 +1,184 @@
+"""Tensor-parallel (+ sequence-parallel) SwiGLU MLP stack with explicit forward/backward.
+
+Per layer, with T tokens, model width d, FFN width f and n ranks (f_l = f / n):
+
+    forward    x_n = rmsnorm(x)               on the token shard (fused with the residual add)
+               xg  = all_gather(x_n)          [T/n, d] -> [T, d]          (n > 1)
+               G|U = xg @ [Wg; Wu]^T          fused epilogue also writes H = silu(G) * U
+               yp  = H @ Wd^T                 [T, d] partial sums
+               y   = reduce_scatter(yp)       [T, d] -> [T/n, d]          (n > 1);  x <- x + y
+    backward   dyg = all_gather(dy)
+               dG|dU = (dyg @ Wd) with the SwiGLU derivative fused into the epilogue
+               dWd = dyg^T @ H
+               dxp = dG|dU @ [Wg; Wu];  dx = reduce_scatter(dxp)
+               dWgu = (dG|dU)^T @ xg
+
+Every matrix product runs on the library's tcgen05 kernel (``ops.gemm``); weight and
+activation gradients read their operands in transposed storage through TMA, so no
+transposition pass exists.  Collectives are the native NVL backend's; with
+``fused=True`` the all_gather is overlapped with the GEMM that consumes it and the
+reduce_scatter with the GEMM that produces it (``parallel.tensor_parallel``).
+
+The reference library has no model code: this is the tensor-parallel harness that the
+library's collectives are built to serve.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from ..ops import EPI_DSWIGLU, EPI_SWIGLU, add_rmsnorm, gemm, mse_loss_grad, rmsnorm_bwd, sgd_step
+
+
+@dataclass
+class TPMLPConfig:
+    d_model: int = 8192
+    ffn: int = 28672
+    layers: int = 4
+    tokens: int = 8 * 4096      # global tokens per step
+    init_std: float = 0.02
+    lr: float = 1e-4
+    seed: int = 0
+
+
+class _Layer:
+    def __init__(self, cfg: TPMLPConfig, layer: int, rank: int, n: int, device):
+        d, f = cfg.d_model, cfg.ffn
+        fl = f // n
+        g = torch.Generator(device=device).manual_seed(cfg.seed * 1000 + layer)
+        # global weights from one seed, then this rank's shard (the same numbers for every n)
+        w_gate = torch.empty(f, d, device=device, dtype=torch.bfloat16).normal_(0, cfg.init_std, generator=g)
+        w_up = torch.empty(f, d, device=device, dtype=torch.bfloat16).normal_(0, cfg.init_std, generator=g)
+        w_down = torch.empty(d, f, device=device, dtype=torch.bfloat16).normal_(0, cfg.init_std, generator=g)
+        sl = slice(rank * fl, (rank + 1) * fl)
+        self.w_gu = torch.cat([w_gate[sl], w_up[sl]], 0).contiguous()   # [2 f_l, d]
+        self.w_down = w_down[:, sl].contiguous()                          # [d, f_l]
+        del w_gate, w_up, w_down
+        self.g_gu = torch.empty_like(self.w_gu)
+        self.g_down = torch.empty_like(self.w_down)
+        self.fl = fl
+
+
+class TPMLPStack:
+    """``layers`` pre-norm residual SwiGLU MLP blocks, x <- x + MLP(rmsnorm(x)), sharded over the
+    ranks of ``comm`` (None = 1 GPU).  The normalisation (no learnable gain) and the residual
+    add are one fused memory-bound kernel between the tensor-parallel regions; they act on the
+    token shard, before the all_gather and after the reduce_scatter."""
+
+    def __init__(self, cfg: TPMLPConfig, comm=None, device=None, fused: bool = True):
+        self.cfg = cfg
+        self.comm = comm
+        self.n = comm.nranks if comm is not None else 1
+        self.rank = comm.rank if comm is not None else 0
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        if cfg.ffn % (self.n * 128) or cfg.tokens % (self.n * 128) or cfg.d_model % 256:
+            raise ValueError("ffn and tokens must be multiples of 128 * nranks, d_model of 256")
+        self.layers: List[_Layer] = [_Layer(cfg, l, self.rank, self.n, self.device) for l in range(cfg.layers)]
+        T, d, fl, L = cfg.tokens, cfg.d_model, cfg.ffn // self.n, cfg.layers
+        self.Ts = T // self.n
+        bf = dict(dtype=torch.bfloat16, device=self.device)
+        self.tp = None
+        if self.n > 1:
+            from ..parallel.tensor_parallel import TensorParallelOps
+
+            self.tp = TensorParallelOps(comm, T, d, fused=fused)
+        # kept for backward, one set per layer
+        self.xg = [self._full(T, d) for _ in range(L)]           # normalised input, all tokens
+        self.inv_rms = [torch.empty(self.Ts, dtype=torch.float32, device=self.device) for _ in range(L)]
+        self.gu = [torch.empty(T, 2 * fl, **bf) for _ in range(L)]
+        self.h = [torch.empty(T, fl, **bf) for _ in range(L)]
+        # residual stream and scratch shared by all layers
+        self.xs = [torch.empty(self.Ts, d, **bf) for _ in range(2)]
+        self.y = torch.empty(self.Ts, d, **bf)
+        self.dgu = torch.empty(T, 2 * fl, **bf)
+        self.partial = self._full(T, d) if self.n > 1 else None
+        self.dyg = self._full(T, d) if self.n > 1 else None
+        self.dn = torch.empty(self.Ts, d, **bf)
+        self.dres = [torch.empty(self.Ts, d, **bf) for _ in range(2)]
+        self.x_dev = torch.empty(self.Ts, d, **bf)
+
+    def _full(self, T, d):
+        if self.tp is not None:
+            return self.tp.full_buffer()
+        return torch.empty(T, d, dtype=torch.bfloat16, device=self.device)
+
+    def _shard(self, full: torch.Tensor) -> torch.Tensor:
+        """This rank's rows of an all-token buffer."""
+        return full[self.rank * self.Ts:(self.rank + 1) * self.Ts]
+
+    # ------------------------------------------------------------------ forward / backward
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """x: this rank's [T/n, d] token shard (bf16).  Returns the [T/n, d] output shard."""
+        L = len(self.layers)
+        add_rmsnorm(x, None, None, self._shard(self.xg[0]), self.inv_rms[0])
+        for l, layer in enumerate(self.layers):
+            fl = layer.fl
+            if self.tp is None:
+                gemm(self.xg[l], layer.w_gu, self.gu[l], epilogue=EPI_SWIGLU, out2=self.h[l], n=fl)
+                gemm(self.h[l], layer.w_down, self.y)
+            else:
+                self.tp.ag_gemm_swiglu(self.xg[l], layer.w_gu, self.gu[l], self.h[l], fl)
+                self.tp.gemm_rs(self.h[l], layer.w_down, self.partial, self.y)
+            x_next = self.xs[l & 1]
+            if l + 1 < L:
+                add_rmsnorm(x, self.y, x_next, self._shard(self.xg[l + 1]), self.inv_rms[l + 1])
+            else:
+                add_rmsnorm(x, self.y, x_next, None, None)
+            x = x_next
+        return x
+
+    def backward(self, dy: torch.Tensor) -> torch.Tensor:
+        """dy: gradient of the loss w.r.t. the output shard.  Fills the weight gradients and
+        returns the gradient w.r.t. the input shard."""
+        dres = dy
+        for l in reversed(range(len(self.layers))):
+            layer = self.layers[l]
+            fl = layer.fl
+            if self.tp is None:
+                gemm(dres, layer.w_down, self.dgu, b_mn=True, epilogue=EPI_DSWIGLU, aux=self.gu[l], n=fl)
+                gemm(dres, self.h[l], layer.g_down, a_mn=True, b_mn=True)
+                gemm(self.dgu, layer.w_gu, self.dn, b_mn=True)
+                gemm(self.dgu, self.xg[l], layer.g_gu, a_mn=True, b_mn=True)
+            else:
+                self.tp.ag_gemm_dswiglu(dres, self.dyg, layer.w_down, self.gu[l], self.dgu, fl)
+                gemm(self.dyg, self.h[l], layer.g_down, a_mn=True, b_mn=True)
+                self.tp.gemm_rs(self.dgu, layer.w_gu, self.partial, self.dn, b_mn=True)
+                gemm(self.dgu, self.xg[l], layer.g_gu, a_mn=True, b_mn=True)
+            out = self.dres[l & 1]
+            rmsnorm_bwd(self.dn, self._shard(self.xg[l]), self.inv_rms[l], dres, out)
+            dres = out
+        return dres
+
+    def optimizer_step(self) -> None:
+        for layer in self.layers:
+            sgd_step(layer.w_gu, layer.g_gu, self.cfg.lr)
+            sgd_step(layer.w_down, layer.g_down, self.cfg.lr)
+
+    # ------------------------------------------------------------------ public training step
+    def train_step_device(self, x: torch.Tensor) -> torch.Tensor:
+        """One optimisation step on a device-resident token shard; returns the loss (1-element
+        fp32 device tensor: this rank's share of the mean squared output)."""
+        y = self.forward(x)
+        loss, dy = mse_loss_grad(y, None, 1.0 / (self.cfg.tokens * self.cfg.d_model))
+        self.backward(dy)
+        self.optimizer_step()
+        return loss
+
+    def train_step(self, x_host: torch.Tensor) -> float:
+        """The call a user makes: ``x_host`` is this rank's token shard in pinned host memory.
+        Copies it to the GPU, runs forward, loss, backward and the SGD update, and returns
+        the loss as a Python float (a device-to-host read)."""
+        self.x_dev.copy_(x_host, non_blocking=True)
+        return float(self.train_step_device(self.x_dev).item())
+
+    def parameters(self):
+        for layer in self.layers:
+            yield layer.w_gu
+            yield layer.w_down
+
+    def flops_per_step(self) -> float:
+        """Matrix-multiply FLOPs of one step over all ranks (forward + backward)."""
+        c = self.cfg
+        return 3 * 6.0 * c.tokens * c.d_model * c.ffn * c.layers

@@ -1,0 +1,103 @@
+"""bf16 GEMM on the library's tcgen05 kernel (src/kernels/gemm_tcgen05.cu).
+
+``gemm(a, b)`` computes ``D[M, N] = A[M, K] @ B[N, K]^T`` with fp32 accumulation.  Each
+operand can instead be given in its transposed storage ("MN-major"): ``a_mn=True`` means
+``a`` is stored ``[K, M]``, ``b_mn=True`` means ``b`` is stored ``[K, N]``; the kernel reads
+either through TMA without any transposition pass.  Epilogues:
+
+* ``EPI_STORE``   D = acc
+* ``EPI_ACCUM``   D += acc
+* ``EPI_SWIGLU``  ``b`` = [W_gate; W_up] stacked ([2F, K]); writes G|U into ``out`` ([M, 2F]) and
+                  silu(G) * U into ``out2`` ([M, F])
+* ``EPI_DSWIGLU`` acc = dH ([M, F]); reads saved G|U from ``aux`` and writes dG|dU into ``out``
+
+There is no GEMM in the reference library; this one exists for the tensor-parallel MLP and
+MoE entry points.  A missing native library or a launch failure raises: nothing here falls
+back to another implementation.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import _lib
+
+EPI_STORE, EPI_SWIGLU, EPI_DSWIGLU, EPI_ACCUM, EPI_PUSH = 0, 1, 2, 3, 4
+
+_err_flags = {}
+
+
+def gemm_error_flag(device=None) -> torch.Tensor:
+    """Per-device int32 word the kernels set when one of their bounded waits ran out."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = dev.index
+    if key not in _err_flags:
+        _err_flags[key] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return _err_flags[key]
+
+
+def _check2d(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.bfloat16 or t.dim() != 2 or not t.is_cuda:
+        raise ValueError(f"{name}: expected a 2-D CUDA bf16 tensor")
+    if t.stride(1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+        raise ValueError(f"{name}: rows must be contiguous, 16-byte aligned, leading dimension % 8 == 0")
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, *, a_mn: bool = False,
+         b_mn: bool = False, epilogue: int = EPI_STORE, out2: torch.Tensor = None,
+         aux: torch.Tensor = None, n: int = None, sm_limit: int = 0, m_rot: int = 0,
+         a_ready: torch.Tensor = None, rows_per_flag: int = 0, a_ready_target: int = 0,
+         m_block_group: torch.Tensor = None, group_rows_b: int = 0, k_begin: torch.Tensor = None,
+         k_end: torch.Tensor = None, groups: int = 0, peer_out: torch.Tensor = None,
+         rows_per_peer: int = 0, wait_limit_ms: int = 0, variant: int = 0) -> torch.Tensor:
+    """See the module docstring.  ``n`` overrides the output width (needed for SWIGLU, where
+    the logical N is F while ``b`` has 2F rows, and for grouped problems)."""
+    _check2d(a, "a")
+    _check2d(b, "b")
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    Nb, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    grouped = m_block_group is not None or k_begin is not None
+    if not grouped and Kb != K:
+        raise ValueError(f"inner dimensions differ: {K} vs {Kb}")
+    if epilogue == EPI_SWIGLU:
+        N = Nb // 2 if n is None else n
+        aux_off = N
+    else:
+        N = Nb if n is None else n
+        aux_off = N if epilogue == EPI_DSWIGLU else 0
+    out_cols = 2 * N if epilogue in (EPI_SWIGLU, EPI_DSWIGLU) else N
+    out_rows = M * groups if k_begin is not None else M
+    if out is None:
+        out = torch.empty(out_rows, out_cols, dtype=torch.bfloat16, device=a.device)
+    _check2d(out, "out")
+    args = _lib.GemmArgs()
+    args.A, args.B, args.D = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.M, args.N, args.K = M, N, K
+    args.lda, args.ldb, args.ldd = a.stride(0), b.stride(0), out.stride(0)
+    args.a_mn, args.b_mn, args.epilogue, args.aux_off = int(a_mn), int(b_mn), epilogue, aux_off
+    args.m_rot, args.sm_limit, args.variant = m_rot, sm_limit, variant
+    if epilogue == EPI_SWIGLU:
+        if out2 is None:
+            out2 = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+        _check2d(out2, "out2")
+        args.D2, args.ldd2 = out2.data_ptr(), out2.stride(0)
+    if epilogue == EPI_DSWIGLU:
+        if aux is None:
+            raise ValueError("EPI_DSWIGLU needs aux = saved [G | U]")
+        _check2d(aux, "aux")
+        args.aux, args.ldaux = aux.data_ptr(), aux.stride(0)
+    if a_ready is not None:
+        args.a_ready, args.rows_per_flag, args.a_ready_target = a_ready.data_ptr(), rows_per_flag, a_ready_target
+    if m_block_group is not None:
+        args.m_block_group, args.group_rows_b, args.groups = m_block_group.data_ptr(), group_rows_b, groups
+    if k_begin is not None:
+        args.k_begin, args.k_end, args.groups = k_begin.data_ptr(), k_end.data_ptr(), groups
+    if peer_out is not None:
+        args.peer_out, args.rows_per_peer = peer_out.data_ptr(), rows_per_peer
+    args.error_flag = gemm_error_flag(a.device).data_ptr()
+    args.wait_limit_ns = wait_limit_ms * 1_000_000
+    rc = _lib.load().megray_gemm_bf16(C.byref(args), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f"megray_gemm_bf16 failed (code {rc}) for M={M} N={N} K={K}")
+    return (out, out2) if epilogue == EPI_SWIGLU else out

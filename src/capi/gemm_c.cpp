@@ -1,4 +1,5 @@
 // C entry points for the GEMM family (see include/megray/c_api.h).
+#include "kernels/elementwise.cuh"
 #include "kernels/gemm_tcgen05.cuh"
 #include "kernels/launch_count.h"
 #include "megray/c_api.h"
@@ -26,6 +27,7 @@ extern "C" int megray_gemm_bf16(const megray_gemm_args* a, void* stream) {
     g.aux_off = a->aux_off;
     g.m_rot = a->m_rot;
     g.sm_limit = a->sm_limit;
+    g.variant = a->variant;
     g.a_ready = a->a_ready;
     g.rows_per_flag = a->rows_per_flag;
     g.a_ready_target = a->a_ready_target;
@@ -43,3 +45,31 @@ extern "C" int megray_gemm_bf16(const megray_gemm_args* a, void* stream) {
 }
 
 extern "C" uint64_t megray_launch_count(void) { return mgk::launch_count(); }
+
+extern "C" int megray_sgd_bf16(void* w, const void* g, float* momentum, uint64_t n, float lr, float mu,
+                               float weight_decay, void* stream) {
+    cudaError_t e = mgk::ew::launch_sgd_bf16(w, g, momentum, n, lr, mu, weight_decay,
+                                             static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+extern "C" int megray_mse_bf16(const void* y, const void* target, void* dy, float* loss_out, uint64_t n,
+                               float scale, void* stream) {
+    cudaError_t e = mgk::ew::launch_mse_bf16(y, target, dy, loss_out, n, scale,
+                                             static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+extern "C" int megray_add_rmsnorm_bf16(const void* x, const void* y, void* x_out, void* n_out, float* inv_rms,
+                                       int rows, int cols, float eps, void* stream) {
+    cudaError_t e = mgk::ew::launch_add_rmsnorm_bf16(x, y, x_out, n_out, inv_rms, rows, cols, eps,
+                                                     static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+extern "C" int megray_rmsnorm_bwd_bf16(const void* dn, const void* n, const float* inv_rms, const void* dres,
+                                       void* dx, int rows, int cols, void* stream) {
+    cudaError_t e = mgk::ew::launch_rmsnorm_bwd_bf16(dn, n, inv_rms, dres, dx, rows, cols,
+                                                     static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}

@@ -1,14 +1,22 @@
 // Persistent warp-specialised bf16 GEMM for sm_100a on tcgen05 tensor cores.
 //
 //   warp 0      : TMA producer   (cp.async.bulk.tensor 2D tiles -> 128B-swizzled smem ring)
-//   warp 1      : UMMA issuer    (tcgen05.mma cta_group::1, 128x256x16, accumulators in TMEM)
+//   warp 1      : UMMA issuer    (tcgen05.mma, accumulators in TMEM)
 //   warps 2..5  : epilogue       (tcgen05.ld TMEM -> registers -> fused epilogue -> global)
 //
-// Tile 128 x 256 x 64 per stage, 4-stage ring (48 KB per stage), two TMEM
-// accumulators (2 x 256 columns) so the epilogue of tile i overlaps the main
-// loop of tile i+1.  Every wait is bounded: a wait that runs out sets the
-// kernel's error word, all roles leave their loops, TMEM is freed and the
-// kernel returns normally.
+// Two variants of one kernel template:
+//   single : one CTA per tile, tile 128 x 256 x 64, tcgen05.mma.cta_group::1 (M = 128),
+//            4-stage ring of 48 KB.  Used for grouped (per-expert) row blocks.
+//   pair   : a cluster of two CTAs per 256 x 256 tile, tcgen05.mma.cta_group::2 (M = 256)
+//            issued by the leader CTA; each CTA stages its own 128 rows of A and its own
+//            128 rows of B (so B is read from shared memory once per pair), 7-stage ring
+//            of 32 KB per CTA.  Each CTA issues its own TMA loads (no multicast); their
+//            byte counts complete on the leader's barrier, and the leader's commits free
+//            the stage in both CTAs.
+// Both keep two TMEM accumulators (2 x 256 columns) so the epilogue of tile i overlaps
+// the main loop of tile i+1.  Every wait is bounded: a wait that runs out sets the
+// kernel's error word, all roles leave their loops, TMEM is freed and the kernel
+// returns normally.
 //
 // The reference library (MegRay) contains no GEMM; this kernel exists for the
 // fused tensor-parallel and expert-parallel entry points.
@@ -33,18 +41,24 @@ using namespace mgk::ptx;
 
 namespace {
 
-constexpr int BM = 128;
-constexpr int BN = 256;
+constexpr int BM = 128;  // rows of A per CTA
+constexpr int BN = 256;  // accumulator columns
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
-constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
-constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 constexpr int MN_CHUNK_BYTES = 64 * BK * 2;  // one 64(mn) x 64(k) box of an MN-major operand
+constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
+
+template <bool PAIR>
+struct Cfg {
+    static constexpr int TILE_M = PAIR ? 256 : 128;
+    static constexpr int B_ROWS = PAIR ? 128 : 256;  // rows of B staged by one CTA
+    static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr int STAGES = PAIR ? 7 : 4;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+};
 
 struct KParams {
     int M, N, K;
@@ -83,6 +97,7 @@ struct Tile {
     bool skip;     // nothing to do (padding block of a grouped problem)
 };
 
+template <int TILE_M>
 __device__ __forceinline__ Tile decode_tile(const KParams& p, int t) {
     Tile tl;
     tl.skip = false;
@@ -105,7 +120,7 @@ __device__ __forceinline__ Tile decode_tile(const KParams& p, int t) {
     mb += p.m_rot;
     if (mb >= p.m_blocks)
         mb -= p.m_blocks;
-    tl.m0 = mb * BM;
+    tl.m0 = mb * TILE_M;
     tl.n0 = nb * p.n_tile_stride;
     tl.d_row0 = tl.m0;
     if (p.k_begin != nullptr) {
@@ -172,22 +187,151 @@ __device__ __forceinline__ void load_row32(const __nv_bfloat16* src, float (&v)[
     }
 }
 
-template <bool A_MN, bool B_MN, int EPI>
+
+// ---------------------------------------------------------------- cluster helpers
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `addr` (a shared::cta address) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+// TMA load issued by one CTA of a pair; its bytes complete on `bar` (a shared::cluster
+// address, here the leader CTA's barrier).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* map, uint32_t bar, int c0,
+                                                 int c1) {
+    asm volatile(
+            "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+            " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+            "l"(map), "r"(bar), "r"(c0), "r"(c1)
+            : "memory");
+}
+__device__ __forceinline__ void umma_commit_cg2(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                         bar)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+                 : "memory");
+}
+
+// ---------------------------------------------------------------- epilogue of one tile
+// `t_addr`: TMEM address of this warp's lane quarter of the accumulator; `row_in_tile`: the
+// row (0..TILE_M) of the tile this thread owns.
+template <int EPI>
+__device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, uint32_t t_addr,
+                                              int row_in_tile, bool zero_tile) {
+    const int m = tl.m0 + row_in_tile;
+    const bool row_ok = m < p.M;
+    const long drow = tl.d_row0 + row_in_tile;
+    if (EPI == EPI_SWIGLU) {
+        // columns [0,128) = gate, [128,256) = up of output columns n0..n0+127
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            uint32_t rg[32], ru[32];
+            tmem_ld_32x32b_x32(t_addr + c * 32, rg);
+            tmem_ld_32x32b_x32(t_addr + 128 + c * 32, ru);
+            tmem_ld_wait();
+            const int col = tl.n0 + c * 32;
+            const int ok = p.N - col;
+            if (row_ok && ok > 0) {
+                float g[32], u[32], h[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    g[i] = __uint_as_float(rg[i]);
+                    u[i] = __uint_as_float(ru[i]);
+                    h[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+                }
+                store_row32(p.D + drow * p.ldd + col, g, ok);
+                store_row32(p.D + drow * p.ldd + p.aux_off + col, u, ok);
+                store_row32(p.D2 + drow * p.ldd2 + col, h, ok);
+            }
+        }
+        return;
+    }
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        if (!zero_tile) {
+            tmem_ld_32x32b_x32(t_addr + c * 32, r);
+            tmem_ld_wait();
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                r[i] = 0u;
+        }
+        const int col = tl.n0 + c * 32;
+        const int ok = p.N - col;
+        if (!row_ok || ok <= 0)
+            continue;
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            v[i] = __uint_as_float(r[i]);
+        if (EPI == EPI_STORE) {
+            store_row32(p.D + drow * p.ldd + col, v, ok);
+        } else if (EPI == EPI_ACCUM) {
+            float o[32];
+            load_row32(p.D + drow * p.ldd + col, o, ok);
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                v[i] += o[i];
+            store_row32(p.D + drow * p.ldd + col, v, ok);
+        } else if (EPI == EPI_DSWIGLU) {
+            float g[32], u[32];
+            load_row32(p.aux + drow * p.ldaux + col, g, ok);
+            load_row32(p.aux + drow * p.ldaux + p.aux_off + col, u, ok);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float sg = 1.f / (1.f + __expf(-g[i]));
+                const float dh = v[i];
+                const float silu = g[i] * sg;
+                u[i] = dh * u[i] * (sg + silu * (1.f - sg));  // dG
+                g[i] = dh * silu;                              // dU
+            }
+            store_row32(p.D + drow * p.ldd + col, u, ok);
+            store_row32(p.D + drow * p.ldd + p.aux_off + col, g, ok);
+        } else if (EPI == EPI_PUSH) {
+            // output rows are sharded over GPUs: a whole m-block has one owner
+            const int peer = static_cast<int>(drow / p.rows_per_peer);
+            const long prow = drow - static_cast<long>(peer) * p.rows_per_peer;
+            __nv_bfloat16* base = static_cast<__nv_bfloat16*>(p.peer_out[peer]);
+            store_row32(base + prow * p.ldd + col, v, ok);
+        }
+    }
+}
+
+template <bool PAIR, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
         gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
                          const __grid_constant__ CUtensorMap tma_b, const KParams p) {
+    using C = Cfg<PAIR>;
+    constexpr int STAGES = C::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::STAGE_BYTES);
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const int lane = threadIdx.x & 31;
+    // position inside the CTA pair (0 = leader, issues the MMAs); a single CTA is its own leader
+    const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
+    const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
     const uint32_t full0 = smem_u32(bars);
     const uint32_t empty0 = smem_u32(bars + STAGES);
@@ -204,36 +348,46 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull0 + 8 * a, 1);
-            mbar_init(tempty0 + 8 * a, 4);
+            // the leader's MMA thread waits for the epilogue warps of both CTAs
+            mbar_init(tempty0 + 8 * a, PAIR ? 8 : 4);
         }
         mbar_fence_init();
         fence_proxy_async_smem();
     }
     if (warp == 1) {
-        tmem_alloc_cg1(smem_u32(tmem_slot), TMEM_COLS);
-        tmem_relinquish_cg1();
+        if (PAIR) {
+            tmem_alloc_cg2(smem_u32(tmem_slot), TMEM_COLS);
+            tmem_relinquish_cg2();
+        } else {
+            tmem_alloc_cg1(smem_u32(tmem_slot), TMEM_COLS);
+            tmem_relinquish_cg1();
+        }
     }
     tc_fence_before();
-    __syncthreads();
+    if (PAIR)
+        cluster_sync_all();  // barriers of both CTAs exist before any remote arrive / TMA signal
+    else
+        __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
     WaitCtx wc{abort_flag, p.wait_limit_ns};
 
     if (warp == 0) {
-        // ------------------------------------------------------ TMA producer
+        // ------------------------------------------------------ TMA producer (every CTA)
         if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
             bool alive = true;
-            for (int t = blockIdx.x; t < p.num_tiles && alive; t += gridDim.x) {
-                Tile tl = decode_tile(p, t);
+            for (int t = worker; t < p.num_tiles && alive; t += workers) {
+                Tile tl = decode_tile<C::TILE_M>(p, t);
                 if (tl.skip || tl.k_blocks == 0)
                     continue;
+                const int m0 = tl.m0 + static_cast<int>(crank) * BM;  // this CTA's rows of A
                 if (p.a_ready != nullptr) {
                     // all_gather fusion: rows of this m-block arrive from another GPU;
                     // wait (bounded) for the shard's ready counter.
-                    const uint32_t* f = p.a_ready + tl.m0 / p.rows_per_flag;
+                    const uint32_t* f = p.a_ready + m0 / p.rows_per_flag;
                     uint32_t spins = 0;
                     uint64_t t0 = 0;
                     while (ld_acquire_gpu(f) < p.a_ready_target) {
@@ -257,27 +411,52 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         alive = false;
                         break;
                     }
-                    const uint32_t fb = full0 + 8 * s;
-                    mbar_expect_tx(fb, STAGE_BYTES);
                     const int k = tl.k0 + kb * BK;
                     const uint32_t sa = smem_u32(smem_a + s * A_STAGE_BYTES);
-                    const uint32_t sb = smem_u32(smem_b + s * B_STAGE_BYTES);
-                    if (!A_MN) {
-                        tma_load_2d(sa, &tma_a, fb, k, tl.m0);
-                    } else {
+                    const uint32_t sb = smem_u32(smem_b + s * C::B_STAGE_BYTES);
+                    if (!PAIR) {
+                        const uint32_t fb = full0 + 8 * s;
+                        mbar_expect_tx(fb, C::STAGE_BYTES);
+                        if (!A_MN) {
+                            tma_load_2d(sa, &tma_a, fb, k, m0);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < BM / 64; ++j)
-                            tma_load_2d(sa + j * MN_CHUNK_BYTES, &tma_a, fb, tl.m0 + 64 * j, k);
-                    }
-                    if (!B_MN) {
-                        tma_load_2d(sb, &tma_b, fb, k, tl.b_row + tl.n0);
-                        tma_load_2d(sb + B_STAGE_BYTES / 2, &tma_b, fb, k,
-                                    tl.b_row + tl.n0 + p.b_half_off);
-                    } else {
+                            for (int j = 0; j < BM / 64; ++j)
+                                tma_load_2d(sa + j * MN_CHUNK_BYTES, &tma_a, fb, m0 + 64 * j, k);
+                        }
+                        if (!B_MN) {
+                            tma_load_2d(sb, &tma_b, fb, k, tl.b_row + tl.n0);
+                            tma_load_2d(sb + C::B_STAGE_BYTES / 2, &tma_b, fb, k,
+                                        tl.b_row + tl.n0 + p.b_half_off);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j)
-                            tma_load_2d(sb + j * MN_CHUNK_BYTES, &tma_b, fb, tl.n0 + 64 * j,
-                                        tl.b_row + k);
+                            for (int j = 0; j < C::B_ROWS / 64; ++j)
+                                tma_load_2d(sb + j * MN_CHUNK_BYTES, &tma_b, fb, tl.n0 + 64 * j,
+                                            tl.b_row + k);
+                        }
+                    } else {
+                        // both CTAs' bytes complete on the leader's barrier
+                        const uint32_t fb = mapa_u32(full0 + 8 * s, 0);
+                        if (crank == 0)
+                            mbar_expect_tx(full0 + 8 * s, 2 * C::STAGE_BYTES);
+                        if (!A_MN) {
+                            tma_load_2d_pair(sa, &tma_a, fb, k, m0);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < BM / 64; ++j)
+                                tma_load_2d_pair(sa + j * MN_CHUNK_BYTES, &tma_a, fb, m0 + 64 * j, k);
+                        }
+                        // this CTA's half of the 256 columns of B
+                        if (!B_MN) {
+                            tma_load_2d_pair(sb, &tma_b, fb, k,
+                                             tl.b_row + tl.n0 + static_cast<int>(crank) * p.b_half_off);
+                        } else {
+                            const int n0 = tl.n0 + static_cast<int>(crank) * C::B_ROWS;
+#pragma unroll
+                            for (int j = 0; j < C::B_ROWS / 64; ++j)
+                                tma_load_2d_pair(sb + j * MN_CHUNK_BYTES, &tma_b, fb, n0 + 64 * j,
+                                                 tl.b_row + k);
+                        }
                     }
                     if (++s == STAGES) {
                         s = 0;
@@ -287,19 +466,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------ UMMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN, A_MN, B_MN);
+        // ------------------------------------------------------ UMMA issuer (leader CTA only)
+        if (lane == 0 && crank == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16_f32(C::TILE_M, BN, A_MN, B_MN);
             int s = 0;
             uint32_t ph = 0;
             int acc = 0;
             uint32_t acc_ph = 0;
             bool alive = true;
-            for (int t = blockIdx.x; t < p.num_tiles && alive; t += gridDim.x) {
-                Tile tl = decode_tile(p, t);
+            for (int t = worker; t < p.num_tiles && alive; t += workers) {
+                Tile tl = decode_tile<C::TILE_M>(p, t);
                 if (tl.skip || tl.k_blocks == 0)
                     continue;
-                if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1, wc))
+                if (!mbar_wait<PAIR>(tempty0 + 8 * acc, acc_ph ^ 1, wc))
                     break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
@@ -310,7 +489,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem_a + s * A_STAGE_BYTES);
-                    const uint32_t sb = smem_u32(smem_b + s * B_STAGE_BYTES);
+                    const uint32_t sb = smem_u32(smem_b + s * C::B_STAGE_BYTES);
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                         // K-major: 16 k = 32 bytes inside the 128 B row.
@@ -323,9 +502,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                 B_MN ? umma_smem_desc_sw128(sb + kk * (UMMA_K * 128), MN_CHUNK_BYTES,
                                                             1024)
                                      : umma_smem_desc_sw128(sb + kk * (UMMA_K * 2), 16, 1024);
-                        umma_f16_cg1(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        if (PAIR)
+                            umma_f16_cg2(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        else
+                            umma_f16_cg1(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
                     }
-                    umma_commit_cg1(empty0 + 8 * s);  // frees the smem stage when the MMAs retire
+                    // free the smem stage (in both CTAs of a pair) when these MMAs retire
+                    if (PAIR) {
+                        umma_commit_cg2(empty0 + 8 * s);
+                        umma_commit_cg2(mapa_u32(empty0 + 8 * s, 1));
+                    } else {
+                        umma_commit_cg1(empty0 + 8 * s);
+                    }
                     if (++s == STAGES) {
                         s = 0;
                         ph ^= 1;
@@ -333,26 +521,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 }
                 if (!alive)
                     break;
-                umma_commit_cg1(tfull0 + 8 * acc);  // accumulator complete
+                // accumulator complete: wake the epilogue warps (of both CTAs)
+                if (PAIR) {
+                    umma_commit_cg2(tfull0 + 8 * acc);
+                    umma_commit_cg2(mapa_u32(tfull0 + 8 * acc, 1));
+                } else {
+                    umma_commit_cg1(tfull0 + 8 * acc);
+                }
                 acc ^= 1;
                 if (acc == 0)
                     acc_ph ^= 1;
             }
         }
     } else {
-        // ------------------------------------------------------ epilogue (warps 2..5)
+        // ------------------------------------------------------ epilogue (warps 2..5, every CTA)
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         int acc = 0;
         uint32_t acc_ph = 0;
-        bool alive = true;
-        for (int t = blockIdx.x; t < p.num_tiles && alive; t += gridDim.x) {
-            Tile tl = decode_tile(p, t);
+        for (int t = worker; t < p.num_tiles; t += workers) {
+            Tile tl = decode_tile<C::TILE_M>(p, t);
             if (tl.skip)
                 continue;
-            const int row_in_tile = q * 32 + lane;
-            const int m = tl.m0 + row_in_tile;
-            const bool row_ok = m < p.M;
-            const long drow = tl.d_row0 + row_in_tile;
             const bool zero_tile = tl.k_blocks == 0;
             if (!zero_tile) {
                 // the whole warp must agree before the .sync.aligned TMEM loads
@@ -362,87 +551,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 tc_fence_after();
             }
             const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-
-            if (EPI == EPI_SWIGLU) {
-                // columns [0,128) = gate, [128,256) = up of output columns n0..n0+127
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t rg[32], ru[32];
-                    tmem_ld_32x32b_x32(t_addr + c * 32, rg);
-                    tmem_ld_32x32b_x32(t_addr + 128 + c * 32, ru);
-                    tmem_ld_wait();
-                    const int col = tl.n0 + c * 32;
-                    const int ok = p.N - col;
-                    if (row_ok && ok > 0) {
-                        float g[32], u[32], h[32];
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            g[i] = __uint_as_float(rg[i]);
-                            u[i] = __uint_as_float(ru[i]);
-                            h[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
-                        }
-                        store_row32(p.D + drow * p.ldd + col, g, ok);
-                        store_row32(p.D + drow * p.ldd + p.aux_off + col, u, ok);
-                        store_row32(p.D2 + drow * p.ldd2 + col, h, ok);
-                    }
-                }
-            } else {
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t r[32];
-                    if (!zero_tile) {
-                        tmem_ld_32x32b_x32(t_addr + c * 32, r);
-                        tmem_ld_wait();
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            r[i] = 0u;
-                    }
-                    const int col = tl.n0 + c * 32;
-                    const int ok = p.N - col;
-                    if (!row_ok || ok <= 0)
-                        continue;
-                    float v[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        v[i] = __uint_as_float(r[i]);
-                    if (EPI == EPI_STORE) {
-                        store_row32(p.D + drow * p.ldd + col, v, ok);
-                    } else if (EPI == EPI_ACCUM) {
-                        float o[32];
-                        load_row32(p.D + drow * p.ldd + col, o, ok);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            v[i] += o[i];
-                        store_row32(p.D + drow * p.ldd + col, v, ok);
-                    } else if (EPI == EPI_DSWIGLU) {
-                        float g[32], u[32];
-                        load_row32(p.aux + drow * p.ldaux + col, g, ok);
-                        load_row32(p.aux + drow * p.ldaux + p.aux_off + col, u, ok);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const float sg = 1.f / (1.f + __expf(-g[i]));
-                            const float dh = v[i];
-                            const float silu = g[i] * sg;
-                            u[i] = dh * u[i] * (sg + silu * (1.f - sg));  // dG
-                            g[i] = dh * silu;                              // dU
-                        }
-                        store_row32(p.D + drow * p.ldd + col, u, ok);
-                        store_row32(p.D + drow * p.ldd + p.aux_off + col, g, ok);
-                    } else if (EPI == EPI_PUSH) {
-                        // output rows are sharded over GPUs: a whole m-block has one owner
-                        const int peer = static_cast<int>(drow / p.rows_per_peer);
-                        const long prow = drow - static_cast<long>(peer) * p.rows_per_peer;
-                        __nv_bfloat16* base = static_cast<__nv_bfloat16*>(p.peer_out[peer]);
-                        store_row32(base + prow * p.ldd + col, v, ok);
-                    }
-                }
-            }
+            epilogue_tile<EPI>(p, tl, t_addr, static_cast<int>(crank) * BM + q * 32 + lane, zero_tile);
             if (!zero_tile) {
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0)
-                    mbar_arrive(tempty0 + 8 * acc);
+                if (lane == 0) {
+                    if (PAIR && crank != 0)
+                        mbar_arrive_remote(mapa_u32(tempty0 + 8 * acc, 0));
+                    else
+                        mbar_arrive(tempty0 + 8 * acc);
+                }
                 acc ^= 1;
                 if (acc == 0)
                     acc_ph ^= 1;
@@ -453,7 +571,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     // ---------------------------------------------------------- teardown
     __syncwarp();
     tc_fence_before();
-    __syncthreads();
+    if (PAIR)
+        cluster_sync_all();  // the peer may still read this CTA's smem / signal its barriers
+    else
+        __syncthreads();
     if (*abort_flag) {
         // A wait ran out.  TMA copies already issued complete on their own within
         // microseconds (their source is local memory); give them that time before
@@ -467,7 +588,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc_cg1(tmem_base, TMEM_COLS);
+        if (PAIR)
+            tmem_dealloc_cg2(tmem_base, TMEM_COLS);
+        else
+            tmem_dealloc_cg1(tmem_base, TMEM_COLS);
     }
 }
 
@@ -506,54 +630,106 @@ bool make_map(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer,
 
 std::atomic<uint64_t> g_launches{0};
 
-template <bool A_MN, bool B_MN, int EPI>
-cudaError_t launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const KParams& kp, int grid,
+// Launches one instantiation.  `workers` = CTAs (single) or CTA pairs (pair) wanted at most;
+// the pair variant is additionally capped by what the device can co-schedule as 2-CTA clusters.
+template <bool PAIR, bool A_MN, bool B_MN, int EPI>
+cudaError_t launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const KParams& kp, int workers,
                      cudaStream_t stream) {
-    auto kern = gemm_bf16_kernel<A_MN, B_MN, EPI>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    // one attribute set per device would be needed for multi-device processes; set every call
-    // when more than one device is visible to this process
+    auto kern = gemm_bf16_kernel<PAIR, A_MN, B_MN, EPI>;
+    constexpr int smem = Cfg<PAIR>::SMEM_BYTES;
     int dev = 0;
     cudaGetDevice(&dev);
     static std::mutex mu;
-    static std::map<int, bool> done;
+    static std::map<int, int> max_workers;  // per device: attribute set, cluster capacity known
+    int cap = 0;
     {
         std::lock_guard<std::mutex> lk(mu);
-        if (!done[dev]) {
-            attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            SMEM_BYTES);
-            if (attr_err != cudaSuccess)
-                return attr_err;
-            done[dev] = true;
+        auto it = max_workers.find(dev);
+        if (it == max_workers.end()) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (e != cudaSuccess)
+                return e;
+            int n = 0;
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+            if (PAIR) {
+                cudaLaunchConfig_t qc = {};
+                qc.gridDim = dim3(static_cast<unsigned>(n / 2 * 2));
+                qc.blockDim = dim3(NUM_THREADS);
+                qc.dynamicSmemBytes = smem;
+                cudaLaunchAttribute qa[1];
+                qa[0].id = cudaLaunchAttributeClusterDimension;
+                qa[0].val.clusterDim.x = 2;
+                qa[0].val.clusterDim.y = 1;
+                qa[0].val.clusterDim.z = 1;
+                qc.attrs = qa;
+                qc.numAttrs = 1;
+                int clusters = 0;
+                e = cudaOccupancyMaxActiveClusters(&clusters, kern, &qc);
+                if (e != cudaSuccess || clusters <= 0) {
+                    (void)cudaGetLastError();
+                    clusters = n / 2;
+                }
+                n = clusters;
+            }
+            max_workers[dev] = n;
+            cap = n;
+        } else {
+            cap = it->second;
         }
     }
-    (void)once;
-    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, kp);
+    if (workers > cap)
+        workers = cap;
+    if (workers < 1)
+        workers = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(PAIR ? 2 * workers : workers));
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = PAIR ? 2 : 1;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mb, kp);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
-template <bool A_MN, bool B_MN>
+template <bool PAIR, bool A_MN, bool B_MN>
 cudaError_t launch_e(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const KParams& kp,
-                     int grid, cudaStream_t stream) {
+                     int workers, cudaStream_t stream) {
     switch (epi) {
         case EPI_STORE:
-            return launch_t<A_MN, B_MN, EPI_STORE>(ma, mb, kp, grid, stream);
+            return launch_t<PAIR, A_MN, B_MN, EPI_STORE>(ma, mb, kp, workers, stream);
         case EPI_ACCUM:
-            return launch_t<A_MN, B_MN, EPI_ACCUM>(ma, mb, kp, grid, stream);
+            return launch_t<PAIR, A_MN, B_MN, EPI_ACCUM>(ma, mb, kp, workers, stream);
         case EPI_PUSH:
-            return launch_t<A_MN, B_MN, EPI_PUSH>(ma, mb, kp, grid, stream);
+            return launch_t<PAIR, A_MN, B_MN, EPI_PUSH>(ma, mb, kp, workers, stream);
         case EPI_DSWIGLU:
-            return launch_t<A_MN, B_MN, EPI_DSWIGLU>(ma, mb, kp, grid, stream);
+            return launch_t<PAIR, A_MN, B_MN, EPI_DSWIGLU>(ma, mb, kp, workers, stream);
         case EPI_SWIGLU:
             if (B_MN)
                 return cudaErrorInvalidValue;
-            return launch_t<A_MN, false, EPI_SWIGLU>(ma, mb, kp, grid, stream);
+            return launch_t<PAIR, A_MN, false, EPI_SWIGLU>(ma, mb, kp, workers, stream);
         default:
             return cudaErrorInvalidValue;
     }
+}
+
+template <bool PAIR>
+cudaError_t launch_l(bool a_mn, bool b_mn, int epi, const CUtensorMap& ma, const CUtensorMap& mb,
+                     const KParams& kp, int workers, cudaStream_t stream) {
+    if (!a_mn && !b_mn)
+        return launch_e<PAIR, false, false>(epi, ma, mb, kp, workers, stream);
+    if (!a_mn && b_mn)
+        return launch_e<PAIR, false, true>(epi, ma, mb, kp, workers, stream);
+    if (a_mn && !b_mn)
+        return launch_e<PAIR, true, false>(epi, ma, mb, kp, workers, stream);
+    return launch_e<PAIR, true, true>(epi, ma, mb, kp, workers, stream);
 }
 
 int sm_count() {
@@ -586,17 +762,27 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     const bool grouped_m = a.grouped.m_block_group != nullptr;
     const bool grouped_k = a.grouped.k_begin != nullptr;
 
+    // A CTA pair per 256 x 256 tile unless rows are grouped in 128-row blocks (per-expert
+    // forward/backward), which need the 128-row tile.
+    const bool pair = !grouped_m && a.variant != 1 && a.M > 128;
+    const int tile_m = pair ? 256 : BM;
+
     KParams kp{};
     kp.M = a.M;
     kp.N = a.N;
     kp.K = a.K;
-    kp.m_blocks = (a.M + BM - 1) / BM;
+    kp.m_blocks = (a.M + tile_m - 1) / tile_m;
     kp.n_tile_stride = (a.epilogue == EPI_SWIGLU) ? 128 : BN;
     kp.b_half_off = (a.epilogue == EPI_SWIGLU) ? a.aux_off : 128;
     kp.n_blocks = (a.N + kp.n_tile_stride - 1) / kp.n_tile_stride;
     kp.num_tiles = kp.m_blocks * kp.n_blocks * (grouped_k ? a.grouped.groups : 1);
-    kp.group_m = 8;
-    kp.m_rot = (a.m_rot % kp.m_blocks + kp.m_blocks) % kp.m_blocks;
+    // concurrently running tiles form a near-square patch (about 2048 rows x 2300 columns)
+    // so that each loaded A / B panel is shared by as many tiles as possible in L2
+    kp.group_m = pair ? 8 : 16;
+    {
+        const int rot_blocks = a.m_rot / tile_m;  // m_rot is given in rows
+        kp.m_rot = (rot_blocks % kp.m_blocks + kp.m_blocks) % kp.m_blocks;
+    }
     kp.D = static_cast<__nv_bfloat16*>(a.D);
     kp.ldd = a.ldd;
     kp.D2 = static_cast<__nv_bfloat16*>(a.D2);
@@ -620,11 +806,13 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
         return cudaErrorInvalidValue;
     if (a.epilogue == EPI_DSWIGLU && (a.aux == nullptr || (a.ldaux % 8)))
         return cudaErrorInvalidValue;
-    if (a.epilogue == EPI_PUSH && (a.peer_out == nullptr || (kp.rows_per_peer % BM)))
+    if (a.epilogue == EPI_PUSH && (a.peer_out == nullptr || (kp.rows_per_peer % tile_m)))
+        return cudaErrorInvalidValue;
+    if (a.a_ready != nullptr && (kp.rows_per_flag % BM))
         return cudaErrorInvalidValue;
 
     // Extents the tensor maps cover.  Grouped problems stack the groups along the
-    // outer dimension of B (and of A for grouped-K).
+    // outer dimension of B.
     const uint64_t groups = (grouped_m || grouped_k) ? static_cast<uint64_t>(a.grouped.groups) : 1;
     CUtensorMap ma, mb;
     bool ok;
@@ -652,19 +840,15 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     if (!ok)
         return cudaErrorInvalidValue;
 
-    int grid = sm_count();
-    if (a.sm_limit > 0 && a.sm_limit < grid)
-        grid = a.sm_limit;
-    if (grid > kp.num_tiles)
-        grid = kp.num_tiles;
-
-    if (!a.a_mn && !a.b_mn)
-        return launch_e<false, false>(a.epilogue, ma, mb, kp, grid, stream);
-    if (!a.a_mn && a.b_mn)
-        return launch_e<false, true>(a.epilogue, ma, mb, kp, grid, stream);
-    if (a.a_mn && !a.b_mn)
-        return launch_e<true, false>(a.epilogue, ma, mb, kp, grid, stream);
-    return launch_e<true, true>(a.epilogue, ma, mb, kp, grid, stream);
+    int workers = kp.num_tiles;
+    if (a.sm_limit > 0) {
+        const int lim = pair ? a.sm_limit / 2 : a.sm_limit;
+        if (lim < workers)
+            workers = lim > 0 ? lim : 1;
+    }
+    if (pair)
+        return launch_l<true>(a.a_mn, a.b_mn, a.epilogue, ma, mb, kp, workers, stream);
+    return launch_l<false>(a.a_mn, a.b_mn, a.epilogue, ma, mb, kp, workers, stream);
 }
 
 }  // namespace gemm

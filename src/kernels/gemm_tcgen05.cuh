@@ -43,8 +43,9 @@ struct GemmArgs {
     bool a_mn, b_mn;                  // operand is MN-major (stored [K, rows])
     int epilogue;
     int aux_off;  // column offset of the U half (EPI_SWIGLU / EPI_DSWIGLU), also B row offset
-    int m_rot;    // rotate the m-block order by this many blocks (all_gather fused GEMM)
+    int m_rot;    // start the row-block order at this row (all_gather fused GEMM: own shard first)
     int sm_limit; // 0 = all SMs; otherwise cap on the persistent grid
+    int variant;  // 0 = automatic, 1 = force the single-CTA 128 x 256 tile
     // all_gather fusion: wait until a_ready[(m_block*128)/rows_per_flag] >= a_ready_target
     const uint32_t* a_ready;
     int rows_per_flag;
