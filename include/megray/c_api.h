@@ -115,6 +115,17 @@ void megray_set_log_level(int level);
 void megray_trace_enable(const char* path);
 size_t megray_trace_dump(void);
 
+/* ---- tensor-parallel fused kernels (NVL communicators) ----------------------------------------
+ * all_gather -> GEMM: A of `args` is ignored and replaced by `gather_buf` ([M, K], local, in the
+ * symmetric heap); `shard_src` is this rank's [M/n, K] shard (in the heap, possibly its own rows of
+ * gather_buf).  GEMM -> reduce_scatter: D of `args` is ignored; `staging` holds n slots of
+ * [M/n, N]; `out` receives this rank's reduced [M/n, N] shard (+ residual).  `flags`: a 256-byte
+ * zero-initialised block in the heap, the same block for every call on the same buffers. */
+int megray_tp_ag_gemm(void* comm, const megray_gemm_args* args, void* gather_buf, const void* shard_src,
+                      void* flags, void* stream);
+int megray_tp_gemm_rs(void* comm, const megray_gemm_args* args, void* staging, void* out,
+                      const void* residual, void* flags, void* stream);
+
 /* ---- training-harness kernels ---------------------------------------------------------------- */
 int megray_sgd_bf16(void* w, const void* g, float* momentum, uint64_t n, float lr, float mu,
                     float weight_decay, void* stream);

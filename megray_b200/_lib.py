@@ -114,6 +114,8 @@ def _declare(lib) -> None:
     d("megray_mse_bf16", i32, vp, vp, vp, vp, u64, C.c_float, vp)
     d("megray_add_rmsnorm_bf16", i32, vp, vp, vp, vp, vp, i32, i32, C.c_float, vp)
     d("megray_rmsnorm_bwd_bf16", i32, vp, vp, vp, vp, vp, i32, i32, vp)
+    d("megray_tp_ag_gemm", i32, vp, P(GemmArgs), vp, vp, vp, vp)
+    d("megray_tp_gemm_rs", i32, vp, P(GemmArgs), vp, vp, vp, vp, vp)
     d("megray_dtype_size", sz, i32)
     d("megray_set_log_level", None, i32)
     d("megray_trace_enable", None, C.c_char_p)

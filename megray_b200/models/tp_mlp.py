@@ -93,10 +93,13 @@ class TPMLPStack:
         self.xs = [torch.empty(self.Ts, d, **bf) for _ in range(2)]
         self.y = torch.empty(self.Ts, d, **bf)
         self.dgu = torch.empty(T, 2 * fl, **bf)
-        self.partial = self._full(T, d) if self.n > 1 else None
+        self.partial = (torch.empty(T, d, **bf) if self.n > 1 and not self.tp.fused else None)
         self.dyg = self._full(T, d) if self.n > 1 else None
         self.dn = torch.empty(self.Ts, d, **bf)
-        self.dres = [torch.empty(self.Ts, d, **bf) for _ in range(2)]
+        # gradient of the residual stream: the source of the backward gather, so peers read it
+        self.dres = [self.tp.shard_buffer() if self.tp is not None else torch.empty(self.Ts, d, **bf)
+                     for _ in range(2)]
+        self.dy0 = self.tp.shard_buffer() if self.tp is not None else None
         self.x_dev = torch.empty(self.Ts, d, **bf)
 
     def _full(self, T, d):
@@ -132,6 +135,9 @@ class TPMLPStack:
     def backward(self, dy: torch.Tensor) -> torch.Tensor:
         """dy: gradient of the loss w.r.t. the output shard.  Fills the weight gradients and
         returns the gradient w.r.t. the input shard."""
+        if self.dy0 is not None and dy is not self.dy0:
+            self.dy0.copy_(dy)  # the backward gather reads its source from peers' heaps
+            dy = self.dy0
         dres = dy
         for l in reversed(range(len(self.layers))):
             layer = self.layers[l]
@@ -161,7 +167,7 @@ class TPMLPStack:
         """One optimisation step on a device-resident token shard; returns the loss (1-element
         fp32 device tensor: this rank's share of the mean squared output)."""
         y = self.forward(x)
-        loss, dy = mse_loss_grad(y, None, 1.0 / (self.cfg.tokens * self.cfg.d_model))
+        loss, dy = mse_loss_grad(y, None, 1.0 / (self.cfg.tokens * self.cfg.d_model), dy=self.dy0)
         self.backward(dy)
         self.optimizer_step()
         return loss

@@ -24,14 +24,17 @@ def sgd_step(w: torch.Tensor, g: torch.Tensor, lr: float, momentum_buf: torch.Te
         raise RuntimeError(f"megray_sgd_bf16 failed ({rc})")
 
 
-def mse_loss_grad(y: torch.Tensor, target: torch.Tensor = None, scale: float = None):
+def mse_loss_grad(y: torch.Tensor, target: torch.Tensor = None, scale: float = None,
+                  dy: torch.Tensor = None):
     """Returns (loss, dy): loss = scale * sum((y - target)^2) as a 1-element fp32 tensor and
-    dy = d loss / d y in bf16.  ``scale`` defaults to 1 / y.numel() (mean)."""
+    dy = d loss / d y in bf16 (written into ``dy`` when given).  ``scale`` defaults to
+    1 / y.numel() (mean)."""
     assert y.dtype == torch.bfloat16 and y.is_contiguous()
     if scale is None:
         scale = 1.0 / y.numel()
     loss = torch.zeros(1, dtype=torch.float32, device=y.device)
-    dy = torch.empty_like(y)
+    if dy is None:
+        dy = torch.empty_like(y)
     tp = target.data_ptr() if target is not None else None
     rc = _lib.load().megray_mse_bf16(y.data_ptr(), tp, dy.data_ptr(), loss.data_ptr(), y.numel(), scale,
                                      _stream())

@@ -44,15 +44,15 @@ def _check2d(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name}: rows must be contiguous, 16-byte aligned, leading dimension % 8 == 0")
 
 
-def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, *, a_mn: bool = False,
-         b_mn: bool = False, epilogue: int = EPI_STORE, out2: torch.Tensor = None,
-         aux: torch.Tensor = None, n: int = None, sm_limit: int = 0, m_rot: int = 0,
-         a_ready: torch.Tensor = None, rows_per_flag: int = 0, a_ready_target: int = 0,
-         m_block_group: torch.Tensor = None, group_rows_b: int = 0, k_begin: torch.Tensor = None,
-         k_end: torch.Tensor = None, groups: int = 0, peer_out: torch.Tensor = None,
-         rows_per_peer: int = 0, wait_limit_ms: int = 0, variant: int = 0) -> torch.Tensor:
-    """See the module docstring.  ``n`` overrides the output width (needed for SWIGLU, where
-    the logical N is F while ``b`` has 2F rows, and for grouped problems)."""
+def build_gemm_args(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, *, a_mn: bool = False,
+                    b_mn: bool = False, epilogue: int = EPI_STORE, out2: torch.Tensor = None,
+                    aux: torch.Tensor = None, n: int = None, sm_limit: int = 0, m_rot: int = 0,
+                    a_ready: torch.Tensor = None, rows_per_flag: int = 0, a_ready_target: int = 0,
+                    m_block_group: torch.Tensor = None, group_rows_b: int = 0, k_begin: torch.Tensor = None,
+                    k_end: torch.Tensor = None, groups: int = 0, peer_out: torch.Tensor = None,
+                    rows_per_peer: int = 0, wait_limit_ms: int = 0, variant: int = 0, alloc_out: bool = True):
+    """Validates the operands and fills the C argument block; returns (args, out, out2).  The
+    tensors referenced by ``args`` must stay alive until the launch has been enqueued."""
     _check2d(a, "a")
     _check2d(b, "b")
     M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
@@ -68,13 +68,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, *, a_mn: bo
         aux_off = N if epilogue == EPI_DSWIGLU else 0
     out_cols = 2 * N if epilogue in (EPI_SWIGLU, EPI_DSWIGLU) else N
     out_rows = M * groups if k_begin is not None else M
-    if out is None:
+    if out is None and alloc_out:
         out = torch.empty(out_rows, out_cols, dtype=torch.bfloat16, device=a.device)
-    _check2d(out, "out")
     args = _lib.GemmArgs()
-    args.A, args.B, args.D = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.A, args.B = a.data_ptr(), b.data_ptr()
+    if out is not None:
+        _check2d(out, "out")
+        args.D, args.ldd = out.data_ptr(), out.stride(0)
+    else:
+        args.ldd = out_cols
     args.M, args.N, args.K = M, N, K
-    args.lda, args.ldb, args.ldd = a.stride(0), b.stride(0), out.stride(0)
+    args.lda, args.ldb = a.stride(0), b.stride(0)
     args.a_mn, args.b_mn, args.epilogue, args.aux_off = int(a_mn), int(b_mn), epilogue, aux_off
     args.m_rot, args.sm_limit, args.variant = m_rot, sm_limit, variant
     if epilogue == EPI_SWIGLU:
@@ -97,7 +101,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, *, a_mn: bo
         args.peer_out, args.rows_per_peer = peer_out.data_ptr(), rows_per_peer
     args.error_flag = gemm_error_flag(a.device).data_ptr()
     args.wait_limit_ns = wait_limit_ms * 1_000_000
+    return args, out, out2
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, **kw) -> torch.Tensor:
+    """See the module docstring.  Keyword arguments as for :func:`build_gemm_args`; ``n`` overrides
+    the output width (needed for SWIGLU, where the logical N is F while ``b`` has 2F rows, and
+    for grouped problems)."""
+    args, out, out2 = build_gemm_args(a, b, out, **kw)
     rc = _lib.load().megray_gemm_bf16(C.byref(args), C.c_void_p(torch.cuda.current_stream().cuda_stream))
     if rc != 0:
-        raise RuntimeError(f"megray_gemm_bf16 failed (code {rc}) for M={M} N={N} K={K}")
-    return (out, out2) if epilogue == EPI_SWIGLU else out
+        raise RuntimeError(f"megray_gemm_bf16 failed (code {rc}) for M={args.M} N={args.N} K={args.K}")
+    return (out, out2) if args.epilogue == EPI_SWIGLU else out

@@ -2,11 +2,14 @@
 #include "kernels/elementwise.cuh"
 #include "kernels/gemm_tcgen05.cuh"
 #include "kernels/launch_count.h"
-#include "megray/c_api.h"
+#include <memory>
 
-extern "C" int megray_gemm_bf16(const megray_gemm_args* a, void* stream) {
-    if (a == nullptr)
-        return 6;
+#include "megray/c_api.h"
+#include "megray/communicator.h"
+#include "nvl/fused_tp.h"
+
+namespace {
+mgk::gemm::GemmArgs to_gemm_args(const megray_gemm_args* a) {
     mgk::gemm::GemmArgs g{};
     g.A = a->A;
     g.B = a->B;
@@ -40,8 +43,34 @@ extern "C" int megray_gemm_bf16(const megray_gemm_args* a, void* stream) {
     g.grouped.groups = a->groups;
     g.error_flag = a->error_flag;
     g.wait_limit_ns = a->wait_limit_ns;
-    cudaError_t e = mgk::gemm::launch_gemm_bf16(g, static_cast<cudaStream_t>(stream));
+    return g;
+}
+struct CommBoxView {  // layout of the handle made by megray_comm_new (capi/comm_c.cpp)
+    std::shared_ptr<MegRay::Communicator> comm;
+};
+}  // namespace
+
+extern "C" int megray_gemm_bf16(const megray_gemm_args* a, void* stream) {
+    if (a == nullptr)
+        return 6;
+    cudaError_t e = mgk::gemm::launch_gemm_bf16(to_gemm_args(a), static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+extern "C" int megray_tp_ag_gemm(void* comm, const megray_gemm_args* a, void* gather_buf, const void* shard_src,
+                                 void* flags, void* stream) {
+    if (comm == nullptr || a == nullptr)
+        return 6;
+    return MegRay::tp_ag_gemm(static_cast<CommBoxView*>(comm)->comm.get(), to_gemm_args(a), gather_buf, shard_src,
+                              flags, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int megray_tp_gemm_rs(void* comm, const megray_gemm_args* a, void* staging, void* out,
+                                 const void* residual, void* flags, void* stream) {
+    if (comm == nullptr || a == nullptr)
+        return 6;
+    return MegRay::tp_gemm_rs(static_cast<CommBoxView*>(comm)->comm.get(), to_gemm_args(a), staging, out, residual,
+                              flags, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" uint64_t megray_launch_count(void) { return mgk::launch_count(); }

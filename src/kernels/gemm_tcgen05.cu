@@ -46,7 +46,8 @@ constexpr int BN = 256;  // accumulator columns
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int TMEM_COLS = 512;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;   // producer, MMA, 4 epilogue warps, 4 communication warps
+constexpr int COMM_THREADS = 128;
 constexpr int MN_CHUNK_BYTES = 64 * BK * 2;  // one 64(mn) x 64(k) box of an MN-major operand
 constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
 
@@ -85,6 +86,7 @@ struct KParams {
     const int* k_end;
     int* error_flag;
     uint64_t wait_limit_ns;
+    FuseArgs fuse;
 };
 
 struct Tile {
@@ -304,9 +306,146 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
             // output rows are sharded over GPUs: a whole m-block has one owner
             const int peer = static_cast<int>(drow / p.rows_per_peer);
             const long prow = drow - static_cast<long>(peer) * p.rows_per_peer;
-            __nv_bfloat16* base = static_cast<__nv_bfloat16*>(p.peer_out[peer]);
+            __nv_bfloat16* base = static_cast<__nv_bfloat16*>(
+                    p.peer_out != nullptr ? p.peer_out[peer] : p.fuse.rs_peer_out[peer]);
             store_row32(base + prow * p.ldd + col, v, ok);
         }
+    }
+}
+
+
+// ---------------------------------------------------------------- fused all_gather (warps 6..9)
+// The communication warps of all CTAs together copy every peer's shard of A into the local
+// gather buffer, one shard after the other starting with rank+1, and publish a per-shard
+// epoch in `ready` when the last CTA has finished its part.  The TMA producer of the same
+// kernel waits for that epoch before it loads rows of the shard.
+__device__ __forceinline__ void comm_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ void copy16(char* dst, const char* src, uint64_t nbytes, int tid) {
+    // nbytes is a multiple of 16; both pointers are 16-byte aligned
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    const uint64_t n = nbytes / 16;
+    uint64_t i = tid;
+    for (; i + 3ull * COMM_THREADS < n; i += 4ull * COMM_THREADS) {
+        const uint4 a = __ldcg(s4 + i), b = __ldcg(s4 + i + COMM_THREADS),
+                    c = __ldcg(s4 + i + 2ull * COMM_THREADS), d = __ldcg(s4 + i + 3ull * COMM_THREADS);
+        d4[i] = a;
+        d4[i + COMM_THREADS] = b;
+        d4[i + 2ull * COMM_THREADS] = c;
+        d4[i + 3ull * COMM_THREADS] = d;
+    }
+    for (; i < n; i += COMM_THREADS)
+        d4[i] = __ldcg(s4 + i);
+}
+
+// Bounded poll of a flag word until it reaches `target` (wrap-safe).  Warp-uniform result.
+__device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t target, uint64_t limit_ns,
+                                              volatile int* abort_flag) {
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    while (static_cast<int32_t>(ld_acquire_sys(flag) - target) < 0) {
+        if ((++spins & 63) == 0) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0)
+                t0 = now;
+            if (*abort_flag || now - t0 > limit_ns) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void all_gather_warps(const FuseArgs& f, uint64_t limit_ns,
+                                                 volatile int* abort_flag, volatile int* comm_ok) {
+    const int tid = threadIdx.x - (NUM_THREADS - COMM_THREADS);
+    const int n = f.nranks, rank = f.rank;
+    // tell every peer that this rank's shard can be read (earlier kernels of this stream
+    // have completed, so the shard is final)
+    if (blockIdx.x == 0 && tid < n)
+        st_release_sys(f.ag_start_peer[tid] + rank, f.epoch);
+    const uint64_t shard_bytes = static_cast<uint64_t>(f.shard_rows) * f.row_bytes;
+    const uint64_t per_cta = ((shard_bytes + gridDim.x - 1) / gridDim.x + 15) / 16 * 16;
+    const uint64_t b = min(shard_bytes, per_cta * blockIdx.x), e = min(shard_bytes, b + per_cta);
+    for (int qq = 0; qq < n; ++qq) {
+        const int q = (rank + qq) % n;  // own shard first (local), then rank+1, ...
+        const char* src = static_cast<const char*>(f.ag_src[q]);
+        char* dst = static_cast<char*>(f.ag_dst) + static_cast<uint64_t>(q) * shard_bytes;
+        if (q != rank) {
+            // the peer's shard must be final before it is read
+            if (tid == 0)
+                *comm_ok = wait_flag_sys(f.ag_start_local + q, f.epoch, limit_ns, abort_flag) ? 1 : 0;
+            comm_bar();
+            const bool ok = *comm_ok != 0;
+            comm_bar();
+            if (!ok)
+                return;  // a wait ran out: the consumer's own bounded wait ends the kernel
+        }
+        if (src != nullptr && src != dst && e > b)
+            copy16(dst + b, src + b, e - b, tid);
+        comm_bar();
+        if (tid == 0) {
+            __threadfence();
+            const uint32_t done = atomicAdd(f.ag_count + q, 1u);
+            if (done == gridDim.x - 1) {  // the last CTA publishes the shard
+                f.ag_count[q] = 0;
+                __threadfence();
+                st_release_gpu(f.ag_ready + q, f.epoch);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------- fused reduce_scatter tail
+// After its last tile every CTA waits until all ranks have delivered all partial tiles of
+// this rank's shard (one counter per source rank, bumped once per 128-row tile), then sums
+// its slice of the n staging slots in rank order (fp32) into the output shard.
+__device__ __forceinline__ void reduce_scatter_tail(const FuseArgs& f, uint64_t limit_ns,
+                                                    volatile int* abort_flag, volatile int* comm_ok) {
+    __syncthreads();
+    const int n = f.nranks;
+    if (threadIdx.x == 0)
+        *comm_ok = 1;
+    __syncthreads();
+    if (static_cast<int>(threadIdx.x) < n) {
+        if (!wait_flag_sys(f.rs_count_local + threadIdx.x, f.rs_target, limit_ns, abort_flag))
+            *comm_ok = 0;
+    }
+    __syncthreads();
+    if (*comm_ok == 0)
+        return;
+    const uint64_t shard_elems = static_cast<uint64_t>(f.shard_rows) * (f.row_bytes / 2);
+    const uint64_t nvec = shard_elems / 8;
+    const uint64_t per_cta = (nvec + gridDim.x - 1) / gridDim.x;
+    const uint64_t b = min(nvec, per_cta * blockIdx.x), e = min(nvec, b + per_cta);
+    const uint4* slots = static_cast<const uint4*>(f.rs_stage_local);
+    const uint4* resid = static_cast<const uint4*>(f.rs_residual);
+    uint4* out = static_cast<uint4*>(f.rs_out);
+    for (uint64_t i = b + threadIdx.x; i < e; i += NUM_THREADS) {
+        float acc[8];
+        {
+            const uint4 v = __ldcg(slots + i);
+            acc[0] = bf16_lo(v.x); acc[1] = bf16_hi(v.x); acc[2] = bf16_lo(v.y); acc[3] = bf16_hi(v.y);
+            acc[4] = bf16_lo(v.z); acc[5] = bf16_hi(v.z); acc[6] = bf16_lo(v.w); acc[7] = bf16_hi(v.w);
+        }
+        for (int s = 1; s < n; ++s) {
+            const uint4 v = __ldcg(slots + static_cast<uint64_t>(s) * nvec + i);
+            acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+            acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+        }
+        if (resid != nullptr) {
+            const uint4 v = resid[i];
+            acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+            acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]);
+        o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]);
+        o.w = pack_bf16x2(acc[6], acc[7]);
+        out[i] = o;
     }
 }
 
@@ -325,6 +464,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* comm_ok = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const int lane = threadIdx.x & 31;
@@ -390,7 +530,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     const uint32_t* f = p.a_ready + m0 / p.rows_per_flag;
                     uint32_t spins = 0;
                     uint64_t t0 = 0;
-                    while (ld_acquire_gpu(f) < p.a_ready_target) {
+                    while (static_cast<int32_t>(ld_acquire_gpu(f) - p.a_ready_target) < 0) {
                         if ((++spins & 0x3f) == 0) {
                             uint64_t now = globaltimer_ns();
                             if (t0 == 0)
@@ -533,7 +673,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     acc_ph ^= 1;
             }
         }
-    } else {
+    } else if (warp < 6) {
         // ------------------------------------------------------ epilogue (warps 2..5, every CTA)
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         int acc = 0;
@@ -565,8 +705,25 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 if (acc == 0)
                     acc_ph ^= 1;
             }
+            if (EPI == EPI_PUSH && p.fuse.rs_count_peer[0] != nullptr) {
+                // this warp's 32 rows of the partial tile are in the owner's staging slot:
+                // make them visible system-wide, then count them (4 counts per 128-row tile)
+                __syncwarp();
+                if (lane == 0) {
+                    const int row0 = tl.m0 + static_cast<int>(crank) * BM;
+                    const int owner = row0 / p.rows_per_peer;
+                    __threadfence_system();
+                    red_release_sys_add(p.fuse.rs_count_peer[owner] + p.fuse.rank, 1u);
+                }
+            }
         }
+    } else {
+        // ------------------------------------------------------ communication warps (6..9)
+        if (p.fuse.ag_dst != nullptr)
+            all_gather_warps(p.fuse, p.wait_limit_ns, abort_flag, comm_ok);
     }
+    if (EPI == EPI_PUSH && p.fuse.rs_out != nullptr)
+        reduce_scatter_tail(p.fuse, p.wait_limit_ns, abort_flag, comm_ok);
 
     // ---------------------------------------------------------- teardown
     __syncwarp();
@@ -801,12 +958,14 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     kp.k_end = a.grouped.k_end;
     kp.error_flag = a.error_flag;
     kp.wait_limit_ns = a.wait_limit_ns ? a.wait_limit_ns : 4000000000ull;
+    kp.fuse = a.fuse;
 
     if (a.epilogue == EPI_SWIGLU && (a.D2 == nullptr || (a.ldd2 % 8)))
         return cudaErrorInvalidValue;
     if (a.epilogue == EPI_DSWIGLU && (a.aux == nullptr || (a.ldaux % 8)))
         return cudaErrorInvalidValue;
-    if (a.epilogue == EPI_PUSH && (a.peer_out == nullptr || (kp.rows_per_peer % tile_m)))
+    if (a.epilogue == EPI_PUSH &&
+        ((a.peer_out == nullptr && a.fuse.rs_peer_out[0] == nullptr) || (kp.rows_per_peer % tile_m)))
         return cudaErrorInvalidValue;
     if (a.a_ready != nullptr && (kp.rows_per_flag % BM))
         return cudaErrorInvalidValue;

@@ -32,6 +32,35 @@ struct GroupedArgs {
     int groups;
 };
 
+// Collective fused into the GEMM (all pointers are addresses valid on this GPU; peers'
+// memory is reached through the symmetric heap mapping).
+struct FuseArgs {
+    int nranks, rank;
+    int shard_rows;      // rows of one rank's shard of the gathered / scattered matrix
+    int row_bytes;       // bytes of one row (rows are contiguous)
+    uint32_t epoch;      // this call's value for the start flags and ready words
+    // all_gather -> GEMM: the communication warps copy shard q from ag_src[q] into
+    // ag_dst + q * shard bytes (own shard: local copy, or nothing when ag_src[rank] is the
+    // destination itself) and publish `epoch` in ag_ready[q]; pass ag_ready as `a_ready`.
+    void* ag_dst;                    // null = no fused gather
+    const void* ag_src[8];
+    uint32_t* ag_ready;              // [nranks] local
+    uint32_t* ag_count;              // [nranks] local, zero between calls
+    uint32_t* ag_start_peer[8];      // peer q's start-flag array (this rank writes slot [rank])
+    const uint32_t* ag_start_local;  // this rank's start-flag array [nranks]
+    // GEMM -> reduce_scatter (EPI_PUSH): peer_out[p] is rank p's staging slot for this
+    // rank's partial rows; every finished 32-row quarter of a tile bumps rs_count_peer[p][rank]; the tail
+    // waits for rs_count_local[q] >= rs_target for all q and writes
+    // rs_out = sum_q rs_stage_local[q] (+ rs_residual).
+    void* rs_peer_out[8];            // rank p's staging slot for this rank's partial rows
+    uint32_t* rs_count_peer[8];      // [0] null = no counting
+    const uint32_t* rs_count_local;  // [nranks]
+    uint32_t rs_target;
+    const void* rs_stage_local;      // this rank's n staging slots, slot q = rank q's partial rows
+    void* rs_out;                    // null = no tail reduce in this kernel
+    const void* rs_residual;         // optional: added to the reduced shard
+};
+
 struct GemmArgs {
     const void* A;
     const void* B;
@@ -56,6 +85,7 @@ struct GemmArgs {
     uint32_t* tile_done;    // optional: counter bumped once per finished tile (gpu scope)
     // grouped problems (MoE); null m_block_group = dense
     GroupedArgs grouped;
+    FuseArgs fuse;            // zero-initialised = no fused collective
     int* error_flag;          // device word; non-zero after a wait ran out
     uint64_t wait_limit_ns;   // 0 = default (4 s)
 };
