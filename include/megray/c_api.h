@@ -126,6 +126,24 @@ int megray_tp_ag_gemm(void* comm, const megray_gemm_args* args, void* gather_buf
 int megray_tp_gemm_rs(void* comm, const megray_gemm_args* args, void* staging, void* out,
                       const void* residual, void* flags, void* stream);
 
+/* ---- expert-parallel MoE kernels (src/kernels/moe.cuh) ---------------------------------------- */
+int megray_moe_route(const float* logits, int tokens, int experts, int* idx, float* w, int* counts, void* stream);
+int megray_moe_route_bwd(const int* idx, const float* w, const float* dw, int tokens, int experts,
+                         float* dlogits, void* stream);
+int megray_moe_plan(const int* counts_all, int nranks, int rank, int experts, int capacity_rows,
+                    int* send_base, int* seg_begin, int* seg_end, int* seg_rows, int* block_group,
+                    int* total, void* stream);
+int megray_moe_zero_pads(void* buf, int row_elems, const int* seg_begin, const int* seg_rows,
+                         const int* seg_end, int local_experts, void* stream);
+/* peer_bufs: array of `nranks` device addresses (host array), one buffer per owner rank */
+int megray_moe_dispatch(const void* src, int tokens, int row_elems, const int* idx, const float* w,
+                        const int* send_base, int* cursor, const int* pos_in, int* pos_out,
+                        void* const* peer_bufs, int nranks, int local_experts, int capacity_rows, void* stream);
+int megray_moe_combine(void* out, int tokens, int row_elems, const int* idx, const float* w,
+                       const int* pos, void* const* peer_bufs, int nranks, int local_experts, int capacity_rows, void* stream);
+int megray_moe_combine_dw(const void* dout, int tokens, int row_elems, const int* idx, const int* pos,
+                          void* const* peer_bufs, int nranks, int local_experts, int capacity_rows, float* dw, void* stream);
+
 /* ---- training-harness kernels ---------------------------------------------------------------- */
 int megray_sgd_bf16(void* w, const void* g, float* momentum, uint64_t n, float lr, float mu,
                     float weight_decay, void* stream);

@@ -116,6 +116,13 @@ def _declare(lib) -> None:
     d("megray_rmsnorm_bwd_bf16", i32, vp, vp, vp, vp, vp, i32, i32, vp)
     d("megray_tp_ag_gemm", i32, vp, P(GemmArgs), vp, vp, vp, vp)
     d("megray_tp_gemm_rs", i32, vp, P(GemmArgs), vp, vp, vp, vp, vp)
+    d("megray_moe_route", i32, vp, i32, i32, vp, vp, vp, vp)
+    d("megray_moe_route_bwd", i32, vp, vp, vp, i32, i32, vp, vp)
+    d("megray_moe_plan", i32, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp)
+    d("megray_moe_zero_pads", i32, vp, i32, vp, vp, vp, i32, vp)
+    d("megray_moe_dispatch", i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, P(vp), i32, i32, i32, vp)
+    d("megray_moe_combine", i32, vp, i32, i32, vp, vp, vp, P(vp), i32, i32, i32, vp)
+    d("megray_moe_combine_dw", i32, vp, i32, i32, vp, vp, P(vp), i32, i32, i32, vp, vp)
     d("megray_dtype_size", sz, i32)
     d("megray_set_log_level", None, i32)
     d("megray_trace_enable", None, C.c_char_p)

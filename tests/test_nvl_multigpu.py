@@ -34,6 +34,11 @@ def test_tensor_parallel_model_matches_single_gpu():
     assert out.count("RANK_OK") == 2, out[-3000:]
 
 
+def test_expert_parallel_moe_matches_single_gpu():
+    out = torchrun("moe.py", env={"MEGRAY_HEAP_MB": "1024"})
+    assert out.count("RANK_OK") == 2, out[-3000:]
+
+
 def test_device_wait_limit_reports_timeout_and_keeps_the_gpu_usable():
     out = torchrun("timeout.py")
     assert out.count("RANK_OK") == 2, out[-3000:]
