@@ -376,6 +376,200 @@ __global__ void __launch_bounds__(512) exchange_family_kernel(const ExchangeArgs
     }
 }
 
+
+// ------------------------------------------------------------------ direct family
+// multimem (NVLS) loads: the switch combines the 16 bytes at the same heap offset of all ranks.
+template <typename T, int OP>
+__device__ __forceinline__ uint4 mc_ld_reduce(const void* p);
+
+#define MC_LD(T, OP, STR)                                                                       \
+    template <>                                                                                 \
+    __device__ __forceinline__ uint4 mc_ld_reduce<T, OP>(const void* p) {                       \
+        uint4 v;                                                                                \
+        asm volatile("multimem.ld_reduce.relaxed.sys.global." STR " {%0, %1, %2, %3}, [%4];"    \
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)                               \
+                     : "l"(p)                                                                   \
+                     : "memory");                                                               \
+        return v;                                                                               \
+    }
+MC_LD(__nv_bfloat16, MegRay::MEGRAY_SUM, "add.acc::f32.v4.bf16x2")
+MC_LD(__nv_bfloat16, MegRay::MEGRAY_MAX, "max.v4.bf16x2")
+MC_LD(__nv_bfloat16, MegRay::MEGRAY_MIN, "min.v4.bf16x2")
+MC_LD(__half, MegRay::MEGRAY_SUM, "add.acc::f32.v4.f16x2")
+MC_LD(__half, MegRay::MEGRAY_MAX, "max.v4.f16x2")
+MC_LD(__half, MegRay::MEGRAY_MIN, "min.v4.f16x2")
+MC_LD(float, MegRay::MEGRAY_SUM, "add.v4.f32")
+#undef MC_LD
+// combinations the switch cannot reduce are never launched with NVLS; keep the template whole
+template <typename T, int OP>
+__device__ __forceinline__ uint4 mc_ld_reduce(const void* p) {
+    return __ldcg(reinterpret_cast<const uint4*>(p));
+}
+
+__device__ __forceinline__ void mc_st_v4(void* p, const uint4& v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y),
+                 "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ void mc_st_v2(void* p, const uint2& v) {
+    asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+
+// Reduce elements [b, e) of slice `rank`: load from all inputs, combine in rank order, scale,
+// cast; store into every rank's output (all_reduce) or into `out_local` (reduce_scatter).
+template <typename Tin, typename Tout, int OP, bool NVLS>
+__device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, uint64_t elem0, uint64_t b, uint64_t e) {
+    using A = typename Acc<Tin>::type;
+    constexpr int V = 16 / sizeof(Tin);
+    constexpr int OB = V * sizeof(Tout);
+    const int n = a.c.nranks;
+    const bool do_scale = IsFloatAcc<A>::value && OP == MegRay::MEGRAY_SUM && a.scale != 1.0f;
+    const bool to_all = a.kind == DIRECT_ALL_REDUCE;
+    const uint64_t nvec = (e - b) / V;
+    const uint64_t in_byte0 = a.in_off + (elem0 + b) * sizeof(Tin);
+    // all_reduce writes the slice back at the same element positions; reduce_scatter writes the
+    // slice to the start of the local result
+    const uint64_t out_byte0 = to_all ? a.out_off + (elem0 + b) * sizeof(Tout) : b * sizeof(Tout);
+    for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+        A acc[V];
+        if (NVLS) {
+            uint4 raw = mc_ld_reduce<Tin, OP>(a.mc_base + in_byte0 + i * 16);
+            const Tin* el = reinterpret_cast<const Tin*>(&raw);
+#pragma unroll
+            for (int k = 0; k < V; ++k)
+                acc[k] = widen<Tin>(el[k]);
+        } else {
+            uint4 raw[kMaxRanks];
+#pragma unroll
+            for (int q = 0; q < kMaxRanks; ++q)
+                if (q < n)
+                    raw[q] = ld_cg_v4(a.c.peers.heap[q] + in_byte0 + i * 16);
+#pragma unroll
+            for (int q = 0; q < kMaxRanks; ++q) {
+                if (q < n) {
+                    const Tin* el = reinterpret_cast<const Tin*>(&raw[q]);
+#pragma unroll
+                    for (int k = 0; k < V; ++k)
+                        acc[k] = q == 0 ? widen<Tin>(el[k]) : combine<OP, A>(acc[k], widen<Tin>(el[k]));
+                }
+            }
+        }
+        Tout o[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            if (do_scale)
+                acc[k] = static_cast<A>(acc[k] * static_cast<A>(a.scale));
+            o[k] = narrow<Tout, A>(acc[k]);
+        }
+        if (!to_all) {
+            char* dst = static_cast<char*>(a.out_local) + out_byte0 + i * OB;
+            if (OB >= 16) {
+#pragma unroll
+                for (int w = 0; w < OB / 16; ++w)
+                    reinterpret_cast<uint4*>(dst)[w] = reinterpret_cast<const uint4*>(o)[w];
+            } else {
+                *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
+            }
+        } else if (NVLS) {
+            char* dst = a.mc_base + out_byte0 + i * OB;
+            if (OB >= 16) {
+#pragma unroll
+                for (int w = 0; w < OB / 16; ++w)
+                    mc_st_v4(dst + 16 * w, reinterpret_cast<const uint4*>(o)[w]);
+            } else {
+                mc_st_v2(dst, *reinterpret_cast<const uint2*>(o));
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < kMaxRanks; ++q) {
+                if (q < n) {
+                    char* dst = a.c.peers.heap[(a.c.rank + q) % n] + out_byte0 + i * OB;
+                    if (OB >= 16) {
+#pragma unroll
+                        for (int w = 0; w < OB / 16; ++w)
+                            reinterpret_cast<uint4*>(dst)[w] = reinterpret_cast<const uint4*>(o)[w];
+                    } else {
+                        *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
+                    }
+                }
+            }
+        }
+    }
+    // element tail (fewer than V elements): plain peer accesses
+    for (uint64_t i = b + nvec * V + threadIdx.x; i < e; i += blockDim.x) {
+        A acc = widen<Tin>(reinterpret_cast<const Tin*>(a.c.peers.heap[0] + a.in_off)[elem0 + i]);
+        for (int q = 1; q < n; ++q)
+            acc = combine<OP, A>(acc, widen<Tin>(reinterpret_cast<const Tin*>(a.c.peers.heap[q] + a.in_off)[elem0 + i]));
+        if (do_scale)
+            acc = static_cast<A>(acc * static_cast<A>(a.scale));
+        const Tout o = narrow<Tout, A>(acc);
+        if (!to_all) {
+            static_cast<Tout*>(a.out_local)[i] = o;
+        } else {
+            for (int q = 0; q < n; ++q)
+                reinterpret_cast<Tout*>(a.c.peers.heap[q] + a.out_off)[elem0 + i] = o;
+        }
+    }
+}
+
+template <typename Tin, typename Tout, bool NVLS>
+__global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) {
+    const CommonArgs& c = a.c;
+    const int n = c.nranks, rank = c.rank;
+    constexpr uint64_t V = 16 / sizeof(Tin);
+    uint32_t epoch = c.epoch;
+    // inputs are final / outputs may be overwritten on every rank
+    if (!cta_barrier(c, ++epoch))
+        return;
+    if (a.kind == DIRECT_ALL_GATHER) {
+        // this rank's block into slot `rank` of every output
+        const uint64_t bytes = a.len * sizeof(Tin);
+        const uint64_t per_cta = round_up_u64((bytes + gridDim.x - 1) / gridDim.x, 16);
+        const uint64_t b = min(bytes, per_cta * blockIdx.x), e = min(bytes, b + per_cta);
+        const char* src = static_cast<const char*>(a.in_local);
+        if (NVLS && ((reinterpret_cast<uintptr_t>(src) | (a.out_off + rank * bytes)) & 15) == 0) {
+            char* dst = a.mc_base + a.out_off + rank * bytes;
+            const uint64_t nv = (e - b) / 16;
+            for (uint64_t i = threadIdx.x; i < nv; i += blockDim.x)
+                mc_st_v4(dst + b + i * 16, ld_cg_v4(src + b + i * 16));
+            for (uint64_t k = b + nv * 16 + threadIdx.x; k < e; k += blockDim.x)
+                for (int q = 0; q < n; ++q)
+                    (c.peers.heap[q] + a.out_off + rank * bytes)[k] = src[k];
+        } else {
+            for (int qq = 0; qq < n; ++qq) {
+                const int q = (rank + qq) % n;
+                cta_copy(c.peers.heap[q] + a.out_off + rank * bytes + b, src + b, e - b);
+            }
+        }
+    } else {
+        // slice `rank`: all_reduce splits len into n slices of se elements, reduce_scatter's
+        // slice is the rank-th block of len elements
+        uint64_t se, elem0, L;
+        if (a.kind == DIRECT_ALL_REDUCE) {
+            se = round_up_u64((a.len + n - 1) / n, V);
+            elem0 = min(a.len, se * rank);
+            L = min(a.len, elem0 + se) - elem0;
+        } else {
+            elem0 = a.len * rank;
+            L = a.len;
+        }
+        const uint64_t per_cta = round_up_u64((L + gridDim.x - 1) / gridDim.x, V);
+        const uint64_t b = min(L, per_cta * blockIdx.x), e = min(L, b + per_cta);
+        switch (a.op) {
+            case MegRay::MEGRAY_SUM:
+                direct_reduce_range<Tin, Tout, MegRay::MEGRAY_SUM, NVLS>(a, elem0, b, e);
+                break;
+            case MegRay::MEGRAY_MAX:
+                direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MAX, NVLS>(a, elem0, b, e);
+                break;
+            default:
+                direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MIN, NVLS>(a, elem0, b, e);
+        }
+    }
+    // all transfers are complete before any rank uses its output or overwrites its input
+    cta_barrier(c, ++epoch);
+}
+
 // ------------------------------------------------------------------ stand-alone reduce_n
 struct ReduceNArgs {
     const void* in[kMaxRanks];
@@ -509,6 +703,20 @@ struct ReduceLauncher {
         return run_reduce<Tin, Tout>(a, ctas, threads, s);
     }
 };
+struct DirectLauncher {
+    const DirectArgs& a;
+    int ctas, threads;
+    cudaStream_t s;
+    template <typename Tin, typename Tout>
+    cudaError_t operator()() const {
+        if (a.mc_base != nullptr)
+            direct_family_kernel<Tin, Tout, true><<<ctas, threads, 0, s>>>(a);
+        else
+            direct_family_kernel<Tin, Tout, false><<<ctas, threads, 0, s>>>(a);
+        count_launch();
+        return cudaGetLastError();
+    }
+};
 struct ReduceNLauncher {
     const ReduceNArgs& a;
     cudaStream_t s;
@@ -525,6 +733,26 @@ cudaError_t launch_reduce(const ReduceArgs& a, int ctas, int threads, cudaStream
         a.c.nranks > kMaxRanks)
         return cudaErrorInvalidValue;
     return dispatch_types(a.in_dtype, a.out_dtype, ReduceLauncher{a, ctas, threads, stream});
+}
+
+bool nvls_supports(DType in_dtype, DType out_dtype, ReduceOp op) {
+    using namespace MegRay;
+    if (in_dtype == MEGRAY_BFLOAT16 || in_dtype == MEGRAY_FLOAT16)
+        return out_dtype == in_dtype || out_dtype == MEGRAY_FLOAT32 || out_dtype == MEGRAY_BFLOAT16 ||
+               out_dtype == MEGRAY_FLOAT16;
+    if (in_dtype == MEGRAY_FLOAT32)
+        return op == MEGRAY_SUM &&
+               (out_dtype == MEGRAY_FLOAT32 || out_dtype == MEGRAY_BFLOAT16 || out_dtype == MEGRAY_FLOAT16);
+    return false;
+}
+
+cudaError_t launch_direct(const DirectArgs& a, int ctas, int threads, cudaStream_t stream) {
+    if (ctas < 1 || ctas > kMaxCtas || threads < 32 || threads > 512 || a.c.nranks < 1 ||
+        a.c.nranks > kMaxRanks)
+        return cudaErrorInvalidValue;
+    if (a.mc_base != nullptr && a.kind != DIRECT_ALL_GATHER && !nvls_supports(a.in_dtype, a.out_dtype, a.op))
+        return cudaErrorInvalidValue;
+    return dispatch_types(a.in_dtype, a.out_dtype, DirectLauncher{a, ctas, threads, stream});
 }
 
 cudaError_t launch_exchange(const ExchangeArgs& a, int ctas, int threads, cudaStream_t stream) {

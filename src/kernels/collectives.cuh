@@ -94,6 +94,37 @@ struct ExchangeArgs {
     uint64_t pull_bytes[kMaxRanks];  // bytes to load from peer q (<= chunk_bytes)
 };
 
+// Single-pass ("direct") collectives for buffers that live in the symmetric heap at the same
+// offset on every rank: no staging at all.
+//   all_reduce      barrier; rank r loads slice r of all n inputs straight from the peers' heaps
+//                   (or, with NVLS, one multimem.ld_reduce that the NVSwitch reduces), combines,
+//                   scales, casts and stores the result into all n outputs (one multimem.st with
+//                   NVLS); barrier.  Loads and stores overlap, so both link directions are busy.
+//   reduce_scatter  barrier; load slice r of all inputs, combine, store locally; barrier.
+//   all_gather      barrier; store this rank's block into slot r of all n outputs; barrier.
+enum DirectKind : int { DIRECT_ALL_REDUCE = 0, DIRECT_REDUCE_SCATTER = 1, DIRECT_ALL_GATHER = 2 };
+
+struct DirectArgs {
+    CommonArgs c;
+    int kind;
+    uint64_t in_off;       // heap offset of the input (all_reduce, reduce_scatter)
+    uint64_t out_off;      // heap offset of the output (all_reduce, all_gather)
+    const void* in_local;  // all_gather: this rank's block (any device memory)
+    void* out_local;       // reduce_scatter: this rank's result (any device memory)
+    uint64_t len;          // all_reduce: total elements; others: elements per rank
+    float scale;
+    MegRay::DType in_dtype;
+    MegRay::DType out_dtype;
+    MegRay::ReduceOp op;
+    char* mc_base;         // non-null: multicast (NVLS) mapping of the heap, use multimem
+};
+
+// True if the NVSwitch can reduce this dtype/op pair (multimem.ld_reduce): bf16/fp16 all ops,
+// fp32 SUM; the rest takes peer loads.
+bool nvls_supports(MegRay::DType in_dtype, MegRay::DType out_dtype, MegRay::ReduceOp op);
+
+cudaError_t launch_direct(const DirectArgs& args, int ctas, int threads, cudaStream_t stream);
+
 cudaError_t launch_reduce(const ReduceArgs& args, int ctas, int threads, cudaStream_t stream);
 cudaError_t launch_exchange(const ExchangeArgs& args, int ctas, int threads, cudaStream_t stream);
 

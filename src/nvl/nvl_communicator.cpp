@@ -3,8 +3,11 @@
 #include <string.h>
 #include <unistd.h>
 
+#include <stdio.h>
+
 #include <algorithm>
 #include <random>
+#include <string>
 
 #include "megray/cuda_context.h"
 #include "megray/options.h"
@@ -17,6 +20,7 @@
 namespace MegRay {
 
 using mgk::coll::CommonArgs;
+using mgk::coll::DirectArgs;
 using mgk::coll::ExchangeArgs;
 using mgk::coll::kMaxCtas;
 using mgk::coll::kMaxRanks;
@@ -34,6 +38,34 @@ int64_t env_i64(const char* name, int64_t dflt) {
     return atoll(e);
 }
 
+// Reads an integer value of `"key": value` from a small JSON text (the tune table written by
+// bench/tune.py); returns dflt when the key is absent.
+int64_t json_i64(const std::string& text, const char* key, int64_t dflt) {
+    const std::string k = std::string("\"") + key + "\"";
+    size_t at = text.find(k);
+    if (at == std::string::npos)
+        return dflt;
+    at = text.find(':', at + k.size());
+    if (at == std::string::npos)
+        return dflt;
+    char* end = nullptr;
+    const long long v = strtoll(text.c_str() + at + 1, &end, 10);
+    return end == text.c_str() + at + 1 ? dflt : static_cast<int64_t>(v);
+}
+
+std::string read_file(const std::string& path) {
+    std::string out;
+    FILE* f = fopen(path.c_str(), "r");
+    if (f == nullptr)
+        return out;
+    char buf[4096];
+    size_t n;
+    while ((n = fread(buf, 1, sizeof(buf), f)) > 0)
+        out.append(buf, n);
+    fclose(f);
+    return out;
+}
+
 bool is_float(DType t) {
     return t == MEGRAY_FLOAT16 || t == MEGRAY_BFLOAT16 || t == MEGRAY_FLOAT32 ||
            t == MEGRAY_FLOAT64;
@@ -48,6 +80,26 @@ NvlCommunicator::NvlCommunicator(uint32_t nranks, uint32_t rank) : Communicator(
     m_timeout_ns = static_cast<uint64_t>(o.device_timeout_ms) * 1000000ull;
     m_max_ctas = o.max_ctas > 0 ? std::min(o.max_ctas, kMaxCtas) : 64;
     m_oneshot_bytes = static_cast<size_t>(env_i64("MEGRAY_ONESHOT_BYTES", 256 * 1024));
+    m_direct = env_i64("MEGRAY_DIRECT", 1) != 0;
+    m_cta_bytes = static_cast<size_t>(env_i64("MEGRAY_CTA_BYTES", 128 * 1024));
+    // measured crossover points (bench/tune.py) override the built-in defaults; explicit
+    // environment settings override the table
+    if (!o.tune_file.empty()) {
+        const std::string t = read_file(o.tune_file);
+        if (t.empty()) {
+            MEGRAY_WARN("tune file %s is missing or empty", o.tune_file.c_str());
+        } else {
+            if (getenv("MEGRAY_ONESHOT_BYTES") == nullptr)
+                m_oneshot_bytes = static_cast<size_t>(json_i64(t, "oneshot_bytes", static_cast<int64_t>(m_oneshot_bytes)));
+            if (o.max_ctas <= 0)
+                m_max_ctas = std::min<int>(kMaxCtas, static_cast<int>(json_i64(t, "max_ctas", m_max_ctas)));
+            if (getenv("MEGRAY_CTA_BYTES") == nullptr)
+                m_cta_bytes = static_cast<size_t>(json_i64(t, "cta_bytes", static_cast<int64_t>(m_cta_bytes)));
+            m_nvls_min_bytes = static_cast<size_t>(json_i64(t, "nvls_min_bytes", 0));
+        }
+    }
+    if (m_cta_bytes < 1024)
+        m_cta_bytes = 1024;
     if (o.algo == "oneshot")
         m_oneshot_bytes = ~static_cast<size_t>(0);
     else if (o.algo == "twoshot")
@@ -222,10 +274,54 @@ size_t NvlCommunicator::workspace_off() {
 
 int NvlCommunicator::pick_ctas(size_t bytes) const {
     // enough CTAs to keep the links busy, few enough that flag traffic stays small
-    size_t want = (bytes + (128u << 10) - 1) / (128u << 10);
+    size_t want = (bytes + m_cta_bytes - 1) / m_cta_bytes;
     if (want < 1)
         want = 1;
     return static_cast<int>(std::min<size_t>(want, static_cast<size_t>(m_max_ctas)));
+}
+
+
+// ------------------------------------------------------------------ direct (zero-copy) paths
+
+bool NvlCommunicator::aligned_heap(const void* p, size_t bytes) {
+    return in_heap(p, bytes) && (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+}
+
+Status NvlCommunicator::direct_launch(int kind, const void* in, void* out, size_t len, DType in_dtype,
+                                      DType out_dtype, float scale, ReduceOp op, cudaStream_t stream) {
+    DirectArgs a;
+    memset(&a, 0, sizeof(a));
+    a.c = common_args();
+    a.kind = kind;
+    a.len = len;
+    a.scale = scale;
+    a.in_dtype = in_dtype;
+    a.out_dtype = out_dtype;
+    a.op = op;
+    size_t bytes = len * get_dtype_size(in_dtype);
+    if (kind == mgk::coll::DIRECT_ALL_GATHER) {
+        a.in_local = in;
+        a.out_off = static_cast<size_t>(static_cast<char*>(out) - m_heap.local());
+        bytes *= m_nranks;
+    } else {
+        a.in_off = static_cast<size_t>(static_cast<const char*>(in) - m_heap.local());
+        if (kind == mgk::coll::DIRECT_ALL_REDUCE)
+            a.out_off = static_cast<size_t>(static_cast<char*>(out) - m_heap.local());
+        else {
+            a.out_local = out;
+            bytes *= m_nranks;
+        }
+    }
+    const bool nvls = m_heap.multicast() != nullptr && bytes >= m_nvls_min_bytes &&
+                      (kind == mgk::coll::DIRECT_ALL_GATHER || mgk::coll::nvls_supports(in_dtype, out_dtype, op));
+    a.mc_base = nvls ? m_heap.multicast() : nullptr;
+    MEGRAY_CHECK(check_cuda(mgk::coll::launch_direct(a, pick_ctas(bytes), 512, stream)));
+    after_launch(stream);
+    if (nvls)
+        m_stats.algo_nvls++;
+    else
+        m_stats.algo_twoshot++;
+    return MEGRAY_OK;
 }
 
 // ------------------------------------------------------------------ reduce family
@@ -257,6 +353,17 @@ Status NvlCommunicator::reduce_impl(ReduceKind kind, const void* in, void* out, 
 
     const char* inb = static_cast<const char*>(in);
     char* outb = static_cast<char*>(out);
+
+    // Buffers inside the symmetric heap (at the same offset on every rank, which is what
+    // sym_alloc gives) need no staging: single-pass kernels read and write the peers directly.
+    if (m_direct && n > 1 && len * ein > m_oneshot_bytes) {
+        if (kind == ReduceKind::AllReduce && aligned_heap(in, len * ein) && aligned_heap(out, len * eout))
+            return direct_launch(mgk::coll::DIRECT_ALL_REDUCE, in, out, len, in_dtype, out_dtype, scale, op, stream);
+        if (kind == ReduceKind::ReduceScatter && aligned_heap(in, len * ein * n) && (len * ein) % 16 == 0 &&
+            (reinterpret_cast<uintptr_t>(out) & 15) == 0)
+            return direct_launch(mgk::coll::DIRECT_REDUCE_SCATTER, in, out, len, in_dtype, out_dtype, scale, op,
+                                 stream);
+    }
 
     if (kind == ReduceKind::ReduceScatter) {
         // `len` is the per-rank result length; slice j of the input starts at j*len
@@ -380,6 +487,10 @@ Status NvlCommunicator::all_gather(const void* sendbuff, void* recvbuff, size_t 
     m_stats.bytes += bytes;
     if (bytes == 0)
         return MEGRAY_OK;
+    if (m_direct && m_nranks > 1 && bytes > m_oneshot_bytes / m_nranks && aligned_heap(recvbuff, bytes * m_nranks) &&
+        bytes % 16 == 0)
+        return direct_launch(mgk::coll::DIRECT_ALL_GATHER, sendbuff, recvbuff, bytes, MEGRAY_UINT8, MEGRAY_UINT8, 1.0f,
+                             MEGRAY_SUM, stream);
     const size_t cap = round_down(m_ws_bytes - 16, 16);
     for (size_t off = 0; off < bytes; off += cap) {
         const size_t piece = std::min(cap, bytes - off);

@@ -95,6 +95,9 @@ private:
     size_t workspace_off();  // offset of the workspace this launch uses; flips the parity
     void after_launch(cudaStream_t stream);
     int pick_ctas(size_t bytes) const;
+    bool aligned_heap(const void* p, size_t bytes);
+    Status direct_launch(int kind, const void* in, void* out, size_t len, DType in_dtype, DType out_dtype,
+                         float scale, ReduceOp op, cudaStream_t stream);
     Status check_cuda(cudaError_t e);
 
     SymmetricHeap m_heap;
@@ -110,6 +113,9 @@ private:
     uint64_t m_timeout_ns;
     int m_max_ctas;
     size_t m_oneshot_bytes;
+    size_t m_nvls_min_bytes = 0;
+    size_t m_cta_bytes = 128 * 1024;  // message bytes per CTA when sizing a collective's grid
+    bool m_direct = true;
     int* m_status_host = nullptr;  // pinned, mapped
     int* m_status_dev = nullptr;
     cudaStream_t m_last_stream = nullptr;

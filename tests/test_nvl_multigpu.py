@@ -39,6 +39,20 @@ def test_expert_parallel_moe_matches_single_gpu():
     assert out.count("RANK_OK") == 2, out[-3000:]
 
 
+def test_single_pass_collectives_on_heap_tensors():
+    out = torchrun("direct.py", env={"MEGRAY_HEAP_MB": "4096"})
+    print("\n".join(l for l in out.splitlines() if l.startswith(("BW", "RANK_OK"))))
+    assert out.count("RANK_OK") == 2, out[-3000:]
+    assert "nvls_calls=0" in out
+
+
+def test_single_pass_collectives_through_nvswitch_multimem():
+    # falls back to peer loads/stores (with a warning) where multicast is unavailable
+    out = torchrun("direct.py", env={"MEGRAY_HEAP_MB": "4096", "MEGRAY_NVLS": "1", "NCCL_NVLS_ENABLE": "1"})
+    print("\n".join(l for l in out.splitlines() if l.startswith(("BW", "RANK_OK"))))
+    assert out.count("RANK_OK") == 2, out[-3000:]
+
+
 def test_device_wait_limit_reports_timeout_and_keeps_the_gpu_usable():
     out = torchrun("timeout.py")
     assert out.count("RANK_OK") == 2, out[-3000:]
