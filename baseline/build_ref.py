@@ -9,6 +9,7 @@ build.  Products:
 
     baseline/_ref/libmegray_ref.so   reference objects + baseline/ref_shim.cpp (C doorway)
     baseline/_ref/performance        the reference's own benchmark (test/performance.cpp)
+    baseline/_ref/megray_bench_ref   bench/megray_bench.cpp built against the reference (device-timed sweep)
 
     python baseline/build_ref.py [--reference /root/reference]
 """
@@ -68,6 +69,13 @@ def build(ref: str) -> str:
         subprocess.check_call(common + [f"-I{ref}/test", "-c", os.path.join(ref, s), "-o", o])
         perf_objs.append(o)
     subprocess.check_call(["g++", "-o", os.path.join(OUT, "performance")] + perf_objs + objs + link)
+    # the device-timed sweep tool of this repository, compiled against the reference's headers and
+    # linked with the reference's objects: the like-for-like collective baseline
+    bench_src = os.path.join(os.path.dirname(HERE), "bench", "megray_bench.cpp")
+    if os.path.exists(bench_src):
+        bo = os.path.join(OUT, "megray_bench_ref.o")
+        subprocess.check_call(common + ["-DMEGRAY_BENCH_REFERENCE", "-c", bench_src, "-o", bo])
+        subprocess.check_call(["g++", "-o", os.path.join(OUT, "megray_bench_ref"), bo] + objs + link)
     return lib
 
 

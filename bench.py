@@ -14,9 +14,10 @@ scaling).  Synthetic data, random-init weights.
 For N > 1 launch one process per GPU (torchrun / python -m torch.distributed.run); when
 WORLD_SIZE is absent and --gpus > 1 the script re-launches itself that way.  Rank 0 prints
 one JSON line.  `value` is device-timed (CUDA events around exactly K steps, max over
-ranks); `e2e` is the same step through the public `TPMLPStack.train_step` call, which
-copies the step's tokens from pinned host memory and reads the loss back, timed on the
-host clock between two synchronisations.
+ranks); `e2e` is the same step through the public `TPMLPStack.train_step_async` call, which
+every step copies that step's tokens from pinned host memory (on a copy stream) and reads that
+step's loss back (asynchronously, delivered one call later), timed on the host clock between
+two synchronisations.
 """
 from __future__ import annotations
 
@@ -121,11 +122,15 @@ def run_ours(args, rank, world, local_rank):
 
     e2e = None
     if not args.no_e2e:
-        model.train_step(x_host)
+        # the public training-loop call: per step one pinned-host -> device copy of the tokens and
+        # one device -> host read of the loss, both pipelined with the previous / next step
+        model.train_step_async(x_host)
+        model.flush()
         barrier()
         t0 = time.perf_counter()
         for _ in range(args.steps):
-            model.train_step(x_host)
+            model.train_step_async(x_host)
+        model.flush()
         barrier()
         e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1000.0 / args.steps)
         e2e = {"value": cfg.tokens / (e2e_ms / 1000.0), "unit": "tokens/s", "ms_per_step": e2e_ms,

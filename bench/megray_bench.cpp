@@ -148,14 +148,18 @@ Backend backend_of(const std::string& name) {
 // `unit` is the reference tool's notion of buffer size for the function (per-rank send size
 // for all_gather, per-rank receive size for reduce_scatter, per-peer chunk for all_to_all /
 // gather / scatter, the whole buffer otherwise: reference test/performance.cpp:153-252).
-Result run_one(const BenchOptions& o, const std::string& func, Backend backend, size_t unit_bytes,
-               const DTypeInfo& dt, ReduceOp op, int port) {
+// One communicator group serves all sizes of a (backend, function) pair.
+std::vector<Result> run_sizes(const BenchOptions& o, const std::string& func, Backend backend,
+                              const std::vector<size_t>& sizes, const DTypeInfo& dt, ReduceOp op, int port) {
     const int n = o.devices;
-    const size_t len = std::max<size_t>(1, unit_bytes / dt.size);
-    std::vector<double> times(n, 0.0);
-    std::atomic<bool> all_ok{true};
+    std::vector<std::vector<double>> times(sizes.size(), std::vector<double>(n, 0.0));
+    std::vector<std::atomic<int>> bad(sizes.size());
+    for (auto& b : bad) b = 0;
+    std::atomic<bool> init_ok{true};
     ThreadBarrier bar(n);
     std::vector<std::thread> threads;
+    size_t max_unit = 0;
+    for (size_t s : sizes) max_unit = std::max(max_unit, s);
     for (int r = 0; r < n; ++r) {
         threads.emplace_back([&, r] {
             CK(cudaSetDevice(r));
@@ -167,63 +171,66 @@ Result run_one(const BenchOptions& o, const std::string& func, Backend backend, 
                 comm = get_communicator(static_cast<uint32_t>(n), static_cast<uint32_t>(r), backend);
             } catch (const std::exception& e) {
                 if (r == 0) fprintf(stderr, "backend unavailable: %s\n", e.what());
-                all_ok = false;
-                return;
+                init_ok = false;
             }
-            if (comm->init(o.master_ip.c_str(), port) != MEGRAY_OK) {
-                all_ok = false;
-                return;
-            }
-            size_t in_len = len, out_len = len;
-            if (func == "all_gather" || func == "gather") out_len = len * n;
-            if (func == "reduce_scatter" || func == "scatter") in_len = len * n;
-            if (func == "all_to_all") in_len = out_len = len * n;
-            void *in = nullptr, *out = nullptr;
-            CK(cudaMalloc(&in, in_len * dt.size));
-            CK(cudaMalloc(&out, out_len * dt.size));
-            CK(cudaMemset(in, r + 1, in_len * dt.size));
-            CK(cudaMemset(out, 0, out_len * dt.size));
-            const uint32_t root = 0;
-            auto call = [&]() -> Status {
-                if (func == "all_reduce") return comm->all_reduce(in, out, len, dt.dtype, op, ctx);
-                if (func == "all_gather") return comm->all_gather(in, out, len, dt.dtype, ctx);
-                if (func == "reduce_scatter") return comm->reduce_scatter(in, out, len, dt.dtype, op, ctx);
-                if (func == "all_to_all") return comm->all_to_all(in, out, len, dt.dtype, ctx);
-                if (func == "broadcast") return comm->broadcast(in, out, len, dt.dtype, root, ctx);
-                if (func == "reduce") return comm->reduce(in, out, len, dt.dtype, op, root, ctx);
-                if (func == "gather") return comm->gather(in, out, len, dt.dtype, root, ctx);
-                if (func == "scatter") return comm->scatter(in, out, len, dt.dtype, root, ctx);
-                if (func == "send_recv") {
-                    if (r == 0) return comm->send(in, len, dt.dtype, 1, ctx);
-                    if (r == 1) return comm->recv(out, len, dt.dtype, 0, ctx);
-                    return MEGRAY_OK;
-                }
-                return MEGRAY_INVALID_ARGUMENT;
-            };
-            bool ok = true;
-            for (int i = 0; i < o.warmup && ok; ++i) ok = call() == MEGRAY_OK;
-            CK(cudaStreamSynchronize(stream));
+            if (comm && comm->init(o.master_ip.c_str(), port) != MEGRAY_OK) init_ok = false;
             bar.wait();
+            if (!init_ok.load()) return;
+            const size_t max_len = std::max<size_t>(1, max_unit / dt.size);
+            const bool wide_in = func == "reduce_scatter" || func == "scatter" || func == "all_to_all";
+            const bool wide_out = func == "all_gather" || func == "gather" || func == "all_to_all";
+            void *in = nullptr, *out = nullptr;
+            CK(cudaMalloc(&in, max_len * dt.size * (wide_in ? n : 1)));
+            CK(cudaMalloc(&out, max_len * dt.size * (wide_out ? n : 1)));
+            CK(cudaMemset(in, r + 1, max_len * dt.size * (wide_in ? n : 1)));
+            CK(cudaMemset(out, 0, max_len * dt.size * (wide_out ? n : 1)));
             cudaEvent_t e0, e1;
             CK(cudaEventCreate(&e0));
             CK(cudaEventCreate(&e1));
-            CK(cudaEventRecord(e0, stream));
-            for (int i = 0; i < o.iters && ok; ++i) ok = call() == MEGRAY_OK;
-            CK(cudaEventRecord(e1, stream));
-            CK(cudaStreamSynchronize(stream));
-            float ms = 0.f;
-            CK(cudaEventElapsedTime(&ms, e0, e1));
-            times[r] = ms * 1000.0 / o.iters;
-            if (!ok) all_ok = false;
-            if (o.check && ok && func == "all_reduce" && op == MEGRAY_SUM && dt.dtype == MEGRAY_UINT8) {
-                // every input byte is rank+1: the sum is n(n+1)/2 modulo 256
-                std::vector<uint8_t> h(std::min<size_t>(len, 4096));
-                CK(cudaMemcpy(h.data(), out, h.size(), cudaMemcpyDeviceToHost));
-                const uint8_t want = static_cast<uint8_t>(n * (n + 1) / 2);
-                for (uint8_t v : h)
-                    if (v != want) all_ok = false;
+            const uint32_t root = 0;
+            for (size_t si = 0; si < sizes.size(); ++si) {
+                const size_t len = std::max<size_t>(1, sizes[si] / dt.size);
+                auto call = [&]() -> Status {
+                    if (func == "all_reduce") return comm->all_reduce(in, out, len, dt.dtype, op, ctx);
+                    if (func == "all_gather") return comm->all_gather(in, out, len, dt.dtype, ctx);
+                    if (func == "reduce_scatter") return comm->reduce_scatter(in, out, len, dt.dtype, op, ctx);
+                    if (func == "all_to_all") return comm->all_to_all(in, out, len, dt.dtype, ctx);
+                    if (func == "broadcast") return comm->broadcast(in, out, len, dt.dtype, root, ctx);
+                    if (func == "reduce") return comm->reduce(in, out, len, dt.dtype, op, root, ctx);
+                    if (func == "gather") return comm->gather(in, out, len, dt.dtype, root, ctx);
+                    if (func == "scatter") return comm->scatter(in, out, len, dt.dtype, root, ctx);
+                    if (func == "send_recv") {
+                        if (r == 0) return comm->send(in, len, dt.dtype, 1, ctx);
+                        if (r == 1) return comm->recv(out, len, dt.dtype, 0, ctx);
+                        return MEGRAY_OK;
+                    }
+                    return MEGRAY_INVALID_ARGUMENT;
+                };
+                // fewer repetitions for very large messages keep the sweep short
+                const int iters = sizes[si] >= (256u << 20) ? std::max(3, o.iters / 10) : o.iters;
+                const int warm = sizes[si] >= (256u << 20) ? std::max(2, o.warmup / 10) : o.warmup;
+                bool ok = true;
+                for (int i = 0; i < warm && ok; ++i) ok = call() == MEGRAY_OK;
+                CK(cudaStreamSynchronize(stream));
+                bar.wait();
+                CK(cudaEventRecord(e0, stream));
+                for (int i = 0; i < iters && ok; ++i) ok = call() == MEGRAY_OK;
+                CK(cudaEventRecord(e1, stream));
+                CK(cudaStreamSynchronize(stream));
+                float ms = 0.f;
+                CK(cudaEventElapsedTime(&ms, e0, e1));
+                times[si][r] = ms * 1000.0 / iters;
+                if (!ok) bad[si]++;
+                if (o.check && ok && func == "all_reduce" && op == MEGRAY_SUM && dt.dtype == MEGRAY_UINT8) {
+                    // every input byte is rank+1: the sum is n(n+1)/2 modulo 256
+                    std::vector<uint8_t> h(std::min<size_t>(len, 4096));
+                    CK(cudaMemcpy(h.data(), out, h.size(), cudaMemcpyDeviceToHost));
+                    const uint8_t want = static_cast<uint8_t>(n * (n + 1) / 2);
+                    for (uint8_t v : h)
+                        if (v != want) bad[si]++;
+                }
+                bar.wait();
             }
-            bar.wait();
             comm.reset();
             cudaEventDestroy(e0);
             cudaEventDestroy(e1);
@@ -233,9 +240,11 @@ Result run_one(const BenchOptions& o, const std::string& func, Backend backend, 
         });
     }
     for (auto& t : threads) t.join();
-    Result res;
-    res.time_us = *std::max_element(times.begin(), times.end());
-    res.ok = all_ok.load();
+    std::vector<Result> res(sizes.size());
+    for (size_t si = 0; si < sizes.size(); ++si) {
+        res[si].time_us = *std::max_element(times[si].begin(), times[si].end());
+        res[si].ok = init_ok.load() && bad[si].load() == 0;
+    }
     return res;
 }
 
@@ -311,13 +320,15 @@ int main(int argc, char** argv) {
                        o.devices);
                 printf("%14s %12s %14s %14s %8s\n", "bufsize", "time(us)", "speed(GB/s)", "busbw(GB/s)", "iters");
             }
-            for (size_t bytes : o.sizes) {
-                const int port = o.port > 0 ? o.port : get_free_port();
-                if (create_server(static_cast<uint32_t>(o.devices), port) != MEGRAY_OK) {
-                    fprintf(stderr, "cannot start the rendezvous server on port %d\n", port);
-                    return 1;
-                }
-                Result r = run_one(o, func, backend_of(bname), bytes, *dt, op, port);
+            const int port = o.port > 0 ? o.port : get_free_port();
+            if (create_server(static_cast<uint32_t>(o.devices), port) != MEGRAY_OK) {
+                fprintf(stderr, "cannot start the rendezvous server on port %d\n", port);
+                return 1;
+            }
+            std::vector<Result> results = run_sizes(o, func, backend_of(bname), o.sizes, *dt, op, port);
+            for (size_t si = 0; si < o.sizes.size(); ++si) {
+                const size_t bytes = o.sizes[si];
+                const Result& r = results[si];
                 const double speed = bytes / r.time_us / 1000.0;
                 const double busbw = speed * bus_factor(func, o.devices);
                 if (o.json)

@@ -179,6 +179,51 @@ class TPMLPStack:
         self.x_dev.copy_(x_host, non_blocking=True)
         return float(self.train_step_device(self.x_dev).item())
 
+    def train_step_async(self, x_host: torch.Tensor):
+        """Pipelined form of :meth:`train_step` for training loops: the host-to-device copy of
+        this step's tokens runs on a copy stream (into one of two device buffers) and the loss
+        travels back to pinned host memory asynchronously, so neither transfer stalls the GPU.
+        Returns the loss of the PREVIOUS step (None on the first call); :meth:`flush` returns the
+        last one.  Every step still copies its own inputs in and its own loss out."""
+        if not hasattr(self, "_pipe"):
+            self._pipe = {
+                "copy": torch.cuda.Stream(), "i": 0,
+                "x": [torch.empty_like(self.x_dev) for _ in range(2)],
+                "loss": torch.zeros(2, dtype=torch.float32, pin_memory=True),
+                "free": [None, None], "done": [None, None],
+            }
+        p = self._pipe
+        k = p["i"] & 1
+        main = torch.cuda.current_stream()
+        with torch.cuda.stream(p["copy"]):
+            if p["free"][k] is not None:
+                p["copy"].wait_event(p["free"][k])  # the step that last read this buffer is finished
+            p["x"][k].copy_(x_host, non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record(p["copy"])
+        main.wait_event(ready)
+        loss = self.train_step_device(p["x"][k])
+        p["free"][k] = torch.cuda.Event()
+        p["free"][k].record(main)
+        p["loss"][k:k + 1].copy_(loss, non_blocking=True)
+        p["done"][k] = torch.cuda.Event()
+        p["done"][k].record(main)
+        p["i"] += 1
+        prev = k ^ 1
+        if p["done"][prev] is None:
+            return None
+        p["done"][prev].synchronize()
+        return float(p["loss"][prev])
+
+    def flush(self):
+        """Loss of the most recent :meth:`train_step_async` call (waits for it)."""
+        p = getattr(self, "_pipe", None)
+        if p is None or p["i"] == 0:
+            return None
+        k = (p["i"] - 1) & 1
+        p["done"][k].synchronize()
+        return float(p["loss"][k])
+
     def parameters(self):
         for layer in self.layers:
             yield layer.w_gu

@@ -173,20 +173,21 @@ __device__ __forceinline__ void cta_reduce_slots(const char* slots, uint64_t slo
     const uint64_t nvec = n / V;
     const bool do_scale = IsFloatAcc<A>::value && OP == MegRay::MEGRAY_SUM && scale != 1.0f;
     for (uint64_t i = tid; i < nvec; i += nth) {
+        // all slots' loads are issued before the first use
+        uint4 raw[kMaxRanks];
+#pragma unroll
+        for (int s = 0; s < kMaxRanks; ++s)
+            if (s < nslots)
+                raw[s] = ld_cg_v4(slots + s * slot_stride + i * 16);
         A acc[V];
-        {
-            uint4 raw = ld_cg_v4(slots + i * 16);
-            const Tin* e = reinterpret_cast<const Tin*>(&raw);
 #pragma unroll
-            for (int k = 0; k < V; ++k)
-                acc[k] = widen<Tin>(e[k]);
-        }
-        for (int s = 1; s < nslots; ++s) {
-            uint4 raw = ld_cg_v4(slots + s * slot_stride + i * 16);
-            const Tin* e = reinterpret_cast<const Tin*>(&raw);
+        for (int s = 0; s < kMaxRanks; ++s) {
+            if (s < nslots) {
+                const Tin* e = reinterpret_cast<const Tin*>(&raw[s]);
 #pragma unroll
-            for (int k = 0; k < V; ++k)
-                acc[k] = combine<OP, A>(acc[k], widen<Tin>(e[k]));
+                for (int k = 0; k < V; ++k)
+                    acc[k] = s == 0 ? widen<Tin>(e[k]) : combine<OP, A>(acc[k], widen<Tin>(e[k]));
+            }
         }
         if (do_scale) {
 #pragma unroll
@@ -430,66 +431,91 @@ __device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, uint64_
     // all_reduce writes the slice back at the same element positions; reduce_scatter writes the
     // slice to the start of the local result
     const uint64_t out_byte0 = to_all ? a.out_off + (elem0 + b) * sizeof(Tout) : b * sizeof(Tout);
-    for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
-        A acc[V];
+    // U independent vectors per thread and iteration: all their loads are issued before the
+    // first use, which is what keeps enough bytes in flight to fill the links
+    constexpr int U = NVLS ? 4 : 2;
+    for (uint64_t i0 = threadIdx.x; i0 < nvec; i0 += static_cast<uint64_t>(U) * blockDim.x) {
+        A acc[U][V];
         if (NVLS) {
-            uint4 raw = mc_ld_reduce<Tin, OP>(a.mc_base + in_byte0 + i * 16);
-            const Tin* el = reinterpret_cast<const Tin*>(&raw);
+            uint4 raw[U];
 #pragma unroll
-            for (int k = 0; k < V; ++k)
-                acc[k] = widen<Tin>(el[k]);
+            for (int u = 0; u < U; ++u) {
+                const uint64_t i = i0 + static_cast<uint64_t>(u) * blockDim.x;
+                if (i < nvec)
+                    raw[u] = mc_ld_reduce<Tin, OP>(a.mc_base + in_byte0 + i * 16);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const Tin* el = reinterpret_cast<const Tin*>(&raw[u]);
+#pragma unroll
+                for (int k = 0; k < V; ++k)
+                    acc[u][k] = widen<Tin>(el[k]);
+            }
         } else {
-            uint4 raw[kMaxRanks];
+            uint4 raw[U][kMaxRanks];
 #pragma unroll
-            for (int q = 0; q < kMaxRanks; ++q)
-                if (q < n)
-                    raw[q] = ld_cg_v4(a.c.peers.heap[q] + in_byte0 + i * 16);
+            for (int u = 0; u < U; ++u) {
+                const uint64_t i = i0 + static_cast<uint64_t>(u) * blockDim.x;
 #pragma unroll
-            for (int q = 0; q < kMaxRanks; ++q) {
-                if (q < n) {
-                    const Tin* el = reinterpret_cast<const Tin*>(&raw[q]);
+                for (int q = 0; q < kMaxRanks; ++q)
+                    if (q < n && i < nvec)
+                        raw[u][q] = ld_cg_v4(a.c.peers.heap[q] + in_byte0 + i * 16);
+            }
 #pragma unroll
-                    for (int k = 0; k < V; ++k)
-                        acc[k] = q == 0 ? widen<Tin>(el[k]) : combine<OP, A>(acc[k], widen<Tin>(el[k]));
+            for (int u = 0; u < U; ++u) {
+#pragma unroll
+                for (int q = 0; q < kMaxRanks; ++q) {
+                    if (q < n) {
+                        const Tin* el = reinterpret_cast<const Tin*>(&raw[u][q]);
+#pragma unroll
+                        for (int k = 0; k < V; ++k)
+                            acc[u][k] = q == 0 ? widen<Tin>(el[k]) : combine<OP, A>(acc[u][k], widen<Tin>(el[k]));
+                    }
                 }
             }
         }
-        Tout o[V];
 #pragma unroll
-        for (int k = 0; k < V; ++k) {
-            if (do_scale)
-                acc[k] = static_cast<A>(acc[k] * static_cast<A>(a.scale));
-            o[k] = narrow<Tout, A>(acc[k]);
-        }
-        if (!to_all) {
-            char* dst = static_cast<char*>(a.out_local) + out_byte0 + i * OB;
-            if (OB >= 16) {
+        for (int u = 0; u < U; ++u) {
+            const uint64_t i = i0 + static_cast<uint64_t>(u) * blockDim.x;
+            if (i >= nvec)
+                break;
+            Tout o[V];
 #pragma unroll
-                for (int w = 0; w < OB / 16; ++w)
-                    reinterpret_cast<uint4*>(dst)[w] = reinterpret_cast<const uint4*>(o)[w];
-            } else {
-                *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
+            for (int k = 0; k < V; ++k) {
+                if (do_scale)
+                    acc[u][k] = static_cast<A>(acc[u][k] * static_cast<A>(a.scale));
+                o[k] = narrow<Tout, A>(acc[u][k]);
             }
-        } else if (NVLS) {
-            char* dst = a.mc_base + out_byte0 + i * OB;
-            if (OB >= 16) {
+            if (!to_all) {
+                char* dst = static_cast<char*>(a.out_local) + out_byte0 + i * OB;
+                if (OB >= 16) {
 #pragma unroll
-                for (int w = 0; w < OB / 16; ++w)
-                    mc_st_v4(dst + 16 * w, reinterpret_cast<const uint4*>(o)[w]);
+                    for (int w = 0; w < OB / 16; ++w)
+                        reinterpret_cast<uint4*>(dst)[w] = reinterpret_cast<const uint4*>(o)[w];
+                } else {
+                    *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
+                }
+            } else if (NVLS) {
+                char* dst = a.mc_base + out_byte0 + i * OB;
+                if (OB >= 16) {
+#pragma unroll
+                    for (int w = 0; w < OB / 16; ++w)
+                        mc_st_v4(dst + 16 * w, reinterpret_cast<const uint4*>(o)[w]);
+                } else {
+                    mc_st_v2(dst, *reinterpret_cast<const uint2*>(o));
+                }
             } else {
-                mc_st_v2(dst, *reinterpret_cast<const uint2*>(o));
-            }
-        } else {
 #pragma unroll
-            for (int q = 0; q < kMaxRanks; ++q) {
-                if (q < n) {
-                    char* dst = a.c.peers.heap[(a.c.rank + q) % n] + out_byte0 + i * OB;
-                    if (OB >= 16) {
+                for (int q = 0; q < kMaxRanks; ++q) {
+                    if (q < n) {
+                        char* dst = a.c.peers.heap[(a.c.rank + q) % n] + out_byte0 + i * OB;
+                        if (OB >= 16) {
 #pragma unroll
-                        for (int w = 0; w < OB / 16; ++w)
-                            reinterpret_cast<uint4*>(dst)[w] = reinterpret_cast<const uint4*>(o)[w];
-                    } else {
-                        *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
+                            for (int w = 0; w < OB / 16; ++w)
+                                reinterpret_cast<uint4*>(dst)[w] = reinterpret_cast<const uint4*>(o)[w];
+                        } else {
+                            *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
+                        }
                     }
                 }
             }

@@ -315,7 +315,10 @@ Status NvlCommunicator::direct_launch(int kind, const void* in, void* out, size_
     const bool nvls = m_heap.multicast() != nullptr && bytes >= m_nvls_min_bytes &&
                       (kind == mgk::coll::DIRECT_ALL_GATHER || mgk::coll::nvls_supports(in_dtype, out_dtype, op));
     a.mc_base = nvls ? m_heap.multicast() : nullptr;
-    MEGRAY_CHECK(check_cuda(mgk::coll::launch_direct(a, pick_ctas(bytes), 512, stream)));
+    // single-pass kernels are latency-bound per CTA: smaller shares, more CTAs
+    const int ctas = static_cast<int>(std::min<size_t>(std::max<size_t>(1, bytes / (32u << 10)),
+                                                       static_cast<size_t>(2 * m_max_ctas > kMaxCtas ? kMaxCtas : 2 * m_max_ctas)));
+    MEGRAY_CHECK(check_cuda(mgk::coll::launch_direct(a, ctas, 512, stream)));
     after_launch(stream);
     if (nvls)
         m_stats.algo_nvls++;

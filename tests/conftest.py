@@ -27,8 +27,9 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords and n == 0:
             item.add_marker(pytest.mark.skip(reason="no CUDA GPU"))
-        if "multigpu" in item.keywords and n < 2:
-            item.add_marker(pytest.mark.skip(reason="needs two GPUs"))
+        want = int(os.environ.get("MEGRAY_TEST_NPROC", "2"))
+        if "multigpu" in item.keywords and n < want:
+            item.add_marker(pytest.mark.skip(reason=f"needs {want} GPUs"))
 
 
 @pytest.fixture(scope="session", autouse=True)

@@ -8,7 +8,7 @@ from megray_b200.models import TPMLPConfig, TPMLPStack
 from megray_b200.ops import gemm_error_flag
 
 rank, n, dev, comm, server = setup()
-cfg = TPMLPConfig(d_model=512, ffn=1024, layers=2, tokens=1024, init_std=0.05, lr=0.0, seed=3)
+cfg = TPMLPConfig(d_model=512, ffn=1024, layers=2, tokens=max(1024, 256 * n), init_std=0.05, lr=0.0, seed=3)
 g = torch.Generator(device=dev).manual_seed(11)
 x_full = torch.randn(cfg.tokens, cfg.d_model, device=dev, generator=g).to(torch.bfloat16)
 Ts = cfg.tokens // n

@@ -14,7 +14,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 
-def torchrun(script, nproc=2, env=None, timeout=600):
+NPROC = int(os.environ.get("MEGRAY_TEST_NPROC", "2"))  # ranks (= GPUs) per test; 2, 4 or 8
+
+
+def torchrun(script, nproc=None, env=None, timeout=600):
+    nproc = nproc or NPROC
     e = dict(os.environ, NCCL_NVLS_ENABLE="0", MEGRAY_NVLS="0", MEGRAY_LOG_LEVEL="2")
     e.update(env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
@@ -26,23 +30,23 @@ def torchrun(script, nproc=2, env=None, timeout=600):
 
 def test_collectives_against_cpu_reference():
     out = torchrun("collectives.py")
-    assert out.count("RANK_OK") == 2, out[-3000:]
+    assert out.count("RANK_OK") == NPROC, out[-3000:]
 
 
 def test_tensor_parallel_model_matches_single_gpu():
     out = torchrun("tp_model.py", env={"MEGRAY_HEAP_MB": "1024"})
-    assert out.count("RANK_OK") == 2, out[-3000:]
+    assert out.count("RANK_OK") == NPROC, out[-3000:]
 
 
 def test_expert_parallel_moe_matches_single_gpu():
     out = torchrun("moe.py", env={"MEGRAY_HEAP_MB": "1024"})
-    assert out.count("RANK_OK") == 2, out[-3000:]
+    assert out.count("RANK_OK") == NPROC, out[-3000:]
 
 
 def test_single_pass_collectives_on_heap_tensors():
     out = torchrun("direct.py", env={"MEGRAY_HEAP_MB": "4096"})
     print("\n".join(l for l in out.splitlines() if l.startswith(("BW", "RANK_OK"))))
-    assert out.count("RANK_OK") == 2, out[-3000:]
+    assert out.count("RANK_OK") == NPROC, out[-3000:]
     assert "nvls_calls=0" in out
 
 
@@ -50,9 +54,9 @@ def test_single_pass_collectives_through_nvswitch_multimem():
     # falls back to peer loads/stores (with a warning) where multicast is unavailable
     out = torchrun("direct.py", env={"MEGRAY_HEAP_MB": "4096", "MEGRAY_NVLS": "1", "NCCL_NVLS_ENABLE": "1"})
     print("\n".join(l for l in out.splitlines() if l.startswith(("BW", "RANK_OK"))))
-    assert out.count("RANK_OK") == 2, out[-3000:]
+    assert out.count("RANK_OK") == NPROC, out[-3000:]
 
 
 def test_device_wait_limit_reports_timeout_and_keeps_the_gpu_usable():
     out = torchrun("timeout.py")
-    assert out.count("RANK_OK") == 2, out[-3000:]
+    assert out.count("RANK_OK") == NPROC, out[-3000:]
