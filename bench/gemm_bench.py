@@ -46,6 +46,7 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-cublas", action="store_true")
+    ap.add_argument("--epilogue", type=int, default=0, help="0 = per-lane stores, 5 = row segments through smem")
     ap.add_argument("--variant", type=int, default=0, help="0 = automatic (CTA pair), 1 = single-CTA tile")
     a = ap.parse_args()
     peak = None
@@ -72,7 +73,7 @@ def main():
         else:
             B = torch.randn((K, N) if b_mn else (N, K), device=dev).to(torch.bfloat16)
             out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-            fn = lambda: gemm(A, B, out, a_mn=a_mn, b_mn=b_mn, variant=a.variant)  # noqa: E731
+            fn = lambda: gemm(A, B, out, a_mn=a_mn, b_mn=b_mn, variant=a.variant, epilogue=a.epilogue)  # noqa: E731
             flops = 2.0 * M * N * K
         t = time_it(fn, a.warmup, a.iters)
         line = f"{layout:7s} M={M:6d} N={N:6d} K={K:6d}  ours {t:8.3f} ms {flops / t / 1e9:7.1f} TFLOP/s"

@@ -51,6 +51,7 @@ struct BenchOptions {
     std::string op = "sum";
     bool json = false;
     bool check = false;
+    bool heap = false;  // NVL backend: buffers from the symmetric heap (zero-copy / NVSwitch kernels)
 };
 
 const char* kAllFuncs[] = {"send_recv", "scatter", "gather", "all_to_all", "all_gather",
@@ -180,8 +181,23 @@ std::vector<Result> run_sizes(const BenchOptions& o, const std::string& func, Ba
             const bool wide_in = func == "reduce_scatter" || func == "scatter" || func == "all_to_all";
             const bool wide_out = func == "all_gather" || func == "gather" || func == "all_to_all";
             void *in = nullptr, *out = nullptr;
-            CK(cudaMalloc(&in, max_len * dt.size * (wide_in ? n : 1)));
-            CK(cudaMalloc(&out, max_len * dt.size * (wide_out ? n : 1)));
+            bool from_heap = false;
+#ifndef MEGRAY_BENCH_REFERENCE
+            if (o.heap && backend == MEGRAY_NVL) {
+                NvlInterface* nvl = as_nvl(comm.get());
+                in = nvl->sym_alloc(max_len * dt.size * (wide_in ? n : 1), nullptr);
+                out = nvl->sym_alloc(max_len * dt.size * (wide_out ? n : 1), nullptr);
+                from_heap = true;
+                if (in == nullptr || out == nullptr) {
+                    fprintf(stderr, "symmetric heap too small for these sizes: raise MEGRAY_HEAP_MB\n");
+                    exit(1);
+                }
+            }
+#endif
+            if (!from_heap) {
+                CK(cudaMalloc(&in, max_len * dt.size * (wide_in ? n : 1)));
+                CK(cudaMalloc(&out, max_len * dt.size * (wide_out ? n : 1)));
+            }
             CK(cudaMemset(in, r + 1, max_len * dt.size * (wide_in ? n : 1)));
             CK(cudaMemset(out, 0, max_len * dt.size * (wide_out ? n : 1)));
             cudaEvent_t e0, e1;
@@ -234,8 +250,10 @@ std::vector<Result> run_sizes(const BenchOptions& o, const std::string& func, Ba
             comm.reset();
             cudaEventDestroy(e0);
             cudaEventDestroy(e1);
-            cudaFree(in);
-            cudaFree(out);
+            if (!from_heap) {
+                cudaFree(in);
+                cudaFree(out);
+            }
             cudaStreamDestroy(stream);
         });
     }
@@ -250,7 +268,7 @@ std::vector<Result> run_sizes(const BenchOptions& o, const std::string& func, Ba
 
 void usage() {
     printf("megray_bench [-d devices] [-e nccl,nvl] [-f all_reduce,...|all] [-s 1K:1G | 8,1024,...]\n"
-           "             [-t dtype] [-o sum|max|min] [-w warmup] [-i iters] [-j] [-c]\n"
+           "             [-t dtype] [-o sum|max|min] [-w warmup] [-i iters] [-j] [-c] [-H (NVL: symmetric-heap buffers)]\n"
            "             [-I master_ip] [-P port] [-n nodes] [-r node_rank]\n");
 }
 
@@ -262,7 +280,7 @@ int main(int argc, char** argv) {
     std::string backends = "nccl";
     std::string funcs = "all";
     int c;
-    while ((c = getopt(argc, argv, "d:I:P:n:r:e:f:s:w:i:t:o:jch")) != -1) {
+    while ((c = getopt(argc, argv, "d:I:P:n:r:e:f:s:w:i:t:o:jcHh")) != -1) {
         switch (c) {
             case 'd': o.devices = atoi(optarg); break;
             case 'I': o.master_ip = optarg; break;
@@ -278,6 +296,7 @@ int main(int argc, char** argv) {
             case 'o': o.op = optarg; break;
             case 'j': o.json = true; break;
             case 'c': o.check = true; break;
+            case 'H': o.heap = true; break;
             default: usage(); return c == 'h' ? 0 : 1;
         }
     }

@@ -7,6 +7,7 @@ either through TMA without any transposition pass.  Epilogues:
 
 * ``EPI_STORE``   D = acc
 * ``EPI_ACCUM``   D += acc
+* ``EPI_STORE_ROWS`` D = acc, written as whole 128-byte row segments staged through shared memory
 * ``EPI_SWIGLU``  ``b`` = [W_gate; W_up] stacked ([2F, K]); writes G|U into ``out`` ([M, 2F]) and
                   silu(G) * U into ``out2`` ([M, F])
 * ``EPI_DSWIGLU`` acc = dH ([M, F]); reads saved G|U from ``aux`` and writes dG|dU into ``out``
@@ -23,7 +24,7 @@ import torch
 
 from .. import _lib
 
-EPI_STORE, EPI_SWIGLU, EPI_DSWIGLU, EPI_ACCUM, EPI_PUSH = 0, 1, 2, 3, 4
+EPI_STORE, EPI_SWIGLU, EPI_DSWIGLU, EPI_ACCUM, EPI_PUSH, EPI_STORE_ROWS = 0, 1, 2, 3, 4, 5
 
 _err_flags = {}
 

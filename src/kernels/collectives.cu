@@ -567,6 +567,16 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                 cta_copy(c.peers.heap[q] + a.out_off + rank * bytes + b, src + b, e - b);
             }
         }
+    } else if (a.kind == DIRECT_ALL_TO_ALL) {
+        // chunk q of the input into slot `rank` of rank q's output, starting with rank+1
+        const uint64_t bytes = a.len * sizeof(Tin);
+        const uint64_t per_cta = round_up_u64((bytes + gridDim.x - 1) / gridDim.x, 16);
+        const uint64_t b = min(bytes, per_cta * blockIdx.x), e = min(bytes, b + per_cta);
+        const char* src = static_cast<const char*>(a.in_local);
+        for (int qq = 1; qq <= n; ++qq) {
+            const int q = (rank + qq) % n;
+            cta_copy(c.peers.heap[q] + a.out_off + rank * bytes + b, src + q * bytes + b, e - b);
+        }
     } else {
         // slice `rank`: all_reduce splits len into n slices of se elements, reduce_scatter's
         // slice is the rank-th block of len elements
@@ -776,7 +786,8 @@ cudaError_t launch_direct(const DirectArgs& a, int ctas, int threads, cudaStream
     if (ctas < 1 || ctas > kMaxCtas || threads < 32 || threads > 512 || a.c.nranks < 1 ||
         a.c.nranks > kMaxRanks)
         return cudaErrorInvalidValue;
-    if (a.mc_base != nullptr && a.kind != DIRECT_ALL_GATHER && !nvls_supports(a.in_dtype, a.out_dtype, a.op))
+    if (a.mc_base != nullptr && (a.kind == DIRECT_ALL_REDUCE || a.kind == DIRECT_REDUCE_SCATTER) &&
+        !nvls_supports(a.in_dtype, a.out_dtype, a.op))
         return cudaErrorInvalidValue;
     return dispatch_types(a.in_dtype, a.out_dtype, DirectLauncher{a, ctas, threads, stream});
 }

@@ -102,14 +102,20 @@ struct ExchangeArgs {
 //                   NVLS); barrier.  Loads and stores overlap, so both link directions are busy.
 //   reduce_scatter  barrier; load slice r of all inputs, combine, store locally; barrier.
 //   all_gather      barrier; store this rank's block into slot r of all n outputs; barrier.
-enum DirectKind : int { DIRECT_ALL_REDUCE = 0, DIRECT_REDUCE_SCATTER = 1, DIRECT_ALL_GATHER = 2 };
+//   all_to_all      barrier; store chunk q of this rank's input into slot r of rank q's output; barrier.
+enum DirectKind : int {
+    DIRECT_ALL_REDUCE = 0,
+    DIRECT_REDUCE_SCATTER = 1,
+    DIRECT_ALL_GATHER = 2,
+    DIRECT_ALL_TO_ALL = 3
+};
 
 struct DirectArgs {
     CommonArgs c;
     int kind;
     uint64_t in_off;       // heap offset of the input (all_reduce, reduce_scatter)
     uint64_t out_off;      // heap offset of the output (all_reduce, all_gather)
-    const void* in_local;  // all_gather: this rank's block (any device memory)
+    const void* in_local;  // all_gather / all_to_all: this rank's input (any device memory)
     void* out_local;       // reduce_scatter: this rank's result (any device memory)
     uint64_t len;          // all_reduce: total elements; others: elements per rank
     float scale;

@@ -61,6 +61,25 @@ struct Cfg {
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
+// The push epilogue (GEMM -> reduce_scatter) stages 32 rows x 64 columns per epilogue warp in
+// shared memory so that what crosses NVLink are whole 128-byte row segments instead of one
+// 16-byte piece per lane; rows are padded to 144 bytes, which keeps both the per-row writes and
+// the per-segment reads free of bank conflicts.  The pair variant gives up one pipeline stage
+// for the room.
+constexpr int PUSH_ROW_BYTES = 64 * 2 + 16;
+constexpr int PUSH_WARP_BYTES = 32 * PUSH_ROW_BYTES;
+constexpr int PUSH_STAGING_BYTES = 4 * PUSH_WARP_BYTES;
+
+template <bool PAIR, int EPI>
+constexpr int stages_for() {
+    return (PAIR && (EPI == EPI_PUSH || EPI == EPI_STORE_ROWS)) ? 6 : Cfg<PAIR>::STAGES;
+}
+template <bool PAIR, int EPI>
+constexpr int smem_for() {
+    return stages_for<PAIR, EPI>() * Cfg<PAIR>::STAGE_BYTES + 1024 + 256 +
+           ((EPI == EPI_PUSH || EPI == EPI_STORE_ROWS) ? PUSH_STAGING_BYTES : 0);
+}
+
 struct KParams {
     int M, N, K;
     int m_blocks, n_blocks, num_tiles;
@@ -231,7 +250,59 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
 // row (0..TILE_M) of the tile this thread owns.
 template <int EPI>
 __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, uint32_t t_addr,
-                                              int row_in_tile, bool zero_tile) {
+                                              int row_base, int lane, bool zero_tile, uint8_t* stage_warp) {
+    const int row_in_tile = row_base + lane;
+    if (EPI == EPI_PUSH || EPI == EPI_STORE_ROWS) {
+        // The 32 rows of this warp all belong to one owner rank (owners hold whole row blocks).
+        const long drow0 = tl.d_row0 + row_base;
+        const int peer = EPI == EPI_PUSH ? static_cast<int>(drow0 / p.rows_per_peer) : 0;
+        const long prow0 = EPI == EPI_PUSH ? drow0 - static_cast<long>(peer) * p.rows_per_peer : drow0;
+        __nv_bfloat16* base =
+                EPI == EPI_PUSH ? static_cast<__nv_bfloat16*>(p.peer_out != nullptr ? p.peer_out[peer]
+                                                                                   : p.fuse.rs_peer_out[peer])
+                                : p.D;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+            uint32_t r0[32], r1[32];
+            if (!zero_tile) {
+                tmem_ld_32x32b_x32(t_addr + c * 64, r0);
+                tmem_ld_32x32b_x32(t_addr + c * 64 + 32, r1);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    r0[i] = r1[i] = 0u;
+            }
+            // lane = row: 64 bf16 of this row into the padded staging row
+            uint4* srow = reinterpret_cast<uint4*>(stage_warp + lane * PUSH_ROW_BYTES);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(r0[i * 8 + 0]), __uint_as_float(r0[i * 8 + 1]));
+                o.y = pack_bf16x2(__uint_as_float(r0[i * 8 + 2]), __uint_as_float(r0[i * 8 + 3]));
+                o.z = pack_bf16x2(__uint_as_float(r0[i * 8 + 4]), __uint_as_float(r0[i * 8 + 5]));
+                o.w = pack_bf16x2(__uint_as_float(r0[i * 8 + 6]), __uint_as_float(r0[i * 8 + 7]));
+                srow[i] = o;
+                o.x = pack_bf16x2(__uint_as_float(r1[i * 8 + 0]), __uint_as_float(r1[i * 8 + 1]));
+                o.y = pack_bf16x2(__uint_as_float(r1[i * 8 + 2]), __uint_as_float(r1[i * 8 + 3]));
+                o.z = pack_bf16x2(__uint_as_float(r1[i * 8 + 4]), __uint_as_float(r1[i * 8 + 5]));
+                o.w = pack_bf16x2(__uint_as_float(r1[i * 8 + 6]), __uint_as_float(r1[i * 8 + 7]));
+                srow[4 + i] = o;
+            }
+            __syncwarp();
+            // 8 lanes write one row's 128 bytes: four rows per store instruction
+            const int col = tl.n0 + c * 64 + (lane & 7) * 8;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int rr = it * 4 + (lane >> 3);
+                const uint4 v = *reinterpret_cast<const uint4*>(stage_warp + rr * PUSH_ROW_BYTES + (lane & 7) * 16);
+                if (tl.m0 + row_base + rr < p.M && col + 8 <= p.N)
+                    *reinterpret_cast<uint4*>(base + (prow0 + rr) * p.ldd + col) = v;
+            }
+            __syncwarp();
+        }
+        return;
+    }
     const int m = tl.m0 + row_in_tile;
     const bool row_ok = m < p.M;
     const long drow = tl.d_row0 + row_in_tile;
@@ -302,13 +373,6 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
             }
             store_row32(p.D + drow * p.ldd + col, u, ok);
             store_row32(p.D + drow * p.ldd + p.aux_off + col, g, ok);
-        } else if (EPI == EPI_PUSH) {
-            // output rows are sharded over GPUs: a whole m-block has one owner
-            const int peer = static_cast<int>(drow / p.rows_per_peer);
-            const long prow = drow - static_cast<long>(peer) * p.rows_per_peer;
-            __nv_bfloat16* base = static_cast<__nv_bfloat16*>(
-                    p.peer_out != nullptr ? p.peer_out[peer] : p.fuse.rs_peer_out[peer]);
-            store_row32(base + prow * p.ldd + col, v, ok);
         }
     }
 }
@@ -423,29 +487,44 @@ __device__ __forceinline__ void reduce_scatter_tail(const FuseArgs& f, uint64_t 
     const uint4* slots = static_cast<const uint4*>(f.rs_stage_local);
     const uint4* resid = static_cast<const uint4*>(f.rs_residual);
     uint4* out = static_cast<uint4*>(f.rs_out);
-    for (uint64_t i = b + threadIdx.x; i < e; i += NUM_THREADS) {
-        float acc[8];
-        {
-            const uint4 v = __ldcg(slots + i);
-            acc[0] = bf16_lo(v.x); acc[1] = bf16_hi(v.x); acc[2] = bf16_lo(v.y); acc[3] = bf16_hi(v.y);
-            acc[4] = bf16_lo(v.z); acc[5] = bf16_hi(v.z); acc[6] = bf16_lo(v.w); acc[7] = bf16_hi(v.w);
+    // two vectors per thread and iteration, all slots' loads issued before the first use
+    auto add8 = [](float (&acc)[8], const uint4& v) {
+        acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+        acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+    };
+    constexpr int U = 2;
+    for (uint64_t i0 = b + threadIdx.x; i0 < e; i0 += static_cast<uint64_t>(U) * NUM_THREADS) {
+        uint4 raw[U][8];
+        uint4 res[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint64_t i = i0 + static_cast<uint64_t>(u) * NUM_THREADS;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (q < n && i < e)
+                    raw[u][q] = __ldcg(slots + static_cast<uint64_t>(q) * nvec + i);
+            if (resid != nullptr && i < e)
+                res[u] = resid[i];
         }
-        for (int s = 1; s < n; ++s) {
-            const uint4 v = __ldcg(slots + static_cast<uint64_t>(s) * nvec + i);
-            acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
-            acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint64_t i = i0 + static_cast<uint64_t>(u) * NUM_THREADS;
+            if (i >= e)
+                break;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (q < n)
+                    add8(acc, raw[u][q]);
+            if (resid != nullptr)
+                add8(acc, res[u]);
+            uint4 o;
+            o.x = pack_bf16x2(acc[0], acc[1]);
+            o.y = pack_bf16x2(acc[2], acc[3]);
+            o.z = pack_bf16x2(acc[4], acc[5]);
+            o.w = pack_bf16x2(acc[6], acc[7]);
+            out[i] = o;
         }
-        if (resid != nullptr) {
-            const uint4 v = resid[i];
-            acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
-            acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
-        }
-        uint4 o;
-        o.x = pack_bf16x2(acc[0], acc[1]);
-        o.y = pack_bf16x2(acc[2], acc[3]);
-        o.z = pack_bf16x2(acc[4], acc[5]);
-        o.w = pack_bf16x2(acc[6], acc[7]);
-        out[i] = o;
     }
 }
 
@@ -454,7 +533,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
                          const __grid_constant__ CUtensorMap tma_b, const KParams p) {
     using C = Cfg<PAIR>;
-    constexpr int STAGES = C::STAGES;
+    constexpr int STAGES = stages_for<PAIR, EPI>();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
@@ -465,6 +544,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* comm_ok = reinterpret_cast<volatile int*>(tmem_slot + 2);
+    uint8_t* push_staging = smem + STAGES * C::STAGE_BYTES + 256;  // EPI_PUSH only
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const int lane = threadIdx.x & 31;
@@ -691,7 +771,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 tc_fence_after();
             }
             const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-            epilogue_tile<EPI>(p, tl, t_addr, static_cast<int>(crank) * BM + q * 32 + lane, zero_tile);
+            epilogue_tile<EPI>(p, tl, t_addr, static_cast<int>(crank) * BM + q * 32, lane, zero_tile,
+                               push_staging + q * PUSH_WARP_BYTES);
             if (!zero_tile) {
                 tc_fence_before();
                 __syncwarp();
@@ -793,7 +874,7 @@ template <bool PAIR, bool A_MN, bool B_MN, int EPI>
 cudaError_t launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const KParams& kp, int workers,
                      cudaStream_t stream) {
     auto kern = gemm_bf16_kernel<PAIR, A_MN, B_MN, EPI>;
-    constexpr int smem = Cfg<PAIR>::SMEM_BYTES;
+    constexpr int smem = smem_for<PAIR, EPI>();
     int dev = 0;
     cudaGetDevice(&dev);
     static std::mutex mu;
@@ -866,6 +947,8 @@ cudaError_t launch_e(int epi, const CUtensorMap& ma, const CUtensorMap& mb, cons
             return launch_t<PAIR, A_MN, B_MN, EPI_ACCUM>(ma, mb, kp, workers, stream);
         case EPI_PUSH:
             return launch_t<PAIR, A_MN, B_MN, EPI_PUSH>(ma, mb, kp, workers, stream);
+        case EPI_STORE_ROWS:
+            return launch_t<PAIR, A_MN, B_MN, EPI_STORE_ROWS>(ma, mb, kp, workers, stream);
         case EPI_DSWIGLU:
             return launch_t<PAIR, A_MN, B_MN, EPI_DSWIGLU>(ma, mb, kp, workers, stream);
         case EPI_SWIGLU:
@@ -966,6 +1049,8 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
         return cudaErrorInvalidValue;
     if (a.epilogue == EPI_PUSH &&
         ((a.peer_out == nullptr && a.fuse.rs_peer_out[0] == nullptr) || (kp.rows_per_peer % tile_m)))
+        return cudaErrorInvalidValue;
+    if ((a.epilogue == EPI_PUSH || a.epilogue == EPI_STORE_ROWS) && (a.N % 8))
         return cudaErrorInvalidValue;
     if (a.a_ready != nullptr && (kp.rows_per_flag % BM))
         return cudaErrorInvalidValue;

@@ -20,6 +20,7 @@ enum Epilogue : int {
     EPI_DSWIGLU = 2,  // acc = dH; reads G,U from aux, writes dG,dU into D (cols n, n+aux_off)
     EPI_ACCUM = 3,    // D = acc + D (bf16 read-modify-write; used for gradient accumulation)
     EPI_PUSH = 4,     // D row blocks live on different GPUs: row r goes to peer_out[r / rows_per_peer]
+    EPI_STORE_ROWS = 5,  // D = acc, written as whole 128-byte row segments through shared memory
 };
 
 // One m-block of a grouped (per-expert) problem.

@@ -299,7 +299,7 @@ Status NvlCommunicator::direct_launch(int kind, const void* in, void* out, size_
     a.out_dtype = out_dtype;
     a.op = op;
     size_t bytes = len * get_dtype_size(in_dtype);
-    if (kind == mgk::coll::DIRECT_ALL_GATHER) {
+    if (kind == mgk::coll::DIRECT_ALL_GATHER || kind == mgk::coll::DIRECT_ALL_TO_ALL) {
         a.in_local = in;
         a.out_off = static_cast<size_t>(static_cast<char*>(out) - m_heap.local());
         bytes *= m_nranks;
@@ -313,6 +313,7 @@ Status NvlCommunicator::direct_launch(int kind, const void* in, void* out, size_
         }
     }
     const bool nvls = m_heap.multicast() != nullptr && bytes >= m_nvls_min_bytes &&
+                      kind != mgk::coll::DIRECT_ALL_TO_ALL &&
                       (kind == mgk::coll::DIRECT_ALL_GATHER || mgk::coll::nvls_supports(in_dtype, out_dtype, op));
     a.mc_base = nvls ? m_heap.multicast() : nullptr;
     // single-pass kernels are latency-bound per CTA: smaller shares, more CTAs
@@ -530,6 +531,10 @@ Status NvlCommunicator::all_to_all(const void* sendbuff, void* recvbuff, size_t 
     m_stats.bytes += bytes;
     if (bytes == 0)
         return MEGRAY_OK;
+    if (m_direct && m_nranks > 1 && bytes > m_oneshot_bytes / m_nranks && aligned_heap(recvbuff, bytes * m_nranks) &&
+        bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(sendbuff) & 15) == 0)
+        return direct_launch(mgk::coll::DIRECT_ALL_TO_ALL, sendbuff, recvbuff, bytes, MEGRAY_UINT8, MEGRAY_UINT8, 1.0f,
+                             MEGRAY_SUM, stream);
     const size_t cap = round_down(m_ws_bytes / m_nranks - 16, 16);
     for (size_t off = 0; off < bytes; off += cap) {
         const size_t piece = std::min(cap, bytes - off);

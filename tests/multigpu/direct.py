@@ -59,6 +59,8 @@ for dtype in (torch.bfloat16, torch.float32, torch.float16, torch.int32):
         g = comm.sym_empty((m * n,), dtype)
         comm.all_gather(xs[rank][:m].to(dev), g)
         check(f"all_gather {dtype} {numel}", g, torch.cat([t[:m] for t in xs]))
+        comm.all_to_all(xs[rank][: m * n].to(dev), g)  # receive buffer in the heap: direct stores
+        check(f"all_to_all {dtype} {numel}", g, torch.cat([xs[q][rank * m:(rank + 1) * m] for q in range(n)]))
 
 # gradient-bucket path: bf16 in, fp32 out, 1/n scale, heap resident
 xs = [data(r, 2_000_000, torch.bfloat16, 9) for r in range(n)]

@@ -57,6 +57,18 @@ def test_many_tiles_per_cta_pair_exercise_the_ring_and_both_accumulators():
     close(out[idx], a[idx].float() @ b.float().t(), tol=3e-2)
 
 
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("M,N,K", [(300, 264, 200), (1024, 2048, 512), (129, 8, 64)])
+def test_row_segment_store_epilogue(M, N, K, variant):
+    from megray_b200.ops import EPI_STORE_ROWS, gemm
+
+    torch.manual_seed(8)
+    a, b = mk(M, K), mk(N, K)
+    out = torch.full((M, N), 3.0, device="cuda", dtype=torch.bfloat16)
+    gemm(a, b, out, epilogue=EPI_STORE_ROWS, variant=variant)
+    close(out, a.float() @ b.float().t())
+
+
 def test_accumulate():
     from megray_b200.ops import EPI_ACCUM, gemm
 
