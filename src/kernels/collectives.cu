@@ -75,7 +75,17 @@ __device__ __forceinline__ void cta_copy(char* dst, const char* src, uint64_t nb
         const uint4* s4 = reinterpret_cast<const uint4*>(src + head);
         uint4* d4 = reinterpret_cast<uint4*>(dst + head);
         uint64_t i = tid;
-        // four independent 16-byte loads in flight per thread
+        // eight, then four, independent 16-byte loads in flight per thread: a peer load takes a
+        // few microseconds, and the link only fills with megabytes in flight
+        for (; i + 7ull * nth < body; i += 8ull * nth) {
+            uint4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                v[u] = __ldcg(s4 + i + static_cast<uint64_t>(u) * nth);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                d4[i + static_cast<uint64_t>(u) * nth] = v[u];
+        }
         for (; i + 3ull * nth < body; i += 4ull * nth) {
             uint4 a = __ldcg(s4 + i), b = __ldcg(s4 + i + nth), c2 = __ldcg(s4 + i + 2ull * nth),
                   d = __ldcg(s4 + i + 3ull * nth);
