@@ -5,8 +5,10 @@
     python bench/gemm_bench.py --m 8192 --n 8192 --k 8192 --layout nt --iters 1 --no-cublas
                                                    # a single small case (for an ncu capture)
 
-CUDA events on the launching stream, best of --iters after --warmup launches; operands
-are larger than L2 for the default shapes.  Reports TFLOP/s and the fraction of the measured
+CUDA events on the launching stream around each launch.  All candidates of a case (each
+variant asked for, then cuBLAS) are launched in turn, --iters rounds after --warmup rounds, and
+the median per candidate is reported, so that a drift of the power-capped clock during the case
+hits every candidate alike.  Operands are larger than L2 for the default shapes.  Reports TFLOP/s and the fraction of the measured
 cuBLAS peak in MEASURED_PEAKS.json when that file is present.
 """
 import argparse
@@ -22,19 +24,22 @@ import torch  # noqa: E402
 from megray_b200.ops import EPI_SWIGLU, gemm  # noqa: E402
 
 
-def time_it(fn, warmup, iters):
+def time_round_robin(fns, warmup, iters):
+    """Median milliseconds per candidate, candidates launched in turn."""
     for _ in range(warmup):
-        fn()
+        for fn in fns:
+            fn()
     torch.cuda.synchronize()
-    best = 1e30
+    times = [[] for _ in fns]
     for _ in range(iters):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        fn()
-        e1.record()
-        torch.cuda.synchronize()
-        best = min(best, e0.elapsed_time(e1))
-    return best
+        for i, fn in enumerate(fns):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times[i].append(e0.elapsed_time(e1))
+    return [sorted(t)[len(t) // 2] for t in times]
 
 
 def main():
@@ -47,8 +52,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-cublas", action="store_true")
     ap.add_argument("--epilogue", type=int, default=0, help="0 = per-lane stores, 5 = row segments through smem")
-    ap.add_argument("--variant", type=int, default=0, help="0 = automatic (CTA pair), 1 = single-CTA tile")
+    ap.add_argument("--variant", type=int, default=0, help="0 = automatic, 1 = single-CTA 128x256 tile, 2 = CTA-pair 256x256 tile, 3 = CTA-pair 512x256 tile")
+    ap.add_argument("--variants", default="", help="comma-separated variants to time one after the other on each case")
     a = ap.parse_args()
+    variants = [int(v) for v in a.variants.split(",")] if a.variants else [a.variant]
     peak = None
     pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(pk):
@@ -68,26 +75,29 @@ def main():
             B = torch.randn(2 * N, K, device=dev).to(torch.bfloat16) * 0.02
             out = torch.empty(M, 2 * N, device=dev, dtype=torch.bfloat16)
             out2 = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-            fn = lambda: gemm(A, B, out, epilogue=EPI_SWIGLU, out2=out2, n=N, variant=a.variant)  # noqa: E731
+            fn = lambda v: gemm(A, B, out, epilogue=EPI_SWIGLU, out2=out2, n=N, variant=v)  # noqa: E731
             flops = 2.0 * M * 2 * N * K
         else:
             B = torch.randn((K, N) if b_mn else (N, K), device=dev).to(torch.bfloat16)
             out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-            fn = lambda: gemm(A, B, out, a_mn=a_mn, b_mn=b_mn, variant=a.variant, epilogue=a.epilogue)  # noqa: E731
+            fn = lambda v: gemm(A, B, out, a_mn=a_mn, b_mn=b_mn, variant=v, epilogue=a.epilogue)  # noqa: E731
             flops = 2.0 * M * N * K
-        t = time_it(fn, a.warmup, a.iters)
-        line = f"{layout:7s} M={M:6d} N={N:6d} K={K:6d}  ours {t:8.3f} ms {flops / t / 1e9:7.1f} TFLOP/s"
-        if peak:
-            line += f" ({flops / t / 1e9 / peak:.2f} of measured {peak:.0f})"
+        cands = [(lambda v=v: fn(v)) for v in variants]
         if not a.no_cublas:
             Af = A.t() if a_mn else A
             Bf = B if b_mn else B.t()
-            if layout == "swiglu":
-                ref_out = torch.empty(M, 2 * N, device=dev, dtype=torch.bfloat16)
-            else:
-                ref_out = out
-            t2 = time_it(lambda: torch.matmul(Af, Bf, out=ref_out), a.warmup, a.iters)
-            line += f" | cuBLAS {t2:8.3f} ms {flops / t2 / 1e9:7.1f} TFLOP/s | ours/cuBLAS {t2 / t:.3f}"
+            ref_out = torch.empty(M, 2 * N, device=dev, dtype=torch.bfloat16) if layout == "swiglu" else out
+            cands.append(lambda: torch.matmul(Af, Bf, out=ref_out))
+        ts = time_round_robin(cands, a.warmup, a.iters)
+        line = f"{layout:7s} M={M:6d} N={N:6d} K={K:6d} "
+        for v, t in zip(variants, ts):
+            line += f" ours{'' if len(variants) == 1 else f'[v{v}]'} {t:8.3f} ms {flops / t / 1e9:7.1f} TFLOP/s"
+            if peak:
+                line += f" ({flops / t / 1e9 / peak:.2f} of measured {peak:.0f})"
+        if not a.no_cublas:
+            t2 = ts[-1]
+            line += f" | cuBLAS {t2:8.3f} ms {flops / t2 / 1e9:7.1f} TFLOP/s | ours/cuBLAS " + \
+                    "/".join(f"{t2 / t:.3f}" for t in ts[:-1])
         print(line, flush=True)
         del A, B, out
 

@@ -27,7 +27,7 @@ typedef struct {
     int aux_off;
     int m_rot;
     int sm_limit;
-    int variant;     /* 0 automatic, 1 force the single-CTA tile */
+    int variant;     /* 0 automatic, 1 single-CTA 128x256 tile, 2 CTA-pair 256x256 tile, 3 CTA-pair 512x256 tile */
     const uint32_t* a_ready;
     int rows_per_flag;
     uint32_t a_ready_target;

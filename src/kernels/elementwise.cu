@@ -62,14 +62,45 @@ __global__ void __launch_bounds__(256) sgd_bf16_kernel(uint4* __restrict__ w, co
 __global__ void __launch_bounds__(256) mse_bf16_kernel(const __nv_bfloat16* __restrict__ y,
                                                        const __nv_bfloat16* __restrict__ t,
                                                        __nv_bfloat16* __restrict__ dy, float* loss, uint64_t n,
-                                                       float scale) {
+                                                       float scale, int vec_ok) {
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    const uint64_t tid = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     float acc = 0.f;
-    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const float d = __bfloat162float(y[i]) - (t != nullptr ? __bfloat162float(t[i]) : 0.f);
+    // 16-byte body (two vectors in flight per thread), scalar tail
+    const uint64_t nvec = vec_ok ? n / 8 : 0;
+    const uint4* yv = reinterpret_cast<const uint4*>(y);
+    const uint4* tv = reinterpret_cast<const uint4*>(t);
+    uint4* dv = reinterpret_cast<uint4*>(dy);
+    auto one = [&](const uint4& a, const uint4& b, uint64_t i) {
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+        const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float d0 = lo(aw[k]) - lo(bw[k]);
+            const float d1 = hi(aw[k]) - hi(bw[k]);
+            acc += d0 * d0 + d1 * d1;
+            ow[k] = pack(2.f * d0 * scale, 2.f * d1 * scale);
+        }
+        if (dy != nullptr)
+            dv[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    };
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    uint64_t i = tid;
+    for (; i + stride < nvec; i += 2 * stride) {
+        const uint4 a0 = __ldcs(yv + i), a1 = __ldcs(yv + i + stride);
+        const uint4 b0 = t != nullptr ? __ldcs(tv + i) : zero;
+        const uint4 b1 = t != nullptr ? __ldcs(tv + i + stride) : zero;
+        one(a0, b0, i);
+        one(a1, b1, i + stride);
+    }
+    if (i < nvec)
+        one(__ldcs(yv + i), t != nullptr ? __ldcs(tv + i) : zero, i);
+    for (uint64_t k = nvec * 8 + tid; k < n; k += stride) {
+        const float d = __bfloat162float(y[k]) - (t != nullptr ? __bfloat162float(t[k]) : 0.f);
         acc += d * d;
         if (dy != nullptr)
-            dy[i] = __float2bfloat16_rn(2.f * d * scale);
+            dy[k] = __float2bfloat16_rn(2.f * d * scale);
     }
     for (int o = 16; o > 0; o >>= 1)
         acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -115,7 +146,10 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
     return v;
 }
 
-__global__ void __launch_bounds__(kNormThreads)
+// NV = 16-byte vectors per thread; the row stays in registers as packed bf16 (4 registers per
+// vector), which keeps several CTAs resident per SM.
+template <int NV>
+__global__ void __launch_bounds__(kNormThreads, NV <= 4 ? 4 : 2)
         add_rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ y, uint4* __restrict__ x_out,
                            uint4* __restrict__ n_out, float* __restrict__ inv_rms, int cols, float eps) {
     __shared__ float red[kNormThreads / 32];
@@ -123,29 +157,38 @@ __global__ void __launch_bounds__(kNormThreads)
     const size_t row = blockIdx.x;
     const uint4* xr = x + row * nvec;
     const uint4* yr = y != nullptr ? y + row * nvec : nullptr;
-    float s[kNormMaxVec][8];
-    float ss = 0.f;
+    uint4 xs[NV], ys[NV];
 #pragma unroll
-    for (int v = 0; v < kNormMaxVec; ++v) {
+    for (int v = 0; v < NV; ++v) {
         const int i = threadIdx.x + v * kNormThreads;
         if (i < nvec) {
-            unpack8(xr[i], s[v]);
+            xs[v] = xr[i];
+            if (yr != nullptr)
+                ys[v] = __ldcs(yr + i);
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = threadIdx.x + v * kNormThreads;
+        if (i < nvec) {
+            float s[8];
+            unpack8(xs[v], s);
             if (yr != nullptr) {
                 float t[8];
-                unpack8(__ldcs(yr + i), t);
+                unpack8(ys[v], t);
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
-                    s[v][k] += t[k];
-            }
-            if (x_out != nullptr) {
+                    s[k] += t[k];
                 // the sum is rounded to bf16 where it is stored; normalise what was stored
-                const uint4 st = pack8(s[v]);
-                x_out[row * nvec + i] = st;
-                unpack8(st, s[v]);
+                xs[v] = pack8(s);
+                unpack8(xs[v], s);
             }
+            if (x_out != nullptr)
+                x_out[row * nvec + i] = xs[v];
 #pragma unroll
             for (int k = 0; k < 8; ++k)
-                ss += s[v][k] * s[v][k];
+                ss += s[k] * s[k];
         }
     }
     if (n_out == nullptr && inv_rms == nullptr)
@@ -156,51 +199,66 @@ __global__ void __launch_bounds__(kNormThreads)
         inv_rms[row] = r;
     if (n_out != nullptr) {
 #pragma unroll
-        for (int v = 0; v < kNormMaxVec; ++v) {
+        for (int v = 0; v < NV; ++v) {
             const int i = threadIdx.x + v * kNormThreads;
             if (i < nvec) {
                 float o[8];
+                unpack8(xs[v], o);
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
-                    o[k] = s[v][k] * r;
+                    o[k] *= r;
                 n_out[row * nvec + i] = pack8(o);
             }
         }
     }
 }
 
-__global__ void __launch_bounds__(kNormThreads)
+template <int NV>
+__global__ void __launch_bounds__(kNormThreads, NV <= 4 ? 4 : 2)
         rmsnorm_bwd_kernel(const uint4* __restrict__ dn, const uint4* __restrict__ n, const float* __restrict__ inv_rms,
                            const uint4* __restrict__ dres, uint4* __restrict__ dx, int cols) {
     __shared__ float red[kNormThreads / 32];
     const int nvec = cols / 8;
     const size_t row = blockIdx.x;
-    float g[kNormMaxVec][8], nn[kNormMaxVec][8];
-    float dot = 0.f;
+    uint4 gs[NV], ns[NV], ds[NV];
 #pragma unroll
-    for (int v = 0; v < kNormMaxVec; ++v) {
+    for (int v = 0; v < NV; ++v) {
         const int i = threadIdx.x + v * kNormThreads;
         if (i < nvec) {
-            unpack8(__ldcs(dn + row * nvec + i), g[v]);
-            unpack8(n[row * nvec + i], nn[v]);
+            gs[v] = __ldcs(dn + row * nvec + i);
+            ns[v] = __ldcs(n + row * nvec + i);
+            if (dres != nullptr)
+                ds[v] = __ldcs(dres + row * nvec + i);
+        }
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const int i = threadIdx.x + v * kNormThreads;
+        if (i < nvec) {
+            float g[8], nn[8];
+            unpack8(gs[v], g);
+            unpack8(ns[v], nn);
 #pragma unroll
             for (int k = 0; k < 8; ++k)
-                dot += g[v][k] * nn[v][k];
+                dot += g[k] * nn[k];
         }
     }
     const float mean = block_sum(dot, red) / static_cast<float>(cols);
     const float r = inv_rms[row];
 #pragma unroll
-    for (int v = 0; v < kNormMaxVec; ++v) {
+    for (int v = 0; v < NV; ++v) {
         const int i = threadIdx.x + v * kNormThreads;
         if (i < nvec) {
-            float o[8];
+            float g[8], nn[8], o[8];
+            unpack8(gs[v], g);
+            unpack8(ns[v], nn);
 #pragma unroll
             for (int k = 0; k < 8; ++k)
-                o[k] = r * (g[v][k] - nn[v][k] * mean);
+                o[k] = r * (g[k] - nn[k] * mean);
             if (dres != nullptr) {
                 float d[8];
-                unpack8(__ldcs(dres + row * nvec + i), d);
+                unpack8(ds[v], d);
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
                     o[k] += d[k];
@@ -208,6 +266,12 @@ __global__ void __launch_bounds__(kNormThreads)
             dx[row * nvec + i] = pack8(o);
         }
     }
+}
+
+// Smallest vectors-per-thread count that covers the row.
+inline int norm_nv(int cols) {
+    const int need = (cols / 8 + kNormThreads - 1) / kNormThreads;
+    return need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
 }
 
 }  // namespace
@@ -242,9 +306,11 @@ cudaError_t launch_mse_bf16(const void* y, const void* target, void* dy, float* 
     uint64_t blocks = (n + 256 * 8 - 1) / (256 * 8);
     if (blocks > 148 * 8)
         blocks = 148 * 8;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(target) |
+                           reinterpret_cast<uintptr_t>(dy);
     mse_bf16_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
             static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(target),
-            static_cast<__nv_bfloat16*>(dy), loss_out, n, scale);
+            static_cast<__nv_bfloat16*>(dy), loss_out, n, scale, (bits & 15) == 0 ? 1 : 0);
     count_launch();
     return cudaGetLastError();
 }
@@ -255,9 +321,17 @@ cudaError_t launch_add_rmsnorm_bf16(const void* x, const void* y, void* x_out, v
         return cudaSuccess;
     if (cols <= 0 || cols % 8 || cols > kNormThreads * kNormMaxVec * 8)
         return cudaErrorInvalidValue;
-    add_rmsnorm_kernel<<<rows, kNormThreads, 0, stream>>>(
-            static_cast<const uint4*>(x), static_cast<const uint4*>(y), static_cast<uint4*>(x_out),
-            static_cast<uint4*>(n_out), inv_rms, cols, eps);
+    auto go = [&](auto kernel) {
+        kernel<<<rows, kNormThreads, 0, stream>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(y),
+                                                  static_cast<uint4*>(x_out), static_cast<uint4*>(n_out), inv_rms,
+                                                  cols, eps);
+    };
+    switch (norm_nv(cols)) {
+        case 1: go(add_rmsnorm_kernel<1>); break;
+        case 2: go(add_rmsnorm_kernel<2>); break;
+        case 4: go(add_rmsnorm_kernel<4>); break;
+        default: go(add_rmsnorm_kernel<8>); break;
+    }
     count_launch();
     return cudaGetLastError();
 }
@@ -268,9 +342,17 @@ cudaError_t launch_rmsnorm_bwd_bf16(const void* dn, const void* n, const float* 
         return cudaSuccess;
     if (cols <= 0 || cols % 8 || cols > kNormThreads * kNormMaxVec * 8)
         return cudaErrorInvalidValue;
-    rmsnorm_bwd_kernel<<<rows, kNormThreads, 0, stream>>>(
-            static_cast<const uint4*>(dn), static_cast<const uint4*>(n), inv_rms,
-            static_cast<const uint4*>(dres), static_cast<uint4*>(dx), cols);
+    auto go = [&](auto kernel) {
+        kernel<<<rows, kNormThreads, 0, stream>>>(static_cast<const uint4*>(dn), static_cast<const uint4*>(n),
+                                                  inv_rms, static_cast<const uint4*>(dres),
+                                                  static_cast<uint4*>(dx), cols);
+    };
+    switch (norm_nv(cols)) {
+        case 1: go(rmsnorm_bwd_kernel<1>); break;
+        case 2: go(rmsnorm_bwd_kernel<2>); break;
+        case 4: go(rmsnorm_bwd_kernel<4>); break;
+        default: go(rmsnorm_bwd_kernel<8>); break;
+    }
     count_launch();
     return cudaGetLastError();
 }

@@ -4,7 +4,7 @@
 //   warp 1      : UMMA issuer    (tcgen05.mma, accumulators in TMEM)
 //   warps 2..5  : epilogue       (tcgen05.ld TMEM -> registers -> fused epilogue -> global)
 //
-// Two variants of one kernel template:
+// Three variants of one kernel template:
 //   single : one CTA per tile, tile 128 x 256 x 64, tcgen05.mma.cta_group::1 (M = 128),
 //            4-stage ring of 48 KB.  Used for grouped (per-expert) row blocks.
 //   pair   : a cluster of two CTAs per 256 x 256 tile, tcgen05.mma.cta_group::2 (M = 256)
@@ -13,10 +13,15 @@
 //            of 32 KB per CTA.  Each CTA issues its own TMA loads (no multicast); their
 //            byte counts complete on the leader's barrier, and the leader's commits free
 //            the stage in both CTAs.
-// Both keep two TMEM accumulators (2 x 256 columns) so the epilogue of tile i overlaps
-// the main loop of tile i+1.  Every wait is bounded: a wait that runs out sets the
-// kernel's error word, all roles leave their loops, TMEM is freed and the kernel
-// returns normally.
+//   wide   : a CTA pair per 512 x 256 tile: two 256-row sub-tiles of A against one B tile,
+//            each with its own 256-column accumulator, so every staged byte of B feeds twice
+//            the math (0.75 of the pair variant's L2 -> shared-memory traffic per FLOP).
+//            4-stage ring of 48 KB per CTA.
+// single and pair keep two TMEM accumulators (2 x 256 columns) so the epilogue of tile i
+// overlaps the main loop of tile i+1; wide uses all 512 columns for one tile and restarts
+// the main loop on each sub-tile's accumulator as soon as the epilogue has drained it.
+// Every wait is bounded: a wait that runs out sets the kernel's error word, all roles
+// leave their loops, TMEM is freed and the kernel returns normally.
 //
 // The reference library (MegRay) contains no GEMM; this kernel exists for the
 // fused tensor-parallel and expert-parallel entry points.
@@ -27,6 +32,7 @@
 #include <cuda_bf16.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -49,16 +55,21 @@ constexpr int TMEM_COLS = 512;
 constexpr int NUM_THREADS = 320;   // producer, MMA, 4 epilogue warps, 4 communication warps
 constexpr int COMM_THREADS = 128;
 constexpr int MN_CHUNK_BYTES = 64 * BK * 2;  // one 64(mn) x 64(k) box of an MN-major operand
-constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
+constexpr int A_SUB_BYTES = BM * BK * 2;     // 16 KB: one CTA's 128 rows of one sub-tile of A
 
-template <bool PAIR>
+constexpr int MODE_SINGLE = 0, MODE_PAIR = 1, MODE_WIDE = 2;
+
+template <int MODE>
 struct Cfg {
-    static constexpr int TILE_M = PAIR ? 256 : 128;
+    static constexpr bool PAIR = MODE != MODE_SINGLE;
+    static constexpr int MSUB = MODE == MODE_WIDE ? 2 : 1;  // 256-row sub-tiles (accumulators) per tile
+    static constexpr int ACCS = MODE == MODE_WIDE ? 1 : 2;  // tiles whose accumulators fit in TMEM
+    static constexpr int TILE_M = MODE == MODE_SINGLE ? 128 : 256 * MSUB;
     static constexpr int B_ROWS = PAIR ? 128 : 256;  // rows of B staged by one CTA
+    static constexpr int A_STAGE_BYTES = MSUB * A_SUB_BYTES;
     static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-    static constexpr int STAGES = PAIR ? 7 : 4;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+    static constexpr int STAGES = MODE == MODE_PAIR ? 6 : 4;  // 192 KB of operand stages in every variant
 };
 
 // The push epilogue (GEMM -> reduce_scatter) stages 32 rows x 64 columns per epilogue warp in
@@ -70,14 +81,22 @@ constexpr int PUSH_ROW_BYTES = 64 * 2 + 16;
 constexpr int PUSH_WARP_BYTES = 32 * PUSH_ROW_BYTES;
 constexpr int PUSH_STAGING_BYTES = 4 * PUSH_WARP_BYTES;
 
-template <bool PAIR, int EPI>
-constexpr int stages_for() {
-    return (PAIR && (EPI == EPI_PUSH || EPI == EPI_STORE_ROWS)) ? 6 : Cfg<PAIR>::STAGES;
+// The other epilogues leave through TMA stores from 2 KB staging boxes: 16 boxes, two per warp
+// when both groups of epilogue warps work (wide variant), four per warp otherwise.
+constexpr int OUT_STAGING_BYTES = 16 * 2048;
+
+template <int EPI>
+constexpr int staging_for() {
+    return (EPI == EPI_PUSH || EPI == EPI_STORE_ROWS) ? PUSH_STAGING_BYTES : OUT_STAGING_BYTES;
 }
-template <bool PAIR, int EPI>
+template <int MODE, int EPI>
+constexpr int stages_for() {
+    return Cfg<MODE>::STAGES;
+}
+template <int MODE, int EPI>
 constexpr int smem_for() {
-    return stages_for<PAIR, EPI>() * Cfg<PAIR>::STAGE_BYTES + 1024 + 256 +
-           ((EPI == EPI_PUSH || EPI == EPI_STORE_ROWS) ? PUSH_STAGING_BYTES : 0);
+    return stages_for<MODE, EPI>() * Cfg<MODE>::STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ +
+           staging_for<EPI>();
 }
 
 struct KParams {
@@ -166,26 +185,6 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
-// Store 32 consecutive fp32 values of one row as bf16.
-__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const float (&v)[32], int ncols_ok) {
-    if (ncols_ok >= 32) {
-        uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint4 o;
-            o.x = pack_bf16x2(v[i * 8 + 0], v[i * 8 + 1]);
-            o.y = pack_bf16x2(v[i * 8 + 2], v[i * 8 + 3]);
-            o.z = pack_bf16x2(v[i * 8 + 4], v[i * 8 + 5]);
-            o.w = pack_bf16x2(v[i * 8 + 6], v[i * 8 + 7]);
-            d4[i] = o;
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-            if (i < ncols_ok)
-                dst[i] = __float2bfloat16_rn(v[i]);
-    }
-}
 __device__ __forceinline__ void load_row32(const __nv_bfloat16* src, float (&v)[32], int ncols_ok) {
     if (ncols_ok >= 32) {
         const uint4* s4 = reinterpret_cast<const uint4*>(src);
@@ -246,49 +245,99 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
 }
 
 // ---------------------------------------------------------------- epilogue of one tile
-// `t_addr`: TMEM address of this warp's lane quarter of the accumulator; `row_in_tile`: the
-// row (0..TILE_M) of the tile this thread owns.
+// `t_addr`: TMEM address of this warp's lane quarter of the accumulator; `row_base`: the first
+// of the warp's 32 rows inside the tile.  TMEM loads run one chunk ahead of the arithmetic and
+// the stores (two register sets in turn), so their latency is hidden behind the previous chunk.
+__device__ __forceinline__ void pack_row32(const uint32_t (&r)[32], uint4* dst) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint4 o;
+        o.x = pack_bf16x2(__uint_as_float(r[i * 8 + 0]), __uint_as_float(r[i * 8 + 1]));
+        o.y = pack_bf16x2(__uint_as_float(r[i * 8 + 2]), __uint_as_float(r[i * 8 + 3]));
+        o.z = pack_bf16x2(__uint_as_float(r[i * 8 + 4]), __uint_as_float(r[i * 8 + 5]));
+        o.w = pack_bf16x2(__uint_as_float(r[i * 8 + 6]), __uint_as_float(r[i * 8 + 7]));
+        dst[i] = o;
+    }
+}
+
+// One epilogue warp's way out to global memory for the TMA-store epilogues: a ring of 2 KB
+// staging boxes (32 rows x 32 bf16, 64-byte swizzle) and the output tensor maps.  Lane 0 issues
+// every store of the warp, so its bulk groups count them.
+struct OutRing {
+    uint8_t* base;
+    int nslots;  // 2 or 4
+    int slot;
+    const CUtensorMap* map_d;   // D, columns [0, N)
+    const CUtensorMap* map_du;  // D + aux_off, columns [0, N): the second half of a gate/up pair
+    const CUtensorMap* map_d2;  // D2
+};
+constexpr int OUT_BOX_BYTES = 32 * 32 * 2;
+
+// Stores the warp's 32 rows x 32 columns (lane = row, 16 packed pairs) at (row, col) of `map`;
+// the tensor map clips what lies past the matrix.
+__device__ __forceinline__ void emit_box32(const CUtensorMap* map, OutRing& ring, int lane, int col, int row,
+                                           const uint32_t (&pk)[16]) {
+    // the store that last used this box has read it
+    if (lane == 0) {
+        if (ring.nslots == 2)
+            tma_store_wait_read<1>();
+        else
+            tma_store_wait_read<3>();
+    }
+    __syncwarp();
+    uint8_t* buf = ring.base + ring.slot * OUT_BOX_BYTES;
+    const int sw = (lane >> 1) & 3;  // 64-byte swizzle: 16-byte piece index ^ address bits 7..8
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint4*>(buf + lane * 64 + ((j ^ sw) << 4)) =
+                make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+        tma_store_2d(map, smem_u32(buf), col, row);
+        tma_store_commit();
+    }
+    ring.slot = ring.slot + 1 == ring.nslots ? 0 : ring.slot + 1;
+}
+
 template <int EPI>
 __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, uint32_t t_addr,
-                                              int row_base, int lane, bool zero_tile, uint8_t* stage_warp) {
+                                              int row_base, int lane, bool zero_tile, uint8_t* stage_warp,
+                                              OutRing& out) {
     const int row_in_tile = row_base + lane;
     if (EPI == EPI_PUSH || EPI == EPI_STORE_ROWS) {
         // The 32 rows of this warp all belong to one owner rank (owners hold whole row blocks).
+        // (rows past M are never stored; keep their owner index inside the table)
         const long drow0 = tl.d_row0 + row_base;
-        const int peer = EPI == EPI_PUSH ? static_cast<int>(drow0 / p.rows_per_peer) : 0;
+        const int peer = EPI == EPI_PUSH ? min(static_cast<int>(drow0 / p.rows_per_peer), 7) : 0;
         const long prow0 = EPI == EPI_PUSH ? drow0 - static_cast<long>(peer) * p.rows_per_peer : drow0;
         __nv_bfloat16* base =
                 EPI == EPI_PUSH ? static_cast<__nv_bfloat16*>(p.peer_out != nullptr ? p.peer_out[peer]
                                                                                    : p.fuse.rs_peer_out[peer])
                                 : p.D;
+        uint32_t ra[32], rb[32];
+        if (zero_tile) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                ra[i] = rb[i] = 0u;
+        } else {
+            tmem_ld_32x32b_x32(t_addr, ra);
+        }
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
-            uint32_t r0[32], r1[32];
-            if (!zero_tile) {
-                tmem_ld_32x32b_x32(t_addr + c * 64, r0);
-                tmem_ld_32x32b_x32(t_addr + c * 64 + 32, r1);
-                tmem_ld_wait();
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    r0[i] = r1[i] = 0u;
-            }
             // lane = row: 64 bf16 of this row into the padded staging row
             uint4* srow = reinterpret_cast<uint4*>(stage_warp + lane * PUSH_ROW_BYTES);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                uint4 o;
-                o.x = pack_bf16x2(__uint_as_float(r0[i * 8 + 0]), __uint_as_float(r0[i * 8 + 1]));
-                o.y = pack_bf16x2(__uint_as_float(r0[i * 8 + 2]), __uint_as_float(r0[i * 8 + 3]));
-                o.z = pack_bf16x2(__uint_as_float(r0[i * 8 + 4]), __uint_as_float(r0[i * 8 + 5]));
-                o.w = pack_bf16x2(__uint_as_float(r0[i * 8 + 6]), __uint_as_float(r0[i * 8 + 7]));
-                srow[i] = o;
-                o.x = pack_bf16x2(__uint_as_float(r1[i * 8 + 0]), __uint_as_float(r1[i * 8 + 1]));
-                o.y = pack_bf16x2(__uint_as_float(r1[i * 8 + 2]), __uint_as_float(r1[i * 8 + 3]));
-                o.z = pack_bf16x2(__uint_as_float(r1[i * 8 + 4]), __uint_as_float(r1[i * 8 + 5]));
-                o.w = pack_bf16x2(__uint_as_float(r1[i * 8 + 6]), __uint_as_float(r1[i * 8 + 7]));
-                srow[4 + i] = o;
+            if (!zero_tile) {
+                tmem_ld_wait(ra);
+                tmem_ld_32x32b_x32(t_addr + c * 64 + 32, rb);
             }
+            pack_row32(ra, srow);
+            if (!zero_tile) {
+                tmem_ld_wait(rb);
+                if (c + 1 < BN / 64)
+                    tmem_ld_32x32b_x32(t_addr + (c + 1) * 64, ra);
+            }
+            pack_row32(rb, srow + 4);
             __syncwarp();
             // 8 lanes write one row's 128 bytes: four rows per store instruction
             const int col = tl.n0 + c * 64 + (lane & 7) * 8;
@@ -303,76 +352,105 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
         }
         return;
     }
+    // ---- TMA-store epilogues: 32-column boxes through the warp's ring of staging boxes
     const int m = tl.m0 + row_in_tile;
     const bool row_ok = m < p.M;
     const long drow = tl.d_row0 + row_in_tile;
+    const bool rows_in = tl.m0 + row_base < p.M;  // warp-uniform: some of the 32 rows exist
+    const int box_row = static_cast<int>(tl.d_row0 + row_base);
     if (EPI == EPI_SWIGLU) {
         // columns [0,128) = gate, [128,256) = up of output columns n0..n0+127
+        uint32_t rg[32], ru[32];
+        tmem_ld_32x32b_x32(t_addr, rg);
+        tmem_ld_32x32b_x32(t_addr + 128, ru);
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
-            uint32_t rg[32], ru[32];
-            tmem_ld_32x32b_x32(t_addr + c * 32, rg);
-            tmem_ld_32x32b_x32(t_addr + 128 + c * 32, ru);
-            tmem_ld_wait();
-            const int col = tl.n0 + c * 32;
-            const int ok = p.N - col;
-            if (row_ok && ok > 0) {
-                float g[32], u[32], h[32];
+            tmem_ld_wait(rg);
+            tmem_ld_wait(ru);
+            uint32_t pg[16], pu[16], ph[16];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    g[i] = __uint_as_float(rg[i]);
-                    u[i] = __uint_as_float(ru[i]);
-                    h[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
-                }
-                store_row32(p.D + drow * p.ldd + col, g, ok);
-                store_row32(p.D + drow * p.ldd + p.aux_off + col, u, ok);
-                store_row32(p.D2 + drow * p.ldd2 + col, h, ok);
+            for (int i = 0; i < 16; ++i) {
+                const float g0 = __uint_as_float(rg[2 * i]), g1 = __uint_as_float(rg[2 * i + 1]);
+                const float u0 = __uint_as_float(ru[2 * i]), u1 = __uint_as_float(ru[2 * i + 1]);
+                pg[i] = pack_bf16x2(g0, g1);
+                pu[i] = pack_bf16x2(u0, u1);
+                ph[i] = pack_bf16x2(__fdividef(g0, 1.f + __expf(-g0)) * u0,
+                                    __fdividef(g1, 1.f + __expf(-g1)) * u1);
+            }
+            if (c + 1 < 4) {
+                tmem_ld_32x32b_x32(t_addr + (c + 1) * 32, rg);
+                tmem_ld_32x32b_x32(t_addr + 128 + (c + 1) * 32, ru);
+            }
+            const int col = tl.n0 + c * 32;
+            if (rows_in && col < p.N) {
+                emit_box32(out.map_d, out, lane, col, box_row, pg);
+                emit_box32(out.map_du, out, lane, col, box_row, pu);
+                emit_box32(out.map_d2, out, lane, col, box_row, ph);
             }
         }
         return;
     }
-#pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        if (!zero_tile) {
-            tmem_ld_32x32b_x32(t_addr + c * 32, r);
-            tmem_ld_wait();
-        } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-                r[i] = 0u;
-        }
-        const int col = tl.n0 + c * 32;
-        const int ok = p.N - col;
-        if (!row_ok || ok <= 0)
-            continue;
-        float v[32];
+    uint32_t r[32];
+    if (zero_tile) {
 #pragma unroll
         for (int i = 0; i < 32; ++i)
-            v[i] = __uint_as_float(r[i]);
+            r[i] = 0u;
+    } else {
+        tmem_ld_32x32b_x32(t_addr, r);
+    }
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+        const int col = tl.n0 + c * 32;
+        const int ok = p.N - col;
+        const bool lane_ok = row_ok && ok > 0;
+        uint32_t pk[16], pk2[16];
         if (EPI == EPI_STORE) {
-            store_row32(p.D + drow * p.ldd + col, v, ok);
+            if (!zero_tile)
+                tmem_ld_wait(r);
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
         } else if (EPI == EPI_ACCUM) {
             float o[32];
-            load_row32(p.D + drow * p.ldd + col, o, ok);
+            if (lane_ok)
+                load_row32(p.D + drow * p.ldd + col, o, ok);
+            if (!zero_tile)
+                tmem_ld_wait(r);
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-                v[i] += o[i];
-            store_row32(p.D + drow * p.ldd + col, v, ok);
+            for (int i = 0; i < 16; ++i)
+                pk[i] = lane_ok ? pack_bf16x2(__uint_as_float(r[2 * i]) + o[2 * i],
+                                              __uint_as_float(r[2 * i + 1]) + o[2 * i + 1])
+                                : 0u;
         } else if (EPI == EPI_DSWIGLU) {
             float g[32], u[32];
-            load_row32(p.aux + drow * p.ldaux + col, g, ok);
-            load_row32(p.aux + drow * p.ldaux + p.aux_off + col, u, ok);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const float sg = 1.f / (1.f + __expf(-g[i]));
-                const float dh = v[i];
-                const float silu = g[i] * sg;
-                u[i] = dh * u[i] * (sg + silu * (1.f - sg));  // dG
-                g[i] = dh * silu;                              // dU
+            if (lane_ok) {
+                load_row32(p.aux + drow * p.ldaux + col, g, ok);
+                load_row32(p.aux + drow * p.ldaux + p.aux_off + col, u, ok);
             }
-            store_row32(p.D + drow * p.ldd + col, u, ok);
-            store_row32(p.D + drow * p.ldd + p.aux_off + col, g, ok);
+            if (!zero_tile)
+                tmem_ld_wait(r);
+            if (lane_ok) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float sg = __fdividef(1.f, 1.f + __expf(-g[i]));
+                    const float dh = __uint_as_float(r[i]);
+                    const float silu = g[i] * sg;
+                    u[i] = dh * u[i] * (sg + silu * (1.f - sg));  // dG
+                    g[i] = dh * silu;                              // dU
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                pk[i] = lane_ok ? pack_bf16x2(u[2 * i], u[2 * i + 1]) : 0u;
+                pk2[i] = lane_ok ? pack_bf16x2(g[2 * i], g[2 * i + 1]) : 0u;
+            }
+        }
+        if (!zero_tile && c + 1 < BN / 32)
+            tmem_ld_32x32b_x32(t_addr + (c + 1) * 32, r);
+        if (rows_in && ok > 0) {
+            emit_box32(out.map_d, out, lane, col, box_row, pk);
+            if (EPI == EPI_DSWIGLU)
+                emit_box32(out.map_du, out, lane, col, box_row, pk2);
         }
     }
 }
@@ -528,23 +606,29 @@ __device__ __forceinline__ void reduce_scatter_tail(const FuseArgs& f, uint64_t 
     }
 }
 
-template <bool PAIR, bool A_MN, bool B_MN, int EPI>
+template <int MODE, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-        gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
-                         const __grid_constant__ CUtensorMap tma_b, const KParams p) {
-    using C = Cfg<PAIR>;
-    constexpr int STAGES = stages_for<PAIR, EPI>();
+        gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                         const __grid_constant__ CUtensorMap tma_d, const __grid_constant__ CUtensorMap tma_du,
+                         const __grid_constant__ CUtensorMap tma_d2, const KParams p) {
+    using C = Cfg<MODE>;
+    constexpr bool PAIR = C::PAIR;
+    constexpr int MSUB = C::MSUB;
+    constexpr int A_STAGE_BYTES = C::A_STAGE_BYTES;
+    constexpr int STAGES = stages_for<MODE, EPI>();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::STAGE_BYTES);
-    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+    uint8_t* push_staging = smem + STAGES * C::STAGE_BYTES;  // 1024-byte aligned: the staging boxes
+    uint64_t* bars = reinterpret_cast<uint64_t*>(push_staging + staging_for<EPI>());
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty.
+    // single / pair: tmem_full[a] and tmem_empty[a] belong to accumulator buffer a.
+    // wide: tmem_full[0] covers the whole tile, tmem_empty[s] belongs to sub-tile s.
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* comm_ok = reinterpret_cast<volatile int*>(tmem_slot + 2);
-    uint8_t* push_staging = smem + STAGES * C::STAGE_BYTES + 256;  // EPI_PUSH only
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const int lane = threadIdx.x & 31;
@@ -592,6 +676,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const uint32_t tmem_base = *tmem_slot;
 
     WaitCtx wc{abort_flag, p.wait_limit_ns};
+    // (the staged epilogues have shared-memory room for one group of four warps only)
+    const bool two_groups = MSUB > 1 && EPI != EPI_PUSH && EPI != EPI_STORE_ROWS && p.fuse.ag_dst == nullptr;
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer (every CTA)
@@ -603,22 +689,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 Tile tl = decode_tile<C::TILE_M>(p, t);
                 if (tl.skip || tl.k_blocks == 0)
                     continue;
-                const int m0 = tl.m0 + static_cast<int>(crank) * BM;  // this CTA's rows of A
+                // this CTA's rows of A: 128 of each 256-row sub-tile
+                const int m0 = tl.m0 + static_cast<int>(crank) * BM;
                 if (p.a_ready != nullptr) {
                     // all_gather fusion: rows of this m-block arrive from another GPU;
-                    // wait (bounded) for the shard's ready counter.
-                    const uint32_t* f = p.a_ready + m0 / p.rows_per_flag;
-                    uint32_t spins = 0;
-                    uint64_t t0 = 0;
-                    while (static_cast<int32_t>(ld_acquire_gpu(f) - p.a_ready_target) < 0) {
-                        if ((++spins & 0x3f) == 0) {
-                            uint64_t now = globaltimer_ns();
-                            if (t0 == 0)
-                                t0 = now;
-                            if (*abort_flag || now - t0 > p.wait_limit_ns) {
-                                *abort_flag = 1;
-                                alive = false;
-                                break;
+                    // wait (bounded) for the ready counter of each sub-tile's shard.
+                    for (int sub = 0; sub < MSUB && alive; ++sub) {
+                        if (m0 + sub * 256 >= p.M)
+                            break;
+                        const uint32_t* f = p.a_ready + (m0 + sub * 256) / p.rows_per_flag;
+                        uint32_t spins = 0;
+                        uint64_t t0 = 0;
+                        while (static_cast<int32_t>(ld_acquire_gpu(f) - p.a_ready_target) < 0) {
+                            if ((++spins & 0x3f) == 0) {
+                                uint64_t now = globaltimer_ns();
+                                if (t0 == 0)
+                                    t0 = now;
+                                if (*abort_flag || now - t0 > p.wait_limit_ns) {
+                                    *abort_flag = 1;
+                                    alive = false;
+                                    break;
+                                }
                             }
                         }
                     }
@@ -659,12 +750,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         const uint32_t fb = mapa_u32(full0 + 8 * s, 0);
                         if (crank == 0)
                             mbar_expect_tx(full0 + 8 * s, 2 * C::STAGE_BYTES);
-                        if (!A_MN) {
-                            tma_load_2d_pair(sa, &tma_a, fb, k, m0);
-                        } else {
 #pragma unroll
-                            for (int j = 0; j < BM / 64; ++j)
-                                tma_load_2d_pair(sa + j * MN_CHUNK_BYTES, &tma_a, fb, m0 + 64 * j, k);
+                        for (int sub = 0; sub < MSUB; ++sub) {
+                            const uint32_t sas = sa + sub * A_SUB_BYTES;
+                            const int ms = m0 + sub * 256;
+                            if (!A_MN) {
+                                tma_load_2d_pair(sas, &tma_a, fb, k, ms);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < BM / 64; ++j)
+                                    tma_load_2d_pair(sas + j * MN_CHUNK_BYTES, &tma_a, fb, ms + 64 * j, k);
+                            }
                         }
                         // this CTA's half of the 256 columns of B
                         if (!B_MN) {
@@ -688,7 +784,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     } else if (warp == 1) {
         // ------------------------------------------------------ UMMA issuer (leader CTA only)
         if (lane == 0 && crank == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16_f32(C::TILE_M, BN, A_MN, B_MN);
+            constexpr uint32_t idesc = umma_idesc_bf16_f32(PAIR ? 256 : 128, BN, A_MN, B_MN);
             int s = 0;
             uint32_t ph = 0;
             int acc = 0;
@@ -698,35 +794,50 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 Tile tl = decode_tile<C::TILE_M>(p, t);
                 if (tl.skip || tl.k_blocks == 0)
                     continue;
-                if (!mbar_wait<PAIR>(tempty0 + 8 * acc, acc_ph ^ 1, wc))
-                    break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
+                if (MSUB == 1) {
+                    if (!mbar_wait<PAIR>(tempty0 + 8 * acc, acc_ph ^ 1, wc))
+                        break;
+                    tc_fence_after();
+                }
                 for (int kb = 0; kb < tl.k_blocks; ++kb) {
                     if (!mbar_wait(full0 + 8 * s, ph, wc)) {
                         alive = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem_a + s * A_STAGE_BYTES);
                     const uint32_t sb = smem_u32(smem_b + s * C::B_STAGE_BYTES);
 #pragma unroll
-                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                        // K-major: 16 k = 32 bytes inside the 128 B row.
-                        // MN-major: 16 k = 16 rows of 128 B.
-                        const uint64_t ad =
-                                A_MN ? umma_smem_desc_sw128(sa + kk * (UMMA_K * 128), MN_CHUNK_BYTES,
-                                                            1024)
-                                     : umma_smem_desc_sw128(sa + kk * (UMMA_K * 2), 16, 1024);
-                        const uint64_t bd =
-                                B_MN ? umma_smem_desc_sw128(sb + kk * (UMMA_K * 128), MN_CHUNK_BYTES,
-                                                            1024)
-                                     : umma_smem_desc_sw128(sb + kk * (UMMA_K * 2), 16, 1024);
-                        if (PAIR)
-                            umma_f16_cg2(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
-                        else
-                            umma_f16_cg1(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+                    for (int sub = 0; sub < MSUB; ++sub) {
+                        if (MSUB > 1 && kb == 0) {
+                            // the epilogue of the previous tile has drained this sub-tile's accumulator
+                            if (!mbar_wait<PAIR>(tempty0 + 8 * sub, acc_ph ^ 1, wc)) {
+                                alive = false;
+                                break;
+                            }
+                            tc_fence_after();
+                        }
+                        const uint32_t d_tmem = tmem_base + (MSUB > 1 ? sub : acc) * BN;
+                        const uint32_t sa = smem_u32(smem_a + s * A_STAGE_BYTES + sub * A_SUB_BYTES);
+#pragma unroll
+                        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                            // K-major: 16 k = 32 bytes inside the 128 B row.
+                            // MN-major: 16 k = 16 rows of 128 B.
+                            const uint64_t ad =
+                                    A_MN ? umma_smem_desc_sw128(sa + kk * (UMMA_K * 128), MN_CHUNK_BYTES,
+                                                                1024)
+                                         : umma_smem_desc_sw128(sa + kk * (UMMA_K * 2), 16, 1024);
+                            const uint64_t bd =
+                                    B_MN ? umma_smem_desc_sw128(sb + kk * (UMMA_K * 128), MN_CHUNK_BYTES,
+                                                                1024)
+                                         : umma_smem_desc_sw128(sb + kk * (UMMA_K * 2), 16, 1024);
+                            if (PAIR)
+                                umma_f16_cg2(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+                            else
+                                umma_f16_cg1(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        }
                     }
+                    if (!alive)
+                        break;
                     // free the smem stage (in both CTAs of a pair) when these MMAs retire
                     if (PAIR) {
                         umma_commit_cg2(empty0 + 8 * s);
@@ -748,14 +859,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 } else {
                     umma_commit_cg1(tfull0 + 8 * acc);
                 }
-                acc ^= 1;
-                if (acc == 0)
+                if (++acc == C::ACCS) {
+                    acc = 0;
                     acc_ph ^= 1;
+                }
             }
         }
-    } else if (warp < 6) {
-        // ------------------------------------------------------ epilogue (warps 2..5, every CTA)
+    } else if (warp < 6 || two_groups) {
+        // ------------------------------------------------------ epilogue (warps 2..5, every CTA;
+        // in the wide variant warps 6..9 too when they have nothing to gather: the first group
+        // drains sub-tile 0 while the second drains sub-tile 1)
         const int q = warp & 3;  // TMEM lane quarter this warp may read
+        const int sub_begin = two_groups ? (warp < 6 ? 0 : 1) : 0;
+        const int sub_end = two_groups ? sub_begin + 1 : MSUB;
+        OutRing out;
+        out.nslots = two_groups ? 2 : 4;
+        out.base = push_staging + (two_groups ? (warp - 2) * 2 : q * 4) * OUT_BOX_BYTES;
+        out.slot = 0;
+        out.map_d = &tma_d;
+        out.map_du = &tma_du;
+        out.map_d2 = &tma_d2;
         int acc = 0;
         uint32_t acc_ph = 0;
         for (int t = worker; t < p.num_tiles; t += workers) {
@@ -770,34 +893,45 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     break;
                 tc_fence_after();
             }
-            const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-            epilogue_tile<EPI>(p, tl, t_addr, static_cast<int>(crank) * BM + q * 32, lane, zero_tile,
-                               push_staging + q * PUSH_WARP_BYTES);
-            if (!zero_tile) {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    if (PAIR && crank != 0)
-                        mbar_arrive_remote(mapa_u32(tempty0 + 8 * acc, 0));
-                    else
-                        mbar_arrive(tempty0 + 8 * acc);
+#pragma unroll 1
+            for (int sub = sub_begin; sub < sub_end; ++sub) {
+                const int sub_row = sub * 256 + static_cast<int>(crank) * BM;  // this CTA's rows of the sub-tile
+                const uint32_t t_addr =
+                        tmem_base + (MSUB > 1 ? sub : acc) * BN + (static_cast<uint32_t>(q * 32) << 16);
+                epilogue_tile<EPI>(p, tl, t_addr, sub_row + q * 32, lane, zero_tile,
+                                   push_staging + q * PUSH_WARP_BYTES, out);
+                if (!zero_tile) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const uint32_t eb = tempty0 + 8 * (MSUB > 1 ? sub : acc);
+                        if (PAIR && crank != 0)
+                            mbar_arrive_remote(mapa_u32(eb, 0));
+                        else
+                            mbar_arrive(eb);
+                    }
                 }
-                acc ^= 1;
-                if (acc == 0)
-                    acc_ph ^= 1;
+                if (EPI == EPI_PUSH && p.fuse.rs_count_peer[0] != nullptr && tl.m0 + sub_row < p.M) {
+                    // this warp's 32 rows of the partial tile are in the owner's staging slot:
+                    // make them visible system-wide, then count them (4 counts per 128-row block)
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int owner = (tl.m0 + sub_row) / p.rows_per_peer;
+                        __threadfence_system();
+                        red_release_sys_add(p.fuse.rs_count_peer[owner] + p.fuse.rank, 1u);
+                    }
+                }
             }
-            if (EPI == EPI_PUSH && p.fuse.rs_count_peer[0] != nullptr) {
-                // this warp's 32 rows of the partial tile are in the owner's staging slot:
-                // make them visible system-wide, then count them (4 counts per 128-row tile)
-                __syncwarp();
-                if (lane == 0) {
-                    const int row0 = tl.m0 + static_cast<int>(crank) * BM;
-                    const int owner = row0 / p.rows_per_peer;
-                    __threadfence_system();
-                    red_release_sys_add(p.fuse.rs_count_peer[owner] + p.fuse.rank, 1u);
+            if (!zero_tile) {
+                if (++acc == C::ACCS) {
+                    acc = 0;
+                    acc_ph ^= 1;
                 }
             }
         }
+        // this thread's TMA stores have left shared memory before the CTA gives it up
+        if (lane == 0)
+            tma_store_wait<0>();
     } else {
         // ------------------------------------------------------ communication warps (6..9)
         if (p.fuse.ag_dst != nullptr)
@@ -866,15 +1000,34 @@ bool make_map(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer,
     return r == CUDA_SUCCESS;
 }
 
+// Output matrix for the TMA-store epilogues: box = 32 columns (64 B, the swizzle span) x 32 rows.
+bool make_out_map(CUtensorMap* map, const void* ptr, uint64_t cols, uint64_t rows, uint64_t ld) {
+    auto fn = get_encode_fn();
+    if (fn == nullptr)
+        return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+struct Maps {
+    CUtensorMap a, b, d, du, d2;
+};
+
 std::atomic<uint64_t> g_launches{0};
 
 // Launches one instantiation.  `workers` = CTAs (single) or CTA pairs (pair) wanted at most;
 // the pair variant is additionally capped by what the device can co-schedule as 2-CTA clusters.
-template <bool PAIR, bool A_MN, bool B_MN, int EPI>
-cudaError_t launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const KParams& kp, int workers,
-                     cudaStream_t stream) {
-    auto kern = gemm_bf16_kernel<PAIR, A_MN, B_MN, EPI>;
-    constexpr int smem = smem_for<PAIR, EPI>();
+template <int MODE, bool A_MN, bool B_MN, int EPI>
+cudaError_t launch_t(const Maps& maps, const KParams& kp, int workers, cudaStream_t stream) {
+    constexpr bool PAIR = Cfg<MODE>::PAIR;
+    auto kern = gemm_bf16_kernel<MODE, A_MN, B_MN, EPI>;
+    constexpr int smem = smem_for<MODE, EPI>();
     int dev = 0;
     cudaGetDevice(&dev);
     static std::mutex mu;
@@ -931,45 +1084,44 @@ cudaError_t launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const KParams
     attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mb, kp);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, maps.a, maps.b, maps.d, maps.du, maps.d2, kp);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     count_launch();
     return e;
 }
 
-template <bool PAIR, bool A_MN, bool B_MN>
-cudaError_t launch_e(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const KParams& kp,
-                     int workers, cudaStream_t stream) {
+template <int MODE, bool A_MN, bool B_MN>
+cudaError_t launch_e(int epi, const Maps& maps, const KParams& kp, int workers, cudaStream_t stream) {
     switch (epi) {
         case EPI_STORE:
-            return launch_t<PAIR, A_MN, B_MN, EPI_STORE>(ma, mb, kp, workers, stream);
+            return launch_t<MODE, A_MN, B_MN, EPI_STORE>(maps, kp, workers, stream);
         case EPI_ACCUM:
-            return launch_t<PAIR, A_MN, B_MN, EPI_ACCUM>(ma, mb, kp, workers, stream);
+            return launch_t<MODE, A_MN, B_MN, EPI_ACCUM>(maps, kp, workers, stream);
         case EPI_PUSH:
-            return launch_t<PAIR, A_MN, B_MN, EPI_PUSH>(ma, mb, kp, workers, stream);
+            return launch_t<MODE, A_MN, B_MN, EPI_PUSH>(maps, kp, workers, stream);
         case EPI_STORE_ROWS:
-            return launch_t<PAIR, A_MN, B_MN, EPI_STORE_ROWS>(ma, mb, kp, workers, stream);
+            return launch_t<MODE, A_MN, B_MN, EPI_STORE_ROWS>(maps, kp, workers, stream);
         case EPI_DSWIGLU:
-            return launch_t<PAIR, A_MN, B_MN, EPI_DSWIGLU>(ma, mb, kp, workers, stream);
+            return launch_t<MODE, A_MN, B_MN, EPI_DSWIGLU>(maps, kp, workers, stream);
         case EPI_SWIGLU:
             if (B_MN)
                 return cudaErrorInvalidValue;
-            return launch_t<PAIR, A_MN, false, EPI_SWIGLU>(ma, mb, kp, workers, stream);
+            return launch_t<MODE, A_MN, false, EPI_SWIGLU>(maps, kp, workers, stream);
         default:
             return cudaErrorInvalidValue;
     }
 }
 
-template <bool PAIR>
-cudaError_t launch_l(bool a_mn, bool b_mn, int epi, const CUtensorMap& ma, const CUtensorMap& mb,
-                     const KParams& kp, int workers, cudaStream_t stream) {
+template <int MODE>
+cudaError_t launch_l(bool a_mn, bool b_mn, int epi, const Maps& maps, const KParams& kp, int workers,
+                     cudaStream_t stream) {
     if (!a_mn && !b_mn)
-        return launch_e<PAIR, false, false>(epi, ma, mb, kp, workers, stream);
+        return launch_e<MODE, false, false>(epi, maps, kp, workers, stream);
     if (!a_mn && b_mn)
-        return launch_e<PAIR, false, true>(epi, ma, mb, kp, workers, stream);
+        return launch_e<MODE, false, true>(epi, maps, kp, workers, stream);
     if (a_mn && !b_mn)
-        return launch_e<PAIR, true, false>(epi, ma, mb, kp, workers, stream);
-    return launch_e<PAIR, true, true>(epi, ma, mb, kp, workers, stream);
+        return launch_e<MODE, true, false>(epi, maps, kp, workers, stream);
+    return launch_e<MODE, true, true>(epi, maps, kp, workers, stream);
 }
 
 int sm_count() {
@@ -1002,10 +1154,18 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     const bool grouped_m = a.grouped.m_block_group != nullptr;
     const bool grouped_k = a.grouped.k_begin != nullptr;
 
-    // A CTA pair per 256 x 256 tile unless rows are grouped in 128-row blocks (per-expert
-    // forward/backward), which need the 128-row tile.
+    // A CTA pair per tile unless rows are grouped in 128-row blocks (per-expert
+    // forward/backward), which need the 128-row tile.  Large dense problems take the
+    // 512-row tile: less operand traffic per FLOP, at the price of an epilogue that is
+    // only half hidden, which a long K loop amortises.
     const bool pair = !grouped_m && a.variant != 1 && a.M > 128;
-    const int tile_m = pair ? 256 : BM;
+    bool wide = pair && a.variant == 3;
+    if (pair && a.variant == 0 && !grouped_k) {
+        const long tiles_wide = static_cast<long>((a.M + 511) / 512) *
+                                ((a.N + (a.epilogue == EPI_SWIGLU ? 127 : 255)) / (a.epilogue == EPI_SWIGLU ? 128 : 256));
+        wide = a.M >= 1024 && a.K >= 3072 && tiles_wide >= 2L * (sm_count() / 2);
+    }
+    const int tile_m = wide ? 512 : pair ? 256 : BM;
 
     KParams kp{};
     kp.M = a.M;
@@ -1018,7 +1178,16 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     kp.num_tiles = kp.m_blocks * kp.n_blocks * (grouped_k ? a.grouped.groups : 1);
     // concurrently running tiles form a near-square patch (about 2048 rows x 2300 columns)
     // so that each loaded A / B panel is shared by as many tiles as possible in L2
-    kp.group_m = pair ? 8 : 16;
+    kp.group_m = wide ? 4 : pair ? 8 : 16;
+    {
+        // tuning aid: MEGRAY_GEMM_GROUP_M overrides the raster's m-blocks per column sweep
+        static const int env_group_m = [] {
+            const char* e = getenv("MEGRAY_GEMM_GROUP_M");
+            return e != nullptr ? atoi(e) : 0;
+        }();
+        if (env_group_m > 0)
+            kp.group_m = env_group_m;
+    }
     {
         const int rot_blocks = a.m_rot / tile_m;  // m_rot is given in rows
         kp.m_rot = (rot_blocks % kp.m_blocks + kp.m_blocks) % kp.m_blocks;
@@ -1048,7 +1217,7 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     if (a.epilogue == EPI_DSWIGLU && (a.aux == nullptr || (a.ldaux % 8)))
         return cudaErrorInvalidValue;
     if (a.epilogue == EPI_PUSH &&
-        ((a.peer_out == nullptr && a.fuse.rs_peer_out[0] == nullptr) || (kp.rows_per_peer % tile_m)))
+        ((a.peer_out == nullptr && a.fuse.rs_peer_out[0] == nullptr) || (kp.rows_per_peer % (pair ? 256 : BM))))
         return cudaErrorInvalidValue;
     if ((a.epilogue == EPI_PUSH || a.epilogue == EPI_STORE_ROWS) && (a.N % 8))
         return cudaErrorInvalidValue;
@@ -1058,7 +1227,9 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     // Extents the tensor maps cover.  Grouped problems stack the groups along the
     // outer dimension of B.
     const uint64_t groups = (grouped_m || grouped_k) ? static_cast<uint64_t>(a.grouped.groups) : 1;
-    CUtensorMap ma, mb;
+    Maps maps;
+    CUtensorMap& ma = maps.a;
+    CUtensorMap& mb = maps.b;
     bool ok;
     if (!a.a_mn) {
         ok = make_map(&ma, a.A, a.K, a.M, a.lda, BM);
@@ -1090,9 +1261,38 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
         if (lim < workers)
             workers = lim > 0 ? lim : 1;
     }
+    // Output maps of the TMA-store epilogues.  A grouped-K problem stacks one [M, N] result per
+    // group; rows that a tile has past M would land in the next group's result, so such shapes
+    // (M not a multiple of the tile) leave through the guarded row-segment stores instead.
+    int epi = a.epilogue;
+    const uint64_t out_rows = static_cast<uint64_t>(a.M) * (grouped_k ? groups : 1);
+    if (epi == EPI_STORE && grouped_k && (a.M % tile_m)) {
+        if (a.N % 8)
+            return cudaErrorInvalidValue;
+        epi = EPI_STORE_ROWS;
+    }
+    if (epi == EPI_PUSH || epi == EPI_STORE_ROWS) {
+        maps.d = maps.du = maps.d2 = maps.a;  // not used by these epilogues
+    } else {
+        if (grouped_k && (a.M % tile_m))
+            return cudaErrorInvalidValue;
+        ok = make_out_map(&maps.d, a.D, a.N, out_rows, a.ldd);
+        maps.du = maps.d2 = maps.d;
+        if (ok && (epi == EPI_SWIGLU || epi == EPI_DSWIGLU)) {
+            if (a.aux_off % 8)
+                return cudaErrorInvalidValue;
+            ok = make_out_map(&maps.du, static_cast<const __nv_bfloat16*>(a.D) + a.aux_off, a.N, out_rows, a.ldd);
+        }
+        if (ok && epi == EPI_SWIGLU)
+            ok = make_out_map(&maps.d2, a.D2, a.N, out_rows, a.ldd2);
+        if (!ok)
+            return cudaErrorInvalidValue;
+    }
+    if (wide)
+        return launch_l<MODE_WIDE>(a.a_mn, a.b_mn, epi, maps, kp, workers, stream);
     if (pair)
-        return launch_l<true>(a.a_mn, a.b_mn, a.epilogue, ma, mb, kp, workers, stream);
-    return launch_l<false>(a.a_mn, a.b_mn, a.epilogue, ma, mb, kp, workers, stream);
+        return launch_l<MODE_PAIR>(a.a_mn, a.b_mn, epi, maps, kp, workers, stream);
+    return launch_l<MODE_SINGLE>(a.a_mn, a.b_mn, epi, maps, kp, workers, stream);
 }
 
 }  // namespace gemm

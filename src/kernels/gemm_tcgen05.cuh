@@ -75,7 +75,7 @@ struct GemmArgs {
     int aux_off;  // column offset of the U half (EPI_SWIGLU / EPI_DSWIGLU), also B row offset
     int m_rot;    // start the row-block order at this row (all_gather fused GEMM: own shard first)
     int sm_limit; // 0 = all SMs; otherwise cap on the persistent grid
-    int variant;  // 0 = automatic, 1 = force the single-CTA 128 x 256 tile
+    int variant;  // 0 = automatic, 1 = single-CTA 128 x 256 tile, 2 = CTA-pair 256 x 256 tile, 3 = CTA-pair 512 x 256 tile
     // all_gather fusion: wait until a_ready[(m_block*128)/rows_per_flag] >= a_ready_target
     const uint32_t* a_ready;
     int rows_per_flag;

@@ -20,9 +20,10 @@ def close(got, want, tol=2e-2):
     assert err <= tol * scale, f"max error {err} vs scale {scale}"
 
 
-# variant 0 picks the CTA-pair kernel (256 x 256 tiles, cta_group::2) when M > 128,
-# variant 1 forces the single-CTA kernel (128 x 256 tiles)
-@pytest.mark.parametrize("variant", [0, 1])
+# variant 0 picks a CTA-pair kernel (cta_group::2; 256 x 256 tiles, or 512 x 256 for large
+# problems) when M > 128, 1 forces the single-CTA kernel (128 x 256 tiles), 2 the 256-row
+# pair tile, 3 the 512-row pair tile (two sub-tiles with one accumulator each)
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (300, 264, 200), (1024, 2048, 512),
                                    (129, 8, 8), (64, 1000, 72), (2048, 1024, 1536)])
 def test_nt(M, N, K, variant):
@@ -33,7 +34,7 @@ def test_nt(M, N, K, variant):
     close(gemm(a, b, variant=variant), a.float() @ b.float().t())
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 3])
 @pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
 def test_transposed_operands(a_mn, b_mn, variant):
     from megray_b200.ops import gemm
@@ -46,18 +47,19 @@ def test_transposed_operands(a_mn, b_mn, variant):
     close(gemm(a, b, a_mn=a_mn, b_mn=b_mn, variant=variant), want)
 
 
-def test_many_tiles_per_cta_pair_exercise_the_ring_and_both_accumulators():
+@pytest.mark.parametrize("variant,sm_limit", [(0, 0), (2, 0), (3, 0), (3, 16)])
+def test_many_tiles_per_cta_pair_exercise_the_ring_and_both_accumulators(variant, sm_limit):
     from megray_b200.ops import gemm
 
     torch.manual_seed(7)
     M, N, K = 4096, 6144, 1088  # 16 x 24 tiles over <= 74 pairs: several tiles each, 17 k-steps
     a, b = mk(M, K), mk(N, K)
-    out = gemm(a, b)
+    out = gemm(a, b, variant=variant, sm_limit=sm_limit)
     idx = torch.randint(0, M, (64,), device="cuda")
     close(out[idx], a[idx].float() @ b.float().t(), tol=3e-2)
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 3])
 @pytest.mark.parametrize("M,N,K", [(300, 264, 200), (1024, 2048, 512), (129, 8, 64)])
 def test_row_segment_store_epilogue(M, N, K, variant):
     from megray_b200.ops import EPI_STORE_ROWS, gemm
@@ -79,7 +81,7 @@ def test_accumulate():
     close(d, a.float() @ b.float().t() + d0.float())
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 3])
 def test_swiglu_and_its_derivative(variant):
     from megray_b200.ops import EPI_DSWIGLU, EPI_SWIGLU, gemm
 
