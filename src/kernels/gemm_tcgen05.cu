@@ -1160,7 +1160,8 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     // only half hidden, which a long K loop amortises.
     const bool pair = !grouped_m && a.variant != 1 && a.M > 128;
     bool wide = pair && a.variant == 3;
-    if (pair && a.variant == 0 && !grouped_k) {
+    // (the push epilogue's remote stores need the next tile's main loop to hide behind: pair tile)
+    if (pair && a.variant == 0 && !grouped_k && a.epilogue != EPI_PUSH) {
         const long tiles_wide = static_cast<long>((a.M + 511) / 512) *
                                 ((a.N + (a.epilogue == EPI_SWIGLU ? 127 : 255)) / (a.epilogue == EPI_SWIGLU ? 128 : 256));
         wide = a.M >= 1024 && a.K >= 3072 && tiles_wide >= 2L * (sm_count() / 2);
