@@ -34,6 +34,8 @@ class TensorParallelOps:
         self.T, self.d = tokens, width
         self.Ts = tokens // self.n
         self.fused = fused and self.Ts % 256 == 0
+        # SMs the GEMMs may occupy (0 = all); lower it to leave room for kernels of other streams
+        self.sm_limit = 0
         self._lib = _lib.load()
         self._stage = []
         self._parity = 0
@@ -90,32 +92,33 @@ class TensorParallelOps:
         [G|U], H = swiglu(xg @ w_gu^T)."""
         if not self.fused:
             self.comm.all_gather(self._shard(xg), xg)
-            gemm(xg, w_gu, gu, epilogue=EPI_SWIGLU, out2=h, n=fl)
+            gemm(xg, w_gu, gu, epilogue=EPI_SWIGLU, out2=h, n=fl, sm_limit=self.sm_limit)
             return
-        args, _, _ = build_gemm_args(xg, w_gu, gu, epilogue=EPI_SWIGLU, out2=h, n=fl)
+        args, _, _ = build_gemm_args(xg, w_gu, gu, epilogue=EPI_SWIGLU, out2=h, n=fl, sm_limit=self.sm_limit)
         self._ag_gemm(self._shard(xg), xg, args)
 
     def ag_gemm_dswiglu(self, dy, dyg, w_down, gu, dgu, fl):
         """dyg = all_gather(dy) while computing dG|dU = dswiglu(dyg @ w_down)."""
         if not self.fused:
             self.comm.all_gather(dy, dyg)
-            gemm(dyg, w_down, dgu, b_mn=True, epilogue=EPI_DSWIGLU, aux=gu, n=fl)
+            gemm(dyg, w_down, dgu, b_mn=True, epilogue=EPI_DSWIGLU, aux=gu, n=fl, sm_limit=self.sm_limit)
             return
-        args, _, _ = build_gemm_args(dyg, w_down, dgu, b_mn=True, epilogue=EPI_DSWIGLU, aux=gu, n=fl)
+        args, _, _ = build_gemm_args(dyg, w_down, dgu, b_mn=True, epilogue=EPI_DSWIGLU, aux=gu, n=fl,
+                                     sm_limit=self.sm_limit)
         self._ag_gemm(dy, dyg, args)
 
     # -- GEMM -> reduce_scatter --------------------------------------------------------------
     def gemm_rs(self, a, b, partial, out, b_mn=False, residual=None):
         """out[T/n, d] = reduce_scatter(a @ b^T) (a @ b when b_mn) (+ residual)."""
         if not self.fused:
-            gemm(a, b, partial, b_mn=b_mn)
+            gemm(a, b, partial, b_mn=b_mn, sm_limit=self.sm_limit)
             self.comm.reduce_scatter(partial, out)
             if residual is not None:
                 out.add_(residual)
             return
         st = self._stage[self._parity]
         self._parity ^= 1
-        args, _, _ = build_gemm_args(a, b, None, b_mn=b_mn, alloc_out=False)
+        args, _, _ = build_gemm_args(a, b, None, b_mn=b_mn, alloc_out=False, sm_limit=self.sm_limit)
         rc = self._lib.megray_tp_gemm_rs(self.comm._h, C.byref(args), st.data_ptr(), out.data_ptr(),
                                          residual.data_ptr() if residual is not None else None,
                                          st._tp_flags.data_ptr(), self._stream())

@@ -74,15 +74,13 @@ struct Cfg {
 
 // The push epilogue (GEMM -> reduce_scatter) stages 32 rows x 64 columns per epilogue warp in
 // shared memory so that what crosses NVLink are whole 128-byte row segments instead of one
-// 16-byte piece per lane; rows are padded to 144 bytes, which keeps both the per-row writes and
-// the per-segment reads free of bank conflicts.  The pair variant gives up one pipeline stage
-// for the room.
-constexpr int PUSH_ROW_BYTES = 64 * 2 + 16;
-constexpr int PUSH_WARP_BYTES = 32 * PUSH_ROW_BYTES;
-constexpr int PUSH_STAGING_BYTES = 4 * PUSH_WARP_BYTES;
+// 16-byte piece per lane.  The 16-byte pieces of row r sit at piece index ^ (r & 7), which keeps
+// both the per-row writes and the per-segment reads free of bank conflicts without padding.
+constexpr int PUSH_WARP_BYTES = 32 * 128;
+constexpr int PUSH_STAGING_BYTES = 8 * PUSH_WARP_BYTES;  // up to eight epilogue warps
 
 // The other epilogues leave through TMA stores from 2 KB staging boxes: 16 boxes, two per warp
-// when both groups of epilogue warps work (wide variant), four per warp otherwise.
+// in the wide variant (eight epilogue warps), four per warp otherwise.
 constexpr int OUT_STAGING_BYTES = 16 * 2048;
 
 template <int EPI>
@@ -248,7 +246,9 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
 // `t_addr`: TMEM address of this warp's lane quarter of the accumulator; `row_base`: the first
 // of the warp's 32 rows inside the tile.  TMEM loads run one chunk ahead of the arithmetic and
 // the stores (two register sets in turn), so their latency is hidden behind the previous chunk.
-__device__ __forceinline__ void pack_row32(const uint32_t (&r)[32], uint4* dst) {
+// 32 fp32 values of one row -> four 16-byte pieces `first`..`first+3` of its 128-byte staging
+// row, each stored at piece index ^ sw.
+__device__ __forceinline__ void pack_row32_swz(const uint32_t (&r)[32], uint8_t* row, int first, int sw) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         uint4 o;
@@ -256,7 +256,7 @@ __device__ __forceinline__ void pack_row32(const uint32_t (&r)[32], uint4* dst) 
         o.y = pack_bf16x2(__uint_as_float(r[i * 8 + 2]), __uint_as_float(r[i * 8 + 3]));
         o.z = pack_bf16x2(__uint_as_float(r[i * 8 + 4]), __uint_as_float(r[i * 8 + 5]));
         o.w = pack_bf16x2(__uint_as_float(r[i * 8 + 6]), __uint_as_float(r[i * 8 + 7]));
-        dst[i] = o;
+        *reinterpret_cast<uint4*>(row + (((first + i) ^ sw) << 4)) = o;
     }
 }
 
@@ -325,26 +325,26 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
         }
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
-            // lane = row: 64 bf16 of this row into the padded staging row
-            uint4* srow = reinterpret_cast<uint4*>(stage_warp + lane * PUSH_ROW_BYTES);
+            // lane = row: 64 bf16 of this row into its staging row, pieces swizzled by the row
+            uint8_t* srow = stage_warp + lane * 128;
             if (!zero_tile) {
                 tmem_ld_wait(ra);
                 tmem_ld_32x32b_x32(t_addr + c * 64 + 32, rb);
             }
-            pack_row32(ra, srow);
+            pack_row32_swz(ra, srow, 0, lane & 7);
             if (!zero_tile) {
                 tmem_ld_wait(rb);
                 if (c + 1 < BN / 64)
                     tmem_ld_32x32b_x32(t_addr + (c + 1) * 64, ra);
             }
-            pack_row32(rb, srow + 4);
+            pack_row32_swz(rb, srow, 4, lane & 7);
             __syncwarp();
             // 8 lanes write one row's 128 bytes: four rows per store instruction
             const int col = tl.n0 + c * 64 + (lane & 7) * 8;
 #pragma unroll
             for (int it = 0; it < 8; ++it) {
                 const int rr = it * 4 + (lane >> 3);
-                const uint4 v = *reinterpret_cast<const uint4*>(stage_warp + rr * PUSH_ROW_BYTES + (lane & 7) * 16);
+                const uint4 v = *reinterpret_cast<const uint4*>(stage_warp + rr * 128 + (((lane & 7) ^ (rr & 7)) << 4));
                 if (tl.m0 + row_base + rr < p.M && col + 8 <= p.N)
                     *reinterpret_cast<uint4*>(base + (prow0 + rr) * p.ldd + col) = v;
             }
@@ -629,6 +629,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* comm_ok = reinterpret_cast<volatile int*>(tmem_slot + 2);
+    // hand-over of sub-tile 1 to the late-joining second epilogue group (wide variant fused with
+    // an all_gather): see the epilogue role below
+    int* split_state = reinterpret_cast<int*>(tmem_slot + 3);
+    volatile int* g0_tiles = reinterpret_cast<volatile int*>(tmem_slot + 4);  // [4], one per lane quarter
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const int lane = threadIdx.x & 31;
@@ -644,6 +648,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
+        *split_state = 0;
+        for (int i = 0; i < 4; ++i)
+            g0_tiles[i] = 0;
         prefetch_tensormap(&tma_a);
         prefetch_tensormap(&tma_b);
         for (int s = 0; s < STAGES; ++s) {
@@ -676,8 +683,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const uint32_t tmem_base = *tmem_slot;
 
     WaitCtx wc{abort_flag, p.wait_limit_ns};
-    // (the staged epilogues have shared-memory room for one group of four warps only)
-    const bool two_groups = MSUB > 1 && EPI != EPI_PUSH && EPI != EPI_STORE_ROWS && p.fuse.ag_dst == nullptr;
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer (every CTA)
@@ -865,77 +870,143 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 }
             }
         }
-    } else if (warp < 6 || two_groups) {
-        // ------------------------------------------------------ epilogue (warps 2..5, every CTA;
-        // in the wide variant warps 6..9 too when they have nothing to gather: the first group
-        // drains sub-tile 0 while the second drains sub-tile 1)
+    } else {
+        // ------------------------------------------------------ warps 2..9
+        // Warps 2..5 are the epilogue group of every variant.  In the wide variant warps 6..9 are
+        // a second epilogue group: the first group drains sub-tile 0 while the second drains
+        // sub-tile 1.
+        //  * Nothing to gather: both groups start with the first tile and stay within one phase
+        //    of the accumulator barrier (the MMA warp needs both sub-tiles drained to go on), so
+        //    its parity is enough for both.
+        //  * Fused with an all_gather: warps 6..9 gather first and join late, at a tile ordinal S
+        //    that nobody can know in advance, and a late joiner cannot tell the barrier's phases
+        //    apart by parity.  So (a) S is agreed through one shared word: every first-group warp
+        //    records each ordinal it starts with atomicMax before it decides how much of that
+        //    tile is its own, and the second group's leader claims S = first ordinal not yet
+        //    recorded with a compare-and-swap; whoever saw no claim at ordinal i has made S > i.
+        //    (b) From S on, first-group warp q tells second-group warp q through a counter in
+        //    shared memory that tile i's accumulators are complete.
+        constexpr int DECIDED = 0x40000000;
+        const bool second = warp >= 6;
+        const bool late_join = MSUB > 1 && p.fuse.ag_dst != nullptr;
         const int q = warp & 3;  // TMEM lane quarter this warp may read
-        const int sub_begin = two_groups ? (warp < 6 ? 0 : 1) : 0;
-        const int sub_end = two_groups ? sub_begin + 1 : MSUB;
-        OutRing out;
-        out.nslots = two_groups ? 2 : 4;
-        out.base = push_staging + (two_groups ? (warp - 2) * 2 : q * 4) * OUT_BOX_BYTES;
-        out.slot = 0;
-        out.map_d = &tma_d;
-        out.map_du = &tma_du;
-        out.map_d2 = &tma_d2;
-        int acc = 0;
-        uint32_t acc_ph = 0;
-        for (int t = worker; t < p.num_tiles; t += workers) {
-            Tile tl = decode_tile<C::TILE_M>(p, t);
-            if (tl.skip)
-                continue;
-            const bool zero_tile = tl.k_blocks == 0;
-            if (!zero_tile) {
-                // the whole warp must agree before the .sync.aligned TMEM loads
-                const bool got = mbar_wait(tfull0 + 8 * acc, acc_ph, wc);
-                if (!__all_sync(0xffffffffu, got))
-                    break;
-                tc_fence_after();
-            }
-#pragma unroll 1
-            for (int sub = sub_begin; sub < sub_end; ++sub) {
-                const int sub_row = sub * 256 + static_cast<int>(crank) * BM;  // this CTA's rows of the sub-tile
-                const uint32_t t_addr =
-                        tmem_base + (MSUB > 1 ? sub : acc) * BN + (static_cast<uint32_t>(q * 32) << 16);
-                epilogue_tile<EPI>(p, tl, t_addr, sub_row + q * 32, lane, zero_tile,
-                                   push_staging + q * PUSH_WARP_BYTES, out);
-                if (!zero_tile) {
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        const uint32_t eb = tempty0 + 8 * (MSUB > 1 ? sub : acc);
-                        if (PAIR && crank != 0)
-                            mbar_arrive_remote(mapa_u32(eb, 0));
-                        else
-                            mbar_arrive(eb);
+        int split_from = MSUB > 1 ? (late_join ? 0x3fffffff : 0) : 0x3fffffff;
+        if (second && p.fuse.ag_dst != nullptr) {
+            all_gather_warps(p.fuse, p.wait_limit_ns, abort_flag, comm_ok);
+            if (late_join) {
+                if (threadIdx.x == NUM_THREADS - COMM_THREADS) {
+                    int cur = *reinterpret_cast<volatile int*>(split_state);
+                    for (;;) {
+                        const int old = atomicCAS(split_state, cur, DECIDED | cur);
+                        if (old == cur)
+                            break;
+                        cur = old;
                     }
                 }
-                if (EPI == EPI_PUSH && p.fuse.rs_count_peer[0] != nullptr && tl.m0 + sub_row < p.M) {
-                    // this warp's 32 rows of the partial tile are in the owner's staging slot:
-                    // make them visible system-wide, then count them (4 counts per 128-row block)
-                    __syncwarp();
-                    if (lane == 0) {
-                        const int owner = (tl.m0 + sub_row) / p.rows_per_peer;
-                        __threadfence_system();
-                        red_release_sys_add(p.fuse.rs_count_peer[owner] + p.fuse.rank, 1u);
-                    }
-                }
-            }
-            if (!zero_tile) {
-                if (++acc == C::ACCS) {
-                    acc = 0;
-                    acc_ph ^= 1;
-                }
+                comm_bar();
+                split_from = *reinterpret_cast<volatile int*>(split_state) & ~DECIDED;
             }
         }
-        // this thread's TMA stores have left shared memory before the CTA gives it up
-        if (lane == 0)
-            tma_store_wait<0>();
-    } else {
-        // ------------------------------------------------------ communication warps (6..9)
-        if (p.fuse.ag_dst != nullptr)
-            all_gather_warps(p.fuse, p.wait_limit_ns, abort_flag, comm_ok);
+        if (!second || MSUB > 1) {
+            OutRing out;
+            out.nslots = MSUB > 1 ? 2 : 4;
+            out.base = push_staging + (MSUB > 1 ? (warp - 2) * 2 : q * 4) * OUT_BOX_BYTES;
+            out.slot = 0;
+            out.map_d = &tma_d;
+            out.map_du = &tma_du;
+            out.map_d2 = &tma_d2;
+            uint8_t* stage_warp = push_staging + (MSUB > 1 ? warp - 2 : q) * PUSH_WARP_BYTES;
+            int acc = 0;
+            uint32_t acc_ph = 0;
+            int ordinal = 0;
+            for (int t = worker; t < p.num_tiles; t += workers) {
+                Tile tl = decode_tile<C::TILE_M>(p, t);
+                if (tl.skip)
+                    continue;
+                const bool zero_tile = tl.k_blocks == 0;
+                const int i = ordinal++;
+                if (late_join && !second) {
+                    int old = 0;
+                    if (lane == 0)
+                        old = atomicMax(split_state, i + 1);
+                    old = __shfl_sync(0xffffffffu, old, 0);
+                    if (old & DECIDED)
+                        split_from = old & ~DECIDED;
+                }
+                const bool split = i >= split_from;
+                const int sub_begin = second ? 1 : 0;
+                const int sub_end = second ? (split ? 2 : 1) : (split ? 1 : MSUB);
+                if (!zero_tile && sub_begin < sub_end) {
+                    // the whole warp must agree before the .sync.aligned TMEM loads
+                    bool got;
+                    if (late_join && second) {
+                        // first-group warp q has seen the accumulator barrier of tile i complete
+                        got = true;
+                        uint32_t spins = 0;
+                        uint64_t t0 = 0;
+                        while (g0_tiles[q] < i + 1) {
+                            if ((++spins & 0xff) == 0) {
+                                const uint64_t now = globaltimer_ns();
+                                if (t0 == 0)
+                                    t0 = now;
+                                if (*abort_flag || now - t0 > p.wait_limit_ns) {
+                                    *abort_flag = 1;
+                                    got = false;
+                                    break;
+                                }
+                            }
+                        }
+                    } else {
+                        got = mbar_wait(tfull0 + 8 * acc, acc_ph, wc);
+                    }
+                    if (!__all_sync(0xffffffffu, got))
+                        break;
+                    tc_fence_after();
+                    if (late_join && !second) {
+                        tc_fence_before();
+                        if (lane == 0)
+                            g0_tiles[q] = i + 1;
+                    }
+                }
+#pragma unroll 1
+                for (int sub = sub_begin; sub < sub_end; ++sub) {
+                    const int sub_row = sub * 256 + static_cast<int>(crank) * BM;  // this CTA's rows of the sub-tile
+                    const uint32_t t_addr =
+                            tmem_base + (MSUB > 1 ? sub : acc) * BN + (static_cast<uint32_t>(q * 32) << 16);
+                    epilogue_tile<EPI>(p, tl, t_addr, sub_row + q * 32, lane, zero_tile, stage_warp, out);
+                    if (!zero_tile) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            const uint32_t eb = tempty0 + 8 * (MSUB > 1 ? sub : acc);
+                            if (PAIR && crank != 0)
+                                mbar_arrive_remote(mapa_u32(eb, 0));
+                            else
+                                mbar_arrive(eb);
+                        }
+                    }
+                    if (EPI == EPI_PUSH && p.fuse.rs_count_peer[0] != nullptr && tl.m0 + sub_row < p.M) {
+                        // this warp's 32 rows of the partial tile are in the owner's staging slot:
+                        // make them visible system-wide, then count them (4 counts per 128-row block)
+                        __syncwarp();
+                        if (lane == 0) {
+                            const int owner = (tl.m0 + sub_row) / p.rows_per_peer;
+                            __threadfence_system();
+                            red_release_sys_add(p.fuse.rs_count_peer[owner] + p.fuse.rank, 1u);
+                        }
+                    }
+                }
+                if (!zero_tile) {
+                    if (++acc == C::ACCS) {
+                        acc = 0;
+                        acc_ph ^= 1;
+                    }
+                }
+            }
+            // this thread's TMA stores have left shared memory before the CTA gives it up
+            if (lane == 0)
+                tma_store_wait<0>();
+        }
     }
     if (EPI == EPI_PUSH && p.fuse.rs_out != nullptr)
         reduce_scatter_tail(p.fuse, p.wait_limit_ns, abort_flag, comm_ok);
@@ -1158,10 +1229,15 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     // forward/backward), which need the 128-row tile.  Large dense problems take the
     // 512-row tile: less operand traffic per FLOP, at the price of an epilogue that is
     // only half hidden, which a long K loop amortises.
-    const bool pair = !grouped_m && a.variant != 1 && a.M > 128;
-    bool wide = pair && a.variant == 3;
-    // (the push epilogue's remote stores need the next tile's main loop to hide behind: pair tile)
-    if (pair && a.variant == 0 && !grouped_k && a.epilogue != EPI_PUSH) {
+    // MEGRAY_GEMM_VARIANT stands in for variant 0 (a tuning and test aid)
+    static const int env_variant = [] {
+        const char* e = getenv("MEGRAY_GEMM_VARIANT");
+        return e != nullptr ? atoi(e) : 0;
+    }();
+    const int variant = a.variant != 0 ? a.variant : env_variant;
+    const bool pair = !grouped_m && variant != 1 && a.M > 128;
+    bool wide = pair && variant == 3;
+    if (pair && variant == 0 && !grouped_k) {
         const long tiles_wide = static_cast<long>((a.M + 511) / 512) *
                                 ((a.N + (a.epilogue == EPI_SWIGLU ? 127 : 255)) / (a.epilogue == EPI_SWIGLU ? 128 : 256));
         wide = a.M >= 1024 && a.K >= 3072 && tiles_wide >= 2L * (sm_count() / 2);

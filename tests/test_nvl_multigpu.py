@@ -38,6 +38,21 @@ def test_tensor_parallel_model_matches_single_gpu():
     assert out.count("RANK_OK") == NPROC, out[-3000:]
 
 
+def test_tensor_parallel_model_on_the_wide_gemm_tile():
+    # the 512-row tile: per-sub-tile shard flags and owners, both epilogue groups, late-joining
+    # second group behind the fused all_gather
+    out = torchrun("tp_model.py", env={"MEGRAY_HEAP_MB": "1024", "MEGRAY_GEMM_VARIANT": "3"})
+    assert out.count("RANK_OK") == NPROC, out[-3000:]
+
+
+@pytest.mark.parametrize("variant", ["2", "3"])
+def test_fused_kernels_with_many_tiles_per_cta_pair(variant):
+    # the gather is still in flight while tiles retire; on the wide tile (variant 3) the second
+    # epilogue group joins in the middle of the tile sequence
+    out = torchrun("fused_many_tiles.py", env={"MEGRAY_HEAP_MB": "1024", "MEGRAY_GEMM_VARIANT": variant})
+    assert out.count("RANK_OK") == NPROC, out[-3000:]
+
+
 def test_expert_parallel_moe_matches_single_gpu():
     out = torchrun("moe.py", env={"MEGRAY_HEAP_MB": "1024"})
     assert out.count("RANK_OK") == NPROC, out[-3000:]
