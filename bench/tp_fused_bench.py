@@ -6,7 +6,7 @@
 For the all_gather -> GEMM (SwiGLU up/gate projection) and the GEMM -> reduce_scatter (down
 projection) of one layer it times, per rank, on the device with CUDA events (max over ranks):
 the GEMM alone on local data, the collective alone, collective + GEMM back to back, and the
-fused kernel.  The roofline of a fused kernel is the slower of FLOPs / measured GEMM peak and
+fused kernel (candidates launched in turn; median over --iters rounds).  The roofline of a fused kernel is the slower of FLOPs / measured GEMM peak and
 bytes over NVLink / measured link bandwidth (MEASURED_PEAKS.json and 770 GB/s per direction).
 """
 import argparse
@@ -55,33 +55,45 @@ def main():
         peak = json.load(open(pk)).get("bf16_tflops_sustained", peak)
     link = 770.0
 
-    def timed(fn):
-        for _ in range(2):
-            fn()
-        torch.cuda.synchronize()
-        comm.stream_barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(a.iters):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return max_over_ranks(comm, e0.elapsed_time(e1) / a.iters, dev)
-
     shard = xg[rank * Ts:(rank + 1) * Ts]
-    res = {}
-    res["gemm_up"] = timed(lambda: gemm(xg, w_gu, gu, epilogue=EPI_SWIGLU, out2=h, n=fl))
-    res["all_gather"] = timed(lambda: comm.all_gather(shard, xg))
-    tp.fused = False
-    res["ag+gemm"] = timed(lambda: tp.ag_gemm_swiglu(xg, w_gu, gu, h, fl))
-    tp.fused = True
-    res["ag_gemm_fused"] = timed(lambda: tp.ag_gemm_swiglu(xg, w_gu, gu, h, fl))
-    res["gemm_down"] = timed(lambda: gemm(h, w_dn, partial))
-    res["reduce_scatter"] = timed(lambda: comm.reduce_scatter(partial, out))
-    tp.fused = False
-    res["gemm+rs"] = timed(lambda: tp.gemm_rs(h, w_dn, partial, out))
-    tp.fused = True
-    res["gemm_rs_fused"] = timed(lambda: tp.gemm_rs(h, w_dn, None, out))
+
+    def unfused_up():
+        tp.fused = False
+        tp.ag_gemm_swiglu(xg, w_gu, gu, h, fl)
+        tp.fused = True
+
+    def unfused_down():
+        tp.fused = False
+        tp.gemm_rs(h, w_dn, partial, out)
+        tp.fused = True
+
+    cands = {
+        "gemm_up": lambda: gemm(xg, w_gu, gu, epilogue=EPI_SWIGLU, out2=h, n=fl),
+        "all_gather": lambda: comm.all_gather(shard, xg),
+        "ag+gemm": unfused_up,
+        "ag_gemm_fused": lambda: tp.ag_gemm_swiglu(xg, w_gu, gu, h, fl),
+        "gemm_down": lambda: gemm(h, w_dn, partial),
+        "reduce_scatter": lambda: comm.reduce_scatter(partial, out),
+        "gemm+rs": unfused_down,
+        "gemm_rs_fused": lambda: tp.gemm_rs(h, w_dn, None, out),
+    }
+    # candidates run in turn, one timed launch each per round, so that a drift of the
+    # power-capped clock hits all of them alike; median over the rounds, max over ranks
+    for _ in range(2):
+        for fn in cands.values():
+            fn()
+    times = {k: [] for k in cands}
+    for _ in range(a.iters):
+        for k, fn in cands.items():
+            torch.cuda.synchronize()
+            comm.stream_barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times[k].append(e0.elapsed_time(e1))
+    res = {k: max_over_ranks(comm, sorted(v)[len(v) // 2], dev) for k, v in times.items()}
     if rank == 0:
         fl_up = 2.0 * T * 2 * fl * d
         fl_dn = 2.0 * T * d * fl
