@@ -105,6 +105,12 @@ void megray_nvl_set_device_timeout_ms(void* comm, int64_t ms);
 
 /* ---- host arithmetic (the oracle) and stand-alone device reduction ----------------------- */
 int megray_cpu_reduce_n(const void* const* in, int n_in, void* out, size_t len, int dtype, int op);
+/* Second oracle: replays the reference's ring all_reduce / binomial-tree reduce schedules over
+ * host buffers (every pairwise step rounded to the element type). */
+int megray_oracle_ring_all_reduce(const void* const* in, void* const* out, int nranks, size_t len, int dtype,
+                                  int op);
+int megray_oracle_tree_reduce(const void* const* in, void* out, int nranks, int root, size_t len, int dtype,
+                              int op);
 int megray_cpu_reduce_scale_cast(const void* const* in, int n_in, int in_dtype, void* out,
                                  int out_dtype, size_t len, int op, double scale);
 int megray_reduce_n(const void* const* in, int n_in, void* out, size_t len, int in_dtype,

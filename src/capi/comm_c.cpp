@@ -4,6 +4,7 @@
 #include <string.h>
 
 #include "host/cpu_reduce.h"
+#include "host/schedule_oracle.h"
 #include "host/host_communicator.h"
 #include "kernels/collectives.cuh"
 #include "megray.h"
@@ -202,6 +203,16 @@ void megray_nvl_set_device_timeout_ms(void* comm, int64_t ms) {
 
 int megray_cpu_reduce_n(const void* const* in, int n_in, void* out, size_t len, int dtype, int op) {
     return host::cpu_reduce_n(in, n_in, out, len, static_cast<DType>(dtype), static_cast<ReduceOp>(op));
+}
+int megray_oracle_ring_all_reduce(const void* const* in, void* const* out, int nranks, size_t len, int dtype,
+                                  int op) {
+    return host::ring_all_reduce_schedule(in, out, nranks, len, static_cast<DType>(dtype),
+                                          static_cast<ReduceOp>(op));
+}
+int megray_oracle_tree_reduce(const void* const* in, void* out, int nranks, int root, size_t len, int dtype,
+                              int op) {
+    return host::tree_reduce_schedule(in, out, nranks, root, len, static_cast<DType>(dtype),
+                                      static_cast<ReduceOp>(op));
 }
 int megray_cpu_reduce_scale_cast(const void* const* in, int n_in, int in_dtype, void* out, int out_dtype,
                                  size_t len, int op, double scale) {
