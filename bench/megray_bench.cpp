@@ -52,6 +52,7 @@ struct BenchOptions {
     bool json = false;
     bool check = false;
     bool heap = false;  // NVL backend: buffers from the symmetric heap (zero-copy / NVSwitch kernels)
+    bool reg = false;   // NVL backend: cudaMalloc buffers registered with the communicator (zero-copy)
 };
 
 const char* kAllFuncs[] = {"send_recv", "scatter", "gather", "all_to_all", "all_gather",
@@ -198,6 +199,17 @@ std::vector<Result> run_sizes(const BenchOptions& o, const std::string& func, Ba
                 CK(cudaMalloc(&in, max_len * dt.size * (wide_in ? n : 1)));
                 CK(cudaMalloc(&out, max_len * dt.size * (wide_out ? n : 1)));
             }
+#ifndef MEGRAY_BENCH_REFERENCE
+            bool registered = false;
+            if (!from_heap && o.reg && backend == MEGRAY_NVL) {
+                NvlInterface* nvl = as_nvl(comm.get());
+                const Status s1 = nvl->register_buffer(in, max_len * dt.size * (wide_in ? n : 1));
+                const Status s2 = nvl->register_buffer(out, max_len * dt.size * (wide_out ? n : 1));
+                registered = s1 == MEGRAY_OK && s2 == MEGRAY_OK;
+                if (!registered && r == 0)
+                    fprintf(stderr, "buffers could not be registered: staged paths\n");
+            }
+#endif
             CK(cudaMemset(in, r + 1, max_len * dt.size * (wide_in ? n : 1)));
             CK(cudaMemset(out, 0, max_len * dt.size * (wide_out ? n : 1)));
             cudaEvent_t e0, e1;
@@ -247,6 +259,13 @@ std::vector<Result> run_sizes(const BenchOptions& o, const std::string& func, Ba
                 }
                 bar.wait();
             }
+#ifndef MEGRAY_BENCH_REFERENCE
+            if (registered) {
+                NvlInterface* nvl = as_nvl(comm.get());
+                nvl->deregister_buffer(out);
+                nvl->deregister_buffer(in);
+            }
+#endif
             comm.reset();
             cudaEventDestroy(e0);
             cudaEventDestroy(e1);
@@ -269,6 +288,7 @@ std::vector<Result> run_sizes(const BenchOptions& o, const std::string& func, Ba
 void usage() {
     printf("megray_bench [-d devices] [-e nccl,nvl] [-f all_reduce,...|all] [-s 1K:1G | 8,1024,...]\n"
            "             [-t dtype] [-o sum|max|min] [-w warmup] [-i iters] [-j] [-c] [-H (NVL: symmetric-heap buffers)]\n"
+           "             [-R (NVL: register the cudaMalloc buffers with the communicator)]\n"
            "             [-I master_ip] [-P port] [-n nodes] [-r node_rank]\n");
 }
 
@@ -280,7 +300,7 @@ int main(int argc, char** argv) {
     std::string backends = "nccl";
     std::string funcs = "all";
     int c;
-    while ((c = getopt(argc, argv, "d:I:P:n:r:e:f:s:w:i:t:o:jcHh")) != -1) {
+    while ((c = getopt(argc, argv, "d:I:P:n:r:e:f:s:w:i:t:o:jcHRh")) != -1) {
         switch (c) {
             case 'd': o.devices = atoi(optarg); break;
             case 'I': o.master_ip = optarg; break;
@@ -297,6 +317,7 @@ int main(int argc, char** argv) {
             case 'j': o.json = true; break;
             case 'c': o.check = true; break;
             case 'H': o.heap = true; break;
+            case 'R': o.reg = true; break;
             default: usage(); return c == 'h' ? 0 : 1;
         }
     }

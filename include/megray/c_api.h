@@ -96,6 +96,9 @@ void megray_host_set_timeout_ms(void* comm, int64_t ms);
 void* megray_nvl_alloc(void* comm, size_t bytes, size_t* offset_out);
 int megray_nvl_free(void* comm, void* ptr);
 void* megray_nvl_peer_ptr(void* comm, void* ptr, uint32_t peer);
+/* Collective: make ordinary device memory reachable by the peers' kernels (single-pass paths). */
+int megray_nvl_register(void* comm, void* ptr, size_t bytes);
+int megray_nvl_deregister(void* comm, void* ptr);
 void* megray_nvl_heap_base(void* comm, uint32_t peer);
 size_t megray_nvl_heap_bytes(void* comm);
 int megray_nvl_all_reduce_scaled(void* comm, const void* send, void* recv, size_t len, int in_dtype,

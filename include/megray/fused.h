@@ -39,6 +39,22 @@ public:
     virtual void* heap_base(uint32_t peer) = 0;
 
     /**
+     * Collective.  Makes [ptr, ptr + bytes), ordinary device memory of this rank (cudaMalloc, a
+     * framework's caching allocator), directly reachable by the kernels of every peer, so that
+     * collectives on it take the single-pass paths instead of staging through the heap.
+     * Every rank calls it with its own buffer, in the same order; a collective then qualifies
+     * when each rank passes an address at the same distance from the start of its registered
+     * range.  Peers in the same process use the address as it is (peer access is enabled);
+     * peers in other processes map it through a CUDA IPC handle, which exists for cudaMalloc
+     * memory only: if any rank's memory has none, every rank gets MEGRAY_NOT_IMPLEMENTED and
+     * the buffer keeps working through the staged paths.
+     */
+    virtual Status register_buffer(void* ptr, size_t bytes) = 0;
+    /** Collective.  Drops the registration that starts at `ptr` (and this rank's mappings of
+     *  the peers' buffers registered in the same call). */
+    virtual Status deregister_buffer(void* ptr) = 0;
+
+    /**
      * out = cast<out_dtype>(scale * reduce_op(in over ranks)): the gradient-bucket path.
      * Floating dtypes (fp16, bf16, fp32; fp64 with out_dtype == in_dtype); scale applies to SUM.
      */

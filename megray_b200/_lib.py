@@ -102,6 +102,8 @@ def _declare(lib) -> None:
     d("megray_nvl_alloc", vp, vp, sz, P(sz))
     d("megray_nvl_free", i32, vp, vp)
     d("megray_nvl_peer_ptr", vp, vp, vp, u32)
+    d("megray_nvl_register", i32, vp, vp, C.c_size_t)
+    d("megray_nvl_deregister", i32, vp, vp)
     d("megray_nvl_heap_base", vp, vp, u32)
     d("megray_nvl_heap_bytes", sz, vp)
     d("megray_nvl_all_reduce_scaled", i32, vp, vp, vp, sz, i32, i32, C.c_float, i32, vp)

@@ -338,6 +338,23 @@ class Communicator:
     def sym_free(self, tensor) -> None:
         _check(self._lib.megray_nvl_free(self._h, C.c_void_p(tensor.data_ptr())), "sym_free")
 
+    def register(self, tensor) -> bool:
+        """Collective.  Makes an ordinary CUDA tensor (not from ``sym_empty``) directly reachable
+        by the peers' kernels, so that collectives on it (and on views that start at the same
+        distance from its beginning on every rank) take the single-pass paths.  Every rank
+        registers its own tensor of the same size, in the same order.  Returns False, on every
+        rank, when some rank's memory cannot be shared (the staged paths keep working)."""
+        rc = self._lib.megray_nvl_register(self._h, C.c_void_p(tensor.data_ptr()),
+                                           tensor.numel() * tensor.element_size())
+        if rc == 9:  # MEGRAY_NOT_IMPLEMENTED: no IPC handle for this memory
+            return False
+        _check(rc, "register")
+        return True
+
+    def deregister(self, tensor) -> None:
+        """Collective.  Drops the registration made with :meth:`register`."""
+        _check(self._lib.megray_nvl_deregister(self._h, C.c_void_p(tensor.data_ptr())), "deregister")
+
     def peer_ptr(self, tensor, peer: int) -> int:
         p = self._lib.megray_nvl_peer_ptr(self._h, C.c_void_p(tensor.data_ptr()), peer)
         if not p:

@@ -173,6 +173,14 @@ void* megray_nvl_peer_ptr(void* comm, void* ptr, uint32_t peer) {
     NvlInterface* n = as_nvl(C(comm));
     return n ? n->peer_ptr(ptr, peer) : nullptr;
 }
+int megray_nvl_register(void* comm, void* ptr, size_t bytes) {
+    NvlInterface* n = as_nvl(C(comm));
+    return n ? n->register_buffer(ptr, bytes) : MEGRAY_INVALID_USAGE;
+}
+int megray_nvl_deregister(void* comm, void* ptr) {
+    NvlInterface* n = as_nvl(C(comm));
+    return n ? n->deregister_buffer(ptr) : MEGRAY_INVALID_USAGE;
+}
 void* megray_nvl_heap_base(void* comm, uint32_t peer) {
     NvlInterface* n = as_nvl(C(comm));
     return n ? n->heap_base(peer) : nullptr;

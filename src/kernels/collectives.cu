@@ -437,10 +437,11 @@ __device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, uint64_
     const bool do_scale = IsFloatAcc<A>::value && OP == MegRay::MEGRAY_SUM && a.scale != 1.0f;
     const bool to_all = a.kind == DIRECT_ALL_REDUCE;
     const uint64_t nvec = (e - b) / V;
-    const uint64_t in_byte0 = a.in_off + (elem0 + b) * sizeof(Tin);
+    // byte positions relative to the start of every rank's input / output buffer
+    const uint64_t in_byte0 = (elem0 + b) * sizeof(Tin);
     // all_reduce writes the slice back at the same element positions; reduce_scatter writes the
     // slice to the start of the local result
-    const uint64_t out_byte0 = to_all ? a.out_off + (elem0 + b) * sizeof(Tout) : b * sizeof(Tout);
+    const uint64_t out_byte0 = to_all ? (elem0 + b) * sizeof(Tout) : b * sizeof(Tout);
     // U independent vectors per thread and iteration: all their loads are issued before the
     // first use, which is what keeps enough bytes in flight to fill the links
     constexpr int U = NVLS ? 4 : 2;
@@ -452,7 +453,7 @@ __device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, uint64_
             for (int u = 0; u < U; ++u) {
                 const uint64_t i = i0 + static_cast<uint64_t>(u) * blockDim.x;
                 if (i < nvec)
-                    raw[u] = mc_ld_reduce<Tin, OP>(a.mc_base + in_byte0 + i * 16);
+                    raw[u] = mc_ld_reduce<Tin, OP>(a.mc_base + a.in_off + in_byte0 + i * 16);
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -469,7 +470,7 @@ __device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, uint64_
 #pragma unroll
                 for (int q = 0; q < kMaxRanks; ++q)
                     if (q < n && i < nvec)
-                        raw[u][q] = ld_cg_v4(a.c.peers.heap[q] + in_byte0 + i * 16);
+                        raw[u][q] = ld_cg_v4(a.in_base[q] + in_byte0 + i * 16);
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -506,7 +507,7 @@ __device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, uint64_
                     *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
                 }
             } else if (NVLS) {
-                char* dst = a.mc_base + out_byte0 + i * OB;
+                char* dst = a.mc_base + a.out_off + out_byte0 + i * OB;
                 if (OB >= 16) {
 #pragma unroll
                     for (int w = 0; w < OB / 16; ++w)
@@ -518,7 +519,7 @@ __device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, uint64_
 #pragma unroll
                 for (int q = 0; q < kMaxRanks; ++q) {
                     if (q < n) {
-                        char* dst = a.c.peers.heap[(a.c.rank + q) % n] + out_byte0 + i * OB;
+                        char* dst = a.out_base[(a.c.rank + q) % n] + out_byte0 + i * OB;
                         if (OB >= 16) {
 #pragma unroll
                             for (int w = 0; w < OB / 16; ++w)
@@ -533,9 +534,9 @@ __device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, uint64_
     }
     // element tail (fewer than V elements): plain peer accesses
     for (uint64_t i = b + nvec * V + threadIdx.x; i < e; i += blockDim.x) {
-        A acc = widen<Tin>(reinterpret_cast<const Tin*>(a.c.peers.heap[0] + a.in_off)[elem0 + i]);
+        A acc = widen<Tin>(reinterpret_cast<const Tin*>(a.in_base[0])[elem0 + i]);
         for (int q = 1; q < n; ++q)
-            acc = combine<OP, A>(acc, widen<Tin>(reinterpret_cast<const Tin*>(a.c.peers.heap[q] + a.in_off)[elem0 + i]));
+            acc = combine<OP, A>(acc, widen<Tin>(reinterpret_cast<const Tin*>(a.in_base[q])[elem0 + i]));
         if (do_scale)
             acc = static_cast<A>(acc * static_cast<A>(a.scale));
         const Tout o = narrow<Tout, A>(acc);
@@ -543,7 +544,7 @@ __device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, uint64_
             static_cast<Tout*>(a.out_local)[i] = o;
         } else {
             for (int q = 0; q < n; ++q)
-                reinterpret_cast<Tout*>(a.c.peers.heap[q] + a.out_off)[elem0 + i] = o;
+                reinterpret_cast<Tout*>(a.out_base[q])[elem0 + i] = o;
         }
     }
 }
@@ -563,18 +564,18 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
         const uint64_t per_cta = round_up_u64((bytes + gridDim.x - 1) / gridDim.x, 16);
         const uint64_t b = min(bytes, per_cta * blockIdx.x), e = min(bytes, b + per_cta);
         const char* src = static_cast<const char*>(a.in_local);
-        if (NVLS && ((reinterpret_cast<uintptr_t>(src) | (a.out_off + rank * bytes)) & 15) == 0) {
+        if (NVLS && ((reinterpret_cast<uintptr_t>(src) | (a.out_off + rank * bytes)) & 15) == 0) {  // (heap-resident output)
             char* dst = a.mc_base + a.out_off + rank * bytes;
             const uint64_t nv = (e - b) / 16;
             for (uint64_t i = threadIdx.x; i < nv; i += blockDim.x)
                 mc_st_v4(dst + b + i * 16, ld_cg_v4(src + b + i * 16));
             for (uint64_t k = b + nv * 16 + threadIdx.x; k < e; k += blockDim.x)
                 for (int q = 0; q < n; ++q)
-                    (c.peers.heap[q] + a.out_off + rank * bytes)[k] = src[k];
+                    (a.out_base[q] + rank * bytes)[k] = src[k];
         } else {
             for (int qq = 0; qq < n; ++qq) {
                 const int q = (rank + qq) % n;
-                cta_copy(c.peers.heap[q] + a.out_off + rank * bytes + b, src + b, e - b);
+                cta_copy(a.out_base[q] + rank * bytes + b, src + b, e - b);
             }
         }
     } else if (a.kind == DIRECT_ALL_TO_ALL) {
@@ -585,7 +586,7 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
         const char* src = static_cast<const char*>(a.in_local);
         for (int qq = 1; qq <= n; ++qq) {
             const int q = (rank + qq) % n;
-            cta_copy(c.peers.heap[q] + a.out_off + rank * bytes + b, src + q * bytes + b, e - b);
+            cta_copy(a.out_base[q] + rank * bytes + b, src + q * bytes + b, e - b);
         }
     } else {
         // slice `rank`: all_reduce splits len into n slices of se elements, reduce_scatter's

@@ -113,8 +113,13 @@ enum DirectKind : int {
 struct DirectArgs {
     CommonArgs c;
     int kind;
-    uint64_t in_off;       // heap offset of the input (all_reduce, reduce_scatter)
-    uint64_t out_off;      // heap offset of the output (all_reduce, all_gather)
+    // every rank's input (all_reduce, reduce_scatter) and output (all_reduce, all_gather,
+    // all_to_all) buffer as mapped in this rank's address space: heap addresses, or peer mappings
+    // of buffers registered with the communicator
+    const char* in_base[kMaxRanks];
+    char* out_base[kMaxRanks];
+    uint64_t in_off;       // heap offset of the input: the multimem address is mc_base + in_off
+    uint64_t out_off;      // heap offset of the output
     const void* in_local;  // all_gather / all_to_all: this rank's input (any device memory)
     void* out_local;       // reduce_scatter: this rank's result (any device memory)
     uint64_t len;          // all_reduce: total elements; others: elements per rank

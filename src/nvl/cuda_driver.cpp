@@ -46,6 +46,7 @@ const Api* api() {
         ok &= resolve("cuMemExportToShareableHandle", g_api.MemExportToShareableHandle);
         ok &= resolve("cuMemImportFromShareableHandle", g_api.MemImportFromShareableHandle);
         ok &= resolve("cuDeviceGetAttribute", g_api.DeviceGetAttribute);
+        ok &= resolve("cuMemGetAddressRange", g_api.MemGetAddressRange);
         resolve("cuMulticastCreate", g_api.MulticastCreate, false);
         resolve("cuMulticastAddDevice", g_api.MulticastAddDevice, false);
         resolve("cuMulticastBindMem", g_api.MulticastBindMem, false);

@@ -26,6 +26,7 @@ struct Api {
     CUresult (*MemImportFromShareableHandle)(CUmemGenericAllocationHandle*, void*,
                                              CUmemAllocationHandleType);
     CUresult (*DeviceGetAttribute)(int*, CUdevice_attribute, CUdevice);
+    CUresult (*MemGetAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr);
     CUresult (*MulticastCreate)(CUmemGenericAllocationHandle*, const CUmulticastObjectProp*);
     CUresult (*MulticastAddDevice)(CUmemGenericAllocationHandle, CUdevice);
     CUresult (*MulticastBindMem)(CUmemGenericAllocationHandle, size_t, CUmemGenericAllocationHandle,

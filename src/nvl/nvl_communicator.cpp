@@ -119,6 +119,9 @@ NvlCommunicator::~NvlCommunicator() {
     // peers may still be inside their last kernel reading this rank's heap: meet first
     if (m_ready && m_client && m_client->connected() && !m_aborted.load())
         m_client->barrier();
+    for (Registration& r : m_regs)
+        drop_registration(r);
+    m_regs.clear();
     m_heap.destroy();
 }
 
@@ -283,8 +286,12 @@ int NvlCommunicator::pick_ctas(size_t bytes) const {
 
 // ------------------------------------------------------------------ direct (zero-copy) paths
 
+// True if every peer's kernels can address [p, p + bytes): it lies in the symmetric heap or in a
+// registered buffer (and is 16-byte aligned).
 bool NvlCommunicator::aligned_heap(const void* p, size_t bytes) {
-    return in_heap(p, bytes) && (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+    char* base[mgk::coll::kMaxRanks];
+    size_t off;
+    return peer_view(p, bytes, base, &off);
 }
 
 Status NvlCommunicator::direct_launch(int kind, const void* in, void* out, size_t len, DType in_dtype,
@@ -299,23 +306,36 @@ Status NvlCommunicator::direct_launch(int kind, const void* in, void* out, size_
     a.out_dtype = out_dtype;
     a.op = op;
     size_t bytes = len * get_dtype_size(in_dtype);
+    size_t in_off = SIZE_MAX, out_off = SIZE_MAX;
+    char* in_base[mgk::coll::kMaxRanks] = {};
+    bool ok = true;
     if (kind == mgk::coll::DIRECT_ALL_GATHER || kind == mgk::coll::DIRECT_ALL_TO_ALL) {
         a.in_local = in;
-        a.out_off = static_cast<size_t>(static_cast<char*>(out) - m_heap.local());
         bytes *= m_nranks;
+        ok = peer_view(out, bytes, a.out_base, &out_off);
+        in_off = 0;  // (no multimem load on these paths)
     } else {
-        a.in_off = static_cast<size_t>(static_cast<const char*>(in) - m_heap.local());
-        if (kind == mgk::coll::DIRECT_ALL_REDUCE)
-            a.out_off = static_cast<size_t>(static_cast<char*>(out) - m_heap.local());
-        else {
+        const size_t in_bytes = kind == mgk::coll::DIRECT_ALL_REDUCE ? bytes : bytes * m_nranks;
+        ok = peer_view(in, in_bytes, in_base, &in_off);
+        for (uint32_t q = 0; q < m_nranks; ++q)
+            a.in_base[q] = in_base[q];
+        if (kind == mgk::coll::DIRECT_ALL_REDUCE) {
+            ok = ok && peer_view(out, len * get_dtype_size(out_dtype), a.out_base, &out_off);
+        } else {
             a.out_local = out;
+            out_off = 0;
             bytes *= m_nranks;
         }
     }
-    const bool nvls = m_heap.multicast() != nullptr && bytes >= m_nvls_min_bytes &&
-                      kind != mgk::coll::DIRECT_ALL_TO_ALL &&
+    if (!ok)
+        return MEGRAY_INVALID_ARGUMENT;
+    // the NVSwitch paths need both buffers inside the multicast-mapped heap
+    const bool nvls = m_heap.multicast() != nullptr && in_off != SIZE_MAX && out_off != SIZE_MAX &&
+                      bytes >= m_nvls_min_bytes && kind != mgk::coll::DIRECT_ALL_TO_ALL &&
                       (kind == mgk::coll::DIRECT_ALL_GATHER || mgk::coll::nvls_supports(in_dtype, out_dtype, op));
     a.mc_base = nvls ? m_heap.multicast() : nullptr;
+    a.in_off = nvls ? in_off : 0;
+    a.out_off = nvls ? out_off : 0;
     // single-pass kernels are latency-bound per CTA: smaller shares, more CTAs
     const int ctas = static_cast<int>(std::min<size_t>(std::max<size_t>(1, bytes / (32u << 10)),
                                                        static_cast<size_t>(2 * m_max_ctas > kMaxCtas ? kMaxCtas : 2 * m_max_ctas)));
@@ -819,6 +839,147 @@ bool NvlCommunicator::in_heap(const void* ptr, size_t bytes) {
         return false;
     const char* p = static_cast<const char*>(ptr);
     return p >= m_heap.local() && p + bytes <= m_heap.local() + m_heap.bytes();
+}
+
+// ------------------------------------------------------------------ registered user buffers
+
+namespace {
+// What the ranks tell each other about the buffers they register in one call.
+struct RegInfo {
+    int32_t pid;
+    int32_t device;
+    int32_t ok;       // 0: this rank could not export its buffer
+    int32_t pad;
+    uint64_t ptr;     // the buffer as its owner addresses it
+    uint64_t bytes;
+    uint64_t offset;  // distance of `ptr` from the start of its allocation (what an IPC handle maps)
+    cudaIpcMemHandle_t handle;
+};
+}  // namespace
+
+bool NvlCommunicator::peer_view(const void* p, size_t bytes, char** base, size_t* heap_off) {
+    if (!m_ready || p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) != 0)
+        return false;
+    const char* c = static_cast<const char*>(p);
+    if (in_heap(p, bytes)) {
+        const size_t off = static_cast<size_t>(c - m_heap.local());
+        for (uint32_t q = 0; q < m_nranks; ++q)
+            base[q] = m_heap.base(q) + off;
+        *heap_off = off;
+        return true;
+    }
+    for (const Registration& r : m_regs) {
+        if (c >= r.local && c + bytes <= r.local + r.bytes) {
+            const size_t off = static_cast<size_t>(c - r.local);
+            for (uint32_t q = 0; q < m_nranks; ++q)
+                base[q] = r.peer[q] + off;
+            *heap_off = SIZE_MAX;
+            return true;
+        }
+    }
+    return false;
+}
+
+void NvlCommunicator::drop_registration(Registration& r) {
+    for (void* b : r.ipc_bases)
+        cudaIpcCloseMemHandle(b);
+    r.ipc_bases.clear();
+}
+
+Status NvlCommunicator::register_buffer(void* ptr, size_t bytes) {
+    if (!m_ready || ptr == nullptr || bytes == 0)
+        return MEGRAY_INVALID_ARGUMENT;
+    const drv::Api* api = drv::api();
+    std::vector<RegInfo> all(m_nranks);
+    RegInfo mine;
+    memset(&mine, 0, sizeof(mine));
+    mine.pid = static_cast<int32_t>(getpid());
+    mine.device = m_heap.device();
+    mine.ptr = reinterpret_cast<uint64_t>(ptr);
+    mine.bytes = bytes;
+    mine.ok = 1;
+    CUdeviceptr alloc_base = 0;
+    size_t alloc_size = 0;
+    if (api == nullptr ||
+        api->MemGetAddressRange(&alloc_base, &alloc_size, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS ||
+        reinterpret_cast<CUdeviceptr>(ptr) + bytes > alloc_base + alloc_size) {
+        mine.ok = 0;  // not one device allocation
+    } else {
+        mine.offset = reinterpret_cast<CUdeviceptr>(ptr) - alloc_base;
+        // only needed by peers in other processes; memory without an IPC handle (virtual memory
+        // management allocations) still works between ranks of one process
+        if (cudaIpcGetMemHandle(&mine.handle, reinterpret_cast<void*>(alloc_base)) != cudaSuccess) {
+            (void)cudaGetLastError();
+            mine.ok = 2;  // usable inside this process only
+        }
+    }
+    MEGRAY_CHECK(m_client->allgather(&mine, all.data(), sizeof(RegInfo)));
+    bool usable = true;
+    for (uint32_t q = 0; q < m_nranks; ++q) {
+        if (all[q].ok == 0)
+            usable = false;
+        if (all[q].ok == 2 && all[q].pid != mine.pid)
+            usable = false;
+        if (all[q].bytes != bytes)
+            usable = false;
+    }
+    Registration r;
+    r.local = static_cast<char*>(ptr);
+    r.bytes = bytes;
+    int32_t opened_ok = usable ? 1 : 0;
+    if (usable) {
+        for (uint32_t q = 0; q < m_nranks && opened_ok; ++q) {
+            if (q == m_rank) {
+                r.peer[q] = r.local;
+            } else if (all[q].pid == mine.pid) {
+                // the same address space: the peer's address is valid here once peer access is on
+                cudaError_t e = cudaDeviceEnablePeerAccess(all[q].device, 0);
+                if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled)
+                    opened_ok = 0;
+                (void)cudaGetLastError();
+                r.peer[q] = reinterpret_cast<char*>(all[q].ptr);
+            } else {
+                void* base = nullptr;
+                cudaError_t e = cudaIpcOpenMemHandle(&base, all[q].handle, cudaIpcMemLazyEnablePeerAccess);
+                if (e != cudaSuccess) {
+                    (void)cudaGetLastError();
+                    opened_ok = 0;
+                } else {
+                    r.ipc_bases.push_back(base);
+                    r.peer[q] = static_cast<char*>(base) + all[q].offset;
+                }
+            }
+        }
+    }
+    // all or nothing: a rank that could not map a peer makes everyone fall back
+    std::vector<int32_t> oks(m_nranks);
+    MEGRAY_CHECK(m_client->allgather(&opened_ok, oks.data(), sizeof(int32_t)));
+    for (uint32_t q = 0; q < m_nranks; ++q)
+        if (!oks[q])
+            usable = false;
+    if (!usable) {
+        drop_registration(r);
+        MEGRAY_INFO("register_buffer: %p (%zu bytes) stays on the staged paths", ptr, bytes);
+        return MEGRAY_NOT_IMPLEMENTED;
+    }
+    m_regs.push_back(std::move(r));
+    return MEGRAY_OK;
+}
+
+Status NvlCommunicator::deregister_buffer(void* ptr) {
+    if (!m_ready)
+        return MEGRAY_INVALID_ARGUMENT;
+    // peers may still be reading or writing this buffer from their last kernel
+    cudaDeviceSynchronize();
+    MEGRAY_CHECK(m_client->barrier());
+    for (size_t i = 0; i < m_regs.size(); ++i) {
+        if (m_regs[i].local == static_cast<char*>(ptr)) {
+            drop_registration(m_regs[i]);
+            m_regs.erase(m_regs.begin() + static_cast<long>(i));
+            return MEGRAY_OK;
+        }
+    }
+    return MEGRAY_INVALID_ARGUMENT;
 }
 
 }  // namespace MegRay

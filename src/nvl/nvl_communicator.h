@@ -65,6 +65,8 @@ public:
     bool in_heap(const void* ptr, size_t bytes) override;
     size_t heap_bytes() override { return m_heap.bytes(); }
     void* heap_base(uint32_t peer) override { return m_heap.base(peer); }
+    Status register_buffer(void* ptr, size_t bytes) override;
+    Status deregister_buffer(void* ptr) override;
     Status all_reduce_scaled(const void* sendbuff, void* recvbuff, size_t len, DType in_dtype,
                              DType out_dtype, float scale, ReduceOp op,
                              std::shared_ptr<Context> ctx) override;
@@ -96,6 +98,18 @@ private:
     void after_launch(cudaStream_t stream);
     int pick_ctas(size_t bytes) const;
     bool aligned_heap(const void* p, size_t bytes);
+    // A user buffer registered with register_buffer(): this rank's range and every rank's twin.
+    struct Registration {
+        char* local = nullptr;
+        size_t bytes = 0;
+        char* peer[mgk::coll::kMaxRanks] = {};
+        std::vector<void*> ipc_bases;  // mappings opened for this registration (other processes)
+    };
+    // Fills base[q] with rank q's twin of [p, p + bytes) when p is 16-byte aligned and lies in
+    // the symmetric heap or in a registered range; `heap_off` receives the heap offset or
+    // SIZE_MAX for a registered buffer.
+    bool peer_view(const void* p, size_t bytes, char** base, size_t* heap_off);
+    void drop_registration(Registration& r);
     Status direct_launch(int kind, const void* in, void* out, size_t len, DType in_dtype, DType out_dtype,
                          float scale, ReduceOp op, cudaStream_t stream);
     Status check_cuda(cudaError_t e);
@@ -108,6 +122,7 @@ private:
     size_t m_user_off = 0;   // first byte of the symmetric allocator's area
     size_t m_user_top = 0;   // bump pointer
     std::vector<size_t> m_allocs;
+    std::vector<Registration> m_regs;
     uint32_t m_epoch = 0;
     int m_parity = 0;
     uint64_t m_timeout_ns;

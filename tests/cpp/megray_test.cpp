@@ -411,6 +411,53 @@ TEST(Nvl_SymmetricAllocAndScaledAllReduce) {
     });
 }
 
+// Ranks as threads of one process: a registered cudaMalloc buffer is reached by its plain
+// address once peer access is enabled (no IPC handle involved).
+TEST(Nvl_RegisteredUserBuffersTakeTheSinglePassKernels) {
+    const int n = std::min(gpu_count(), 4);
+    if (n < 2) SKIP("needs two GPUs");
+    Server server(n);
+    run_ranks(n, [&](int rank) {
+        Env env(true, rank);
+        auto comm = get_communicator(n, rank, MEGRAY_NVL);
+        ASSERT_TRUE(comm->init("127.0.0.1", server.port()) == MEGRAY_OK);
+        NvlInterface* nvl = as_nvl(comm.get());
+        ASSERT_TRUE(nvl != nullptr);
+        const size_t len = (1u << 20) + 8;  // above the one-shot limit
+        std::vector<float> in(len), out(len, 0.f);
+        for (size_t j = 0; j < len; ++j) in[j] = static_cast<float>((rank + 1) * (1 + j % 7));
+        void* d_in = env.alloc(len * 4);
+        void* d_out = env.alloc(len * 4);
+        void* d_gather = env.alloc(len * 4 * n);
+        env.put(d_in, in.data(), len * 4);
+        ASSERT_TRUE(nvl->register_buffer(d_in, len * 4) == MEGRAY_OK);
+        ASSERT_TRUE(nvl->register_buffer(d_out, len * 4) == MEGRAY_OK);
+        ASSERT_TRUE(nvl->register_buffer(d_gather, len * 4 * n) == MEGRAY_OK);
+        const CommStats before = comm->stats();
+        ASSERT_TRUE(comm->all_reduce(d_in, d_out, len, MEGRAY_FLOAT32, MEGRAY_SUM, env.ctx) == MEGRAY_OK);
+        env.get(out.data(), d_out, len * 4);
+        const float tri = n * (n + 1) / 2.0f;
+        size_t wrong = 0;
+        for (size_t j = 0; j < len; ++j) wrong += out[j] != tri * (1 + j % 7);
+        EXPECT_EQ(wrong, 0u);
+        ASSERT_TRUE(comm->all_gather(d_in, d_gather, len, MEGRAY_FLOAT32, env.ctx) == MEGRAY_OK);
+        std::vector<float> all(len * n);
+        env.get(all.data(), d_gather, len * 4 * n);
+        wrong = 0;
+        for (int q = 0; q < n; ++q)
+            for (size_t j = 0; j < len; j += 997) wrong += all[q * len + j] != static_cast<float>((q + 1) * (1 + j % 7));
+        EXPECT_EQ(wrong, 0u);
+        EXPECT_TRUE(comm->stats().calls >= before.calls + 2);
+        EXPECT_EQ(nvl->deregister_buffer(d_gather), MEGRAY_OK);
+        EXPECT_EQ(nvl->deregister_buffer(d_out), MEGRAY_OK);
+        EXPECT_EQ(nvl->deregister_buffer(d_in), MEGRAY_OK);
+        EXPECT_TRUE(nvl->deregister_buffer(d_in) != MEGRAY_OK);
+        env.release(d_in);
+        env.release(d_out);
+        env.release(d_gather);
+    });
+}
+
 int main(int argc, char** argv) {
     setenv("NCCL_LAUNCH_MODE", "PARALLEL", 0);
     return mini::run_all(argc > 1 ? argv[1] : nullptr);

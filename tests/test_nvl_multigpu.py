@@ -65,6 +65,11 @@ def test_single_pass_collectives_on_heap_tensors():
     assert "nvls_calls=0" in out
 
 
+def test_single_pass_collectives_on_registered_user_buffers():
+    out = torchrun("registered.py")
+    assert out.count("RANK_OK") == NPROC, out[-3000:]
+
+
 def test_single_pass_collectives_through_nvswitch_multimem():
     # falls back to peer loads/stores (with a warning) where multicast is unavailable
     out = torchrun("direct.py", env={"MEGRAY_HEAP_MB": "4096", "MEGRAY_NVLS": "1", "NCCL_NVLS_ENABLE": "1"})
