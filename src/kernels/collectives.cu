@@ -352,6 +352,21 @@ __global__ void __launch_bounds__(512) exchange_family_kernel(const ExchangeArgs
     };
     uint32_t epoch = c.epoch;
 
+    if (a.push_all) {
+        uint64_t b, e;
+        sub_range(a.chunk_bytes, &b, &e);
+        for (int jj = 0; jj < n; ++jj) {
+            const int j = (rank + 1 + jj) % n;
+            cta_copy(c.peers.heap[j] + a.pub_off + rank * chunk_stride + b,
+                     in + static_cast<uint64_t>(a.push_chunk[j]) * a.in_pitch + b, e - b);
+        }
+        if (!cta_barrier(c, ++epoch))
+            return;
+        for (int q = 0; q < n; ++q)
+            cta_copy(out + static_cast<uint64_t>(q) * a.out_pitch + b, my_heap + a.pub_off + q * chunk_stride + b,
+                     e - b);
+        return;
+    }
     // phase P
     if (a.push_root == rank) {
         // bandwidth-optimal broadcast, step 1: slice j of the message -> peer j's pub buffer

@@ -92,6 +92,12 @@ struct ExchangeArgs {
     int src_chunk[kMaxRanks];
     int dst_chunk[kMaxRanks];
     uint64_t pull_bytes[kMaxRanks];  // bytes to load from peer q (<= chunk_bytes)
+    // Small messages, push form: instead of publishing locally and loading from the peers
+    // (a load's round trip after the barrier), chunk push_chunk[j] of `in` is stored into slot
+    // `rank` of peer j's pub buffer before the barrier, and after it the n slots are copied
+    // from the local pub buffer to `out` chunk q.  The stores' latency hides behind the flag's.
+    int push_all;
+    int push_chunk[kMaxRanks];
 };
 
 // Single-pass ("direct") collectives for buffers that live in the symmetric heap at the same

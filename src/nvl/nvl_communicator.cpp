@@ -81,6 +81,7 @@ NvlCommunicator::NvlCommunicator(uint32_t nranks, uint32_t rank) : Communicator(
     m_max_ctas = o.max_ctas > 0 ? std::min(o.max_ctas, kMaxCtas) : 64;
     m_oneshot_bytes = static_cast<size_t>(env_i64("MEGRAY_ONESHOT_BYTES", 256 * 1024));
     m_direct = env_i64("MEGRAY_DIRECT", 1) != 0;
+    m_push_exchange = env_i64("MEGRAY_PUSH_EXCHANGE", 1) != 0;
     m_cta_bytes = static_cast<size_t>(env_i64("MEGRAY_CTA_BYTES", 128 * 1024));
     // measured crossover points (bench/tune.py) override the built-in defaults; explicit
     // environment settings override the table
@@ -534,7 +535,10 @@ Status NvlCommunicator::all_gather(const void* sendbuff, void* recvbuff, size_t 
             a.src_chunk[q] = 0;
             a.dst_chunk[q] = static_cast<int>(q);
             a.pull_bytes[q] = piece;
+            a.push_chunk[q] = 0;
         }
+        a.push_all = m_push_exchange && bytes * m_nranks <= kPushExchangeBytes &&
+                     round_up(piece, 16) * m_nranks <= m_ws_bytes;
         MEGRAY_CHECK(check_cuda(mgk::coll::launch_exchange(a, pick_ctas(piece * m_nranks), 512, stream)));
         after_launch(stream);
         m_stats.algo_copy++;
@@ -574,7 +578,9 @@ Status NvlCommunicator::all_to_all(const void* sendbuff, void* recvbuff, size_t 
             a.src_chunk[q] = static_cast<int>(m_rank);
             a.dst_chunk[q] = static_cast<int>(q);
             a.pull_bytes[q] = piece;
+            a.push_chunk[q] = static_cast<int>(q);
         }
+        a.push_all = m_push_exchange && bytes * m_nranks <= kPushExchangeBytes;
         MEGRAY_CHECK(check_cuda(mgk::coll::launch_exchange(a, pick_ctas(piece * m_nranks), 512, stream)));
         after_launch(stream);
         m_stats.algo_copy++;

@@ -33,6 +33,12 @@ def test_collectives_against_cpu_reference():
     assert out.count("RANK_OK") == NPROC, out[-3000:]
 
 
+def test_collectives_with_the_pull_form_of_small_exchanges():
+    # the default is the push form for small all_gather / all_to_all
+    out = torchrun("collectives.py", env={"MEGRAY_PUSH_EXCHANGE": "0"})
+    assert out.count("RANK_OK") == NPROC, out[-3000:]
+
+
 def test_tensor_parallel_model_matches_single_gpu():
     out = torchrun("tp_model.py", env={"MEGRAY_HEAP_MB": "1024"})
     assert out.count("RANK_OK") == NPROC, out[-3000:]
