@@ -1,6 +1,6 @@
 """Builds the reference library, unmodified, into ``baseline/_ref``.
 
-The reference has no Python packaging (``pip install /root/reference`` ends with "Neither
+The reference has no Python packaging (``pip install <reference checkout>`` ends with "Neither
 'setup.py' nor 'pyproject.toml' found") and its own CMake needs the absent
 ``third_party/nccl`` sources, so its translation units are compiled in place against the
 installed NCCL: ``src/megray.cpp``, ``src/core/*.cpp``, ``src/nccl/*.cpp`` with a
@@ -11,7 +11,7 @@ build.  Products:
     baseline/_ref/performance        the reference's own benchmark (test/performance.cpp)
     baseline/_ref/megray_bench_ref   bench/megray_bench.cpp built against the reference (device-timed sweep)
 
-    python baseline/build_ref.py [--reference /root/reference]
+    python baseline/build_ref.py [--reference <reference checkout>]
 """
 import argparse
 import glob
