@@ -42,6 +42,10 @@ typedef struct {
     uint64_t wait_limit_ns;
 } megray_gemm_args;
 
+/* Tile raster of a dense problem on a device with `sms` SMs, without a GPU: 4 ints per tile
+ * (first row, first column, tile rows, output columns per tile) in launch order; returns the
+ * number of tiles or -1. */
+int megray_gemm_tile_schedule(const megray_gemm_args* a, int sms, int* tiles, int max_tiles);
 int megray_gemm_bf16(const megray_gemm_args* args, void* stream);
 
 

@@ -50,6 +50,12 @@ struct CommBoxView {  // layout of the handle made by megray_comm_new (capi/comm
 };
 }  // namespace
 
+extern "C" int megray_gemm_tile_schedule(const megray_gemm_args* a, int sms, int* tiles, int max_tiles) {
+    if (a == nullptr || tiles == nullptr)
+        return -1;
+    return mgk::gemm::tile_schedule(to_gemm_args(a), sms, tiles, max_tiles);
+}
+
 extern "C" int megray_gemm_bf16(const megray_gemm_args* a, void* stream) {
     if (a == nullptr)
         return 6;

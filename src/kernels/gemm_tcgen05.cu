@@ -136,7 +136,7 @@ struct Tile {
 };
 
 template <int TILE_M>
-__device__ __forceinline__ Tile decode_tile(const KParams& p, int t) {
+__host__ __device__ __forceinline__ Tile decode_tile(const KParams& p, int t) {
     Tile tl;
     tl.skip = false;
     tl.b_row = 0;
@@ -151,7 +151,7 @@ __device__ __forceinline__ Tile decode_tile(const KParams& p, int t) {
     int per_group = p.group_m * p.n_blocks;
     int g = t / per_group;
     int first_m = g * p.group_m;
-    int gsz = min(p.group_m, p.m_blocks - first_m);
+    int gsz = p.m_blocks - first_m < p.group_m ? p.m_blocks - first_m : p.group_m;
     int r = t - g * per_group;
     int mb = first_m + r % gsz;
     int nb = r / gsz;
@@ -1214,17 +1214,16 @@ int sm_count() {
 
 uint64_t gemm_launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
-cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
-    if (a.M <= 0 || a.N <= 0 || a.K <= 0)
-        return cudaErrorInvalidValue;
-    if ((a.lda % 8) || (a.ldb % 8) || (a.ldd % 8))
-        return cudaErrorInvalidValue;
-    if ((reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.B) |
-         reinterpret_cast<uintptr_t>(a.D)) & 15)
-        return cudaErrorInvalidValue;
+namespace {
+// Tile variant and raster of a problem: what launch_gemm_bf16 runs and tile_schedule reports.
+struct Plan {
+    bool pair, wide;
+    int tile_m;
+};
+Plan plan_tiles(const GemmArgs& a, KParams* kpp, int sms) {
+    KParams& kp = *kpp;
     const bool grouped_m = a.grouped.m_block_group != nullptr;
     const bool grouped_k = a.grouped.k_begin != nullptr;
-
     // A CTA pair per tile unless rows are grouped in 128-row blocks (per-expert
     // forward/backward), which need the 128-row tile.  Large dense problems take the
     // 512-row tile: less operand traffic per FLOP, at the price of an epilogue that is
@@ -1235,16 +1234,16 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
         return e != nullptr ? atoi(e) : 0;
     }();
     const int variant = a.variant != 0 ? a.variant : env_variant;
-    const bool pair = !grouped_m && variant != 1 && a.M > 128;
-    bool wide = pair && variant == 3;
-    if (pair && variant == 0 && !grouped_k) {
+    Plan pl;
+    pl.pair = !grouped_m && variant != 1 && a.M > 128;
+    pl.wide = pl.pair && variant == 3;
+    if (pl.pair && variant == 0 && !grouped_k) {
         const long tiles_wide = static_cast<long>((a.M + 511) / 512) *
                                 ((a.N + (a.epilogue == EPI_SWIGLU ? 127 : 255)) / (a.epilogue == EPI_SWIGLU ? 128 : 256));
-        wide = a.M >= 1024 && a.K >= 3072 && tiles_wide >= 2L * (sm_count() / 2);
+        pl.wide = a.M >= 1024 && a.K >= 3072 && tiles_wide >= 2L * (sms / 2);
     }
-    const int tile_m = wide ? 512 : pair ? 256 : BM;
-
-    KParams kp{};
+    pl.tile_m = pl.wide ? 512 : pl.pair ? 256 : BM;
+    const int tile_m = pl.tile_m;
     kp.M = a.M;
     kp.N = a.N;
     kp.K = a.K;
@@ -1255,7 +1254,7 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     kp.num_tiles = kp.m_blocks * kp.n_blocks * (grouped_k ? a.grouped.groups : 1);
     // concurrently running tiles form a near-square patch (about 2048 rows x 2300 columns)
     // so that each loaded A / B panel is shared by as many tiles as possible in L2
-    kp.group_m = wide ? 4 : pair ? 8 : 16;
+    kp.group_m = pl.wide ? 4 : pl.pair ? 8 : 16;
     {
         // tuning aid: MEGRAY_GEMM_GROUP_M overrides the raster's m-blocks per column sweep
         static const int env_group_m = [] {
@@ -1269,6 +1268,43 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
         const int rot_blocks = a.m_rot / tile_m;  // m_rot is given in rows
         kp.m_rot = (rot_blocks % kp.m_blocks + kp.m_blocks) % kp.m_blocks;
     }
+    kp.m_block_group = a.grouped.m_block_group;
+    kp.group_rows_b = a.grouped.group_rows_b;
+    kp.k_begin = a.grouped.k_begin;
+    kp.k_end = a.grouped.k_end;
+    return pl;
+}
+}  // namespace
+
+int tile_schedule(const GemmArgs& a, int sms, int* tiles, int max_tiles) {
+    if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.grouped.m_block_group != nullptr || a.grouped.k_begin != nullptr)
+        return -1;
+    KParams kp{};
+    const Plan pl = plan_tiles(a, &kp, sms);
+    for (int t = 0; t < kp.num_tiles && t < max_tiles; ++t) {
+        const Tile tl = pl.wide ? decode_tile<512>(kp, t) : pl.pair ? decode_tile<256>(kp, t) : decode_tile<128>(kp, t);
+        tiles[4 * t + 0] = tl.m0;
+        tiles[4 * t + 1] = tl.n0;
+        tiles[4 * t + 2] = pl.tile_m;
+        tiles[4 * t + 3] = kp.n_tile_stride;
+    }
+    return kp.num_tiles;
+}
+
+cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
+    if (a.M <= 0 || a.N <= 0 || a.K <= 0)
+        return cudaErrorInvalidValue;
+    if ((a.lda % 8) || (a.ldb % 8) || (a.ldd % 8))
+        return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.B) |
+         reinterpret_cast<uintptr_t>(a.D)) & 15)
+        return cudaErrorInvalidValue;
+    const bool grouped_m = a.grouped.m_block_group != nullptr;
+    const bool grouped_k = a.grouped.k_begin != nullptr;
+    KParams kp{};
+    const Plan pl = plan_tiles(a, &kp, sm_count());
+    const bool pair = pl.pair, wide = pl.wide;
+    const int tile_m = pl.tile_m;
     kp.D = static_cast<__nv_bfloat16*>(a.D);
     kp.ldd = a.ldd;
     kp.D2 = static_cast<__nv_bfloat16*>(a.D2);
@@ -1281,10 +1317,6 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     kp.a_ready_target = a.a_ready_target;
     kp.peer_out = a.peer_out;
     kp.rows_per_peer = a.rows_per_peer > 0 ? a.rows_per_peer : a.M;
-    kp.m_block_group = a.grouped.m_block_group;
-    kp.group_rows_b = a.grouped.group_rows_b;
-    kp.k_begin = a.grouped.k_begin;
-    kp.k_end = a.grouped.k_end;
     kp.error_flag = a.error_flag;
     kp.wait_limit_ns = a.wait_limit_ns ? a.wait_limit_ns : 4000000000ull;
     kp.fuse = a.fuse;

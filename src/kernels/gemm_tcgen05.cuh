@@ -96,6 +96,12 @@ struct GemmArgs {
 // multiples of 8 elements, K > 0.
 cudaError_t launch_gemm_bf16(const GemmArgs& args, cudaStream_t stream);
 
+// Host-side view of the tile raster of a dense problem on a device with `sms` SMs: writes
+// (m0, n0, tile rows, output columns per tile) for each tile in launch order (tile t runs on
+// worker t mod workers) into `tiles` (4 ints per tile, at most `max_tiles` tiles) and returns
+// the number of tiles, or -1 for grouped problems.  Needs no GPU.
+int tile_schedule(const GemmArgs& args, int sms, int* tiles, int max_tiles);
+
 // Number of kernels this module has launched since load (for launch accounting).
 uint64_t gemm_launch_count();
 
