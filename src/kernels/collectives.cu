@@ -665,19 +665,26 @@ __global__ void __launch_bounds__(512) reduce_n_kernel(const ReduceNArgs a) {
         first_scalar = nvec * V;
         for (uint64_t i = gid; i < nvec; i += stride) {
             A acc[V];
+            // all inputs' loads are issued before the first use
+            uint4 raw[kMaxRanks];
+#pragma unroll
+            for (int s = 0; s < kMaxRanks; ++s)
+                if (s < a.n_in)
+                    raw[s] = ld_cg_v4(static_cast<const char*>(a.in[s]) + i * 16);
             {
-                uint4 raw = ld_cg_v4(static_cast<const char*>(a.in[0]) + i * 16);
-                const Tin* e = reinterpret_cast<const Tin*>(&raw);
+                const Tin* e = reinterpret_cast<const Tin*>(&raw[0]);
 #pragma unroll
                 for (int k = 0; k < V; ++k)
                     acc[k] = widen<Tin>(e[k]);
             }
-            for (int s = 1; s < a.n_in; ++s) {
-                uint4 raw = ld_cg_v4(static_cast<const char*>(a.in[s]) + i * 16);
-                const Tin* e = reinterpret_cast<const Tin*>(&raw);
 #pragma unroll
-                for (int k = 0; k < V; ++k)
-                    acc[k] = comb(acc[k], widen<Tin>(e[k]));
+            for (int s = 1; s < kMaxRanks; ++s) {
+                if (s < a.n_in) {
+                    const Tin* e = reinterpret_cast<const Tin*>(&raw[s]);
+#pragma unroll
+                    for (int k = 0; k < V; ++k)
+                        acc[k] = comb(acc[k], widen<Tin>(e[k]));
+                }
             }
             Tout o[V];
 #pragma unroll

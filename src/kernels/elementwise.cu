@@ -86,15 +86,21 @@ __global__ void __launch_bounds__(256) mse_bf16_kernel(const __nv_bfloat16* __re
             dv[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     };
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    // four independent vectors per thread and iteration, all loads issued before the first use
+    constexpr int U = 4;
     uint64_t i = tid;
-    for (; i + stride < nvec; i += 2 * stride) {
-        const uint4 a0 = __ldcs(yv + i), a1 = __ldcs(yv + i + stride);
-        const uint4 b0 = t != nullptr ? __ldcs(tv + i) : zero;
-        const uint4 b1 = t != nullptr ? __ldcs(tv + i + stride) : zero;
-        one(a0, b0, i);
-        one(a1, b1, i + stride);
+    for (; i + (U - 1) * stride < nvec; i += U * stride) {
+        uint4 av[U], bv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            av[u] = __ldcs(yv + i + u * stride);
+            bv[u] = t != nullptr ? __ldcs(tv + i + u * stride) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            one(av[u], bv[u], i + u * stride);
     }
-    if (i < nvec)
+    for (; i < nvec; i += stride)
         one(__ldcs(yv + i), t != nullptr ? __ldcs(tv + i) : zero, i);
     for (uint64_t k = nvec * 8 + tid; k < n; k += stride) {
         const float d = __bfloat162float(y[k]) - (t != nullptr ? __bfloat162float(t[k]) : 0.f);
