@@ -171,42 +171,68 @@ __global__ void __launch_bounds__(256) zero_pads_kernel(uint4* __restrict__ buf,
             buf[static_cast<size_t>(r) * row_vecs + v] = z;
 }
 
-// ---------------------------------------------------------------- dispatch: one warp per (token, slot)
+// ---------------------------------------------------------------- dispatch: one warp per token
+// The token's row is read once, eight 16-byte vectors per lane at a time (all loads issued
+// before the first store), and stored to the rows of both of its experts.
 __global__ void __launch_bounds__(256) dispatch_kernel(const uint4* __restrict__ src, int tokens, int row_vecs,
                                                        const int* __restrict__ idx, const float* __restrict__ w,
                                                        const int* __restrict__ send_base, int* __restrict__ cursor,
                                                        const int* __restrict__ pos_in, int* __restrict__ pos_out,
                                                        PeerBufs dst, int local_experts, int capacity) {
+    static_assert(kTopK == 2, "the dispatch kernel stores each token to two experts");
     const int lane = threadIdx.x & 31;
     const int wpb = blockDim.x >> 5;
-    const int pairs = tokens * kTopK;
-    for (int i = blockIdx.x * wpb + (threadIdx.x >> 5); i < pairs; i += gridDim.x * wpb) {
-        const int e = idx[i];
-        int row;
+    for (int t = blockIdx.x * wpb + (threadIdx.x >> 5); t < tokens; t += gridDim.x * wpb) {
+        const int i0 = t * kTopK;
+        const int e0 = idx[i0], e1 = idx[i0 + 1];
+        int row0, row1;
         if (pos_in != nullptr) {
-            row = pos_in[i];
+            row0 = pos_in[i0];
+            row1 = pos_in[i0 + 1];
         } else {
-            row = 0;
+            row0 = row1 = 0;
             if (lane == 0) {
-                row = send_base[e] + atomicAdd(&cursor[e], 1);
-                pos_out[i] = row;
+                row0 = send_base[e0] + atomicAdd(&cursor[e0], 1);
+                row1 = send_base[e1] + atomicAdd(&cursor[e1], 1);
+                pos_out[i0] = row0;
+                pos_out[i0 + 1] = row1;
             }
-            row = __shfl_sync(0xffffffffu, row, 0);
+            row0 = __shfl_sync(0xffffffffu, row0, 0);
+            row1 = __shfl_sync(0xffffffffu, row1, 0);
         }
-        if (row < 0 || row >= capacity)
-            continue;  // the owner's buffer is full (the plan has raised the overflow flag): drop
-        const float scale = w != nullptr ? w[i] : 1.f;
-        const uint4* s = src + static_cast<size_t>(i / kTopK) * row_vecs;
-        uint4* d = static_cast<uint4*>(dst.p[e / local_experts]) + static_cast<size_t>(row) * row_vecs;
-        for (int v = lane; v < row_vecs; v += 32) {
-            uint4 x = s[v];
-            if (w != nullptr) {
-                x.x = pack(lo(x.x) * scale, hi(x.x) * scale);
-                x.y = pack(lo(x.y) * scale, hi(x.y) * scale);
-                x.z = pack(lo(x.z) * scale, hi(x.z) * scale);
-                x.w = pack(lo(x.w) * scale, hi(x.w) * scale);
+        // a full owner buffer (the plan has raised the overflow flag) drops the row
+        const bool ok0 = row0 >= 0 && row0 < capacity, ok1 = row1 >= 0 && row1 < capacity;
+        if (!ok0 && !ok1)
+            continue;
+        const float s0 = w != nullptr ? w[i0] : 1.f, s1 = w != nullptr ? w[i0 + 1] : 1.f;
+        const uint4* s = src + static_cast<size_t>(t) * row_vecs;
+        uint4* d0 = static_cast<uint4*>(dst.p[e0 / local_experts]) + static_cast<size_t>(ok0 ? row0 : 0) * row_vecs;
+        uint4* d1 = static_cast<uint4*>(dst.p[e1 / local_experts]) + static_cast<size_t>(ok1 ? row1 : 0) * row_vecs;
+        auto scaled = [](const uint4& x, float f) {
+            uint4 y;
+            y.x = pack(lo(x.x) * f, hi(x.x) * f);
+            y.y = pack(lo(x.y) * f, hi(x.y) * f);
+            y.z = pack(lo(x.z) * f, hi(x.z) * f);
+            y.w = pack(lo(x.w) * f, hi(x.w) * f);
+            return y;
+        };
+        constexpr int U = 8;
+        for (int v0 = lane; v0 < row_vecs; v0 += 32 * U) {
+            uint4 x[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (v0 + 32 * u < row_vecs)
+                    x[u] = __ldg(s + v0 + 32 * u);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int v = v0 + 32 * u;
+                if (v < row_vecs) {
+                    if (ok0)
+                        d0[v] = w != nullptr ? scaled(x[u], s0) : x[u];
+                    if (ok1)
+                        d1[v] = w != nullptr ? scaled(x[u], s1) : x[u];
+                }
             }
-            d[v] = x;
         }
     }
 }
@@ -232,14 +258,28 @@ __global__ void __launch_bounds__(256) combine_kernel(uint4* __restrict__ out, i
         const uint4* a = static_cast<const uint4*>(src.p[e0 / local_experts]) + static_cast<size_t>(p0) * row_vecs;
         const uint4* b = static_cast<const uint4*>(src.p[e1 / local_experts]) + static_cast<size_t>(p1) * row_vecs;
         uint4* o = out + static_cast<size_t>(t) * row_vecs;
-        for (int v = lane; v < row_vecs; v += 32) {
-            const uint4 x = __ldcg(a + v), y = __ldcg(b + v);
-            uint4 r;
-            r.x = pack(w0 * lo(x.x) + w1 * lo(y.x), w0 * hi(x.x) + w1 * hi(y.x));
-            r.y = pack(w0 * lo(x.y) + w1 * lo(y.y), w0 * hi(x.y) + w1 * hi(y.y));
-            r.z = pack(w0 * lo(x.z) + w1 * lo(y.z), w0 * hi(x.z) + w1 * hi(y.z));
-            r.w = pack(w0 * lo(x.w) + w1 * lo(y.w), w0 * hi(x.w) + w1 * hi(y.w));
-            o[v] = r;
+        // four vectors of each row per lane and iteration: eight (possibly remote) loads in flight
+        constexpr int U = 4;
+        for (int v0 = lane; v0 < row_vecs; v0 += 32 * U) {
+            uint4 x[U], y[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (v0 + 32 * u < row_vecs) {
+                    x[u] = __ldcg(a + v0 + 32 * u);
+                    y[u] = __ldcg(b + v0 + 32 * u);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (v0 + 32 * u < row_vecs) {
+                    uint4 r;
+                    r.x = pack(w0 * lo(x[u].x) + w1 * lo(y[u].x), w0 * hi(x[u].x) + w1 * hi(y[u].x));
+                    r.y = pack(w0 * lo(x[u].y) + w1 * lo(y[u].y), w0 * hi(x[u].y) + w1 * hi(y[u].y));
+                    r.z = pack(w0 * lo(x[u].z) + w1 * lo(y[u].z), w0 * hi(x[u].z) + w1 * hi(y[u].z));
+                    r.w = pack(w0 * lo(x[u].w) + w1 * lo(y[u].w), w0 * hi(x[u].w) + w1 * hi(y[u].w));
+                    o[v0 + 32 * u] = r;
+                }
+            }
         }
     }
 }
@@ -325,7 +365,7 @@ cudaError_t launch_dispatch(const void* src, int tokens, int row_elems, const in
                             int local_experts, int capacity, cudaStream_t stream) {
     if (tokens <= 0 || row_elems % 8 || local_experts < 1)
         return cudaErrorInvalidValue;
-    dispatch_kernel<<<blocks_for(8, static_cast<long>(tokens) * kTopK), 256, 0, stream>>>(
+    dispatch_kernel<<<blocks_for(8, tokens), 256, 0, stream>>>(
             static_cast<const uint4*>(src), tokens, row_elems / 8, idx, w, send_base, cursor, pos_in, pos_out, dst,
             local_experts, capacity);
     count_launch();

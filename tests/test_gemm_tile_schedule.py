@@ -45,9 +45,9 @@ def test_tiles_cover_the_output_exactly_once(variant, tile_m, M, N, epilogue, ti
 def test_rotation_starts_with_the_asked_row_block_and_keeps_column_sweeps_together():
     tiles = schedule(32768, 8192, 8192, variant=3, m_rot=3 * 4096)
     assert tiles[0][0] == 3 * 4096
-    # a sweep of group_m = 4 row blocks x all 32 column tiles comes before the next row blocks
-    first = tiles[: 4 * 32]
-    assert {t[0] for t in first} == {3 * 4096 + 512 * i for i in range(4)}
+    # a sweep of group_m = 8 row blocks x all 32 column tiles comes before the next row blocks
+    first = tiles[: 8 * 32]
+    assert {t[0] for t in first} == {3 * 4096 + 512 * i for i in range(8)}
 
 
 def test_automatic_variant_picks_the_wide_tile_only_for_large_dense_problems():
