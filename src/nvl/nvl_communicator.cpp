@@ -537,7 +537,7 @@ Status NvlCommunicator::all_gather(const void* sendbuff, void* recvbuff, size_t 
             a.pull_bytes[q] = piece;
             a.push_chunk[q] = 0;
         }
-        a.push_all = m_push_exchange && bytes * m_nranks <= kPushExchangeBytes &&
+        a.push_all = m_push_exchange && bytes <= kPushExchangeBytes &&
                      round_up(piece, 16) * m_nranks <= m_ws_bytes;
         MEGRAY_CHECK(check_cuda(mgk::coll::launch_exchange(a, pick_ctas(piece * m_nranks), 512, stream)));
         after_launch(stream);
@@ -580,7 +580,7 @@ Status NvlCommunicator::all_to_all(const void* sendbuff, void* recvbuff, size_t 
             a.pull_bytes[q] = piece;
             a.push_chunk[q] = static_cast<int>(q);
         }
-        a.push_all = m_push_exchange && bytes * m_nranks <= kPushExchangeBytes;
+        a.push_all = m_push_exchange && bytes <= kPushExchangeBytes;
         MEGRAY_CHECK(check_cuda(mgk::coll::launch_exchange(a, pick_ctas(piece * m_nranks), 512, stream)));
         after_launch(stream);
         m_stats.algo_copy++;

@@ -131,10 +131,11 @@ private:
     size_t m_nvls_min_bytes = 0;
     size_t m_cta_bytes = 128 * 1024;  // message bytes per CTA when sizing a collective's grid
     bool m_direct = true;
-    // all_gather / all_to_all of at most this many bytes in total take the push form (stores
-    // into the peers' buffers before the barrier instead of loads from them after it): measured
-    // on 2 GPUs, 9.0 vs 9.7-10.1 us at 1 KiB and 10.1-10.4 vs 11.8-13.0 us at 16 KiB, no gain at
-    // 64 KiB per rank.  MEGRAY_PUSH_EXCHANGE=0 turns it off.
+    // all_gather / all_to_all of at most this many bytes per rank (per peer for all_to_all) take
+    // the push form (stores into the peers' buffers before the barrier instead of loads from
+    // them after it).  Measured: on 2 GPUs 9.0 vs 9.7-10.1 us at 1 KiB and 10.1-10.4 vs
+    // 11.8-13.0 us at 16 KiB; on 8 GPUs 17.9-18.1 us at 1 KiB (push) against 39-44 us at 16 KiB
+    // (pull).  MEGRAY_PUSH_EXCHANGE=0 turns it off.
     static constexpr size_t kPushExchangeBytes = 64 * 1024;
     bool m_push_exchange = true;
     int* m_status_host = nullptr;  // pinned, mapped

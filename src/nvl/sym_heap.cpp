@@ -32,6 +32,9 @@ struct HandleTable {
     std::mutex mu;
     std::condition_variable cv;
     std::map<std::string, CUmemGenericAllocationHandle> map;
+    // multicast objects used by several ranks of this process through one handle value: the
+    // last user to let go releases the object
+    std::map<CUmemGenericAllocationHandle, int> mc_users;
 };
 HandleTable& table() {
     static HandleTable t;
@@ -78,9 +81,21 @@ void SymmetricHeap::destroy() {
     if (m_mc_handle != 0) {
         if (m_mc_bound && m_api->MulticastUnbind != nullptr)
             m_api->MulticastUnbind(m_mc_handle, m_device, 0, m_bytes);
-        if (m_mc_owned)
+        bool release = m_mc_owned;
+        if (m_mc_shared) {
+            // the handle value is shared with the other ranks of this process, which may still
+            // be unbinding: only the last one releases it
+            HandleTable& t = table();
+            std::lock_guard<std::mutex> lk(t.mu);
+            auto it = t.mc_users.find(m_mc_handle);
+            release = it != t.mc_users.end() && --it->second == 0;
+            if (release)
+                t.mc_users.erase(it);
+        }
+        if (release)
             m_api->MemRelease(m_mc_handle);
         m_mc_handle = 0;
+        m_mc_shared = false;
     }
     for (uint32_t q = 0; q < m_base.size(); ++q) {
         if (m_mapped.size() > q && m_mapped[q])
@@ -352,7 +367,16 @@ Status SymmetricHeap::setup_multicast(Client* client, const std::vector<PeerInfo
             all_ok = all_ok && v != 0;
     }
     m_mc_handle = mc;
-    m_mc_owned = !borrowed;  // a borrowed object is released by rank 0 of this process
+    // rank 0's handle value serves every rank of rank 0's process (counted, the last user
+    // releases it); ranks of other processes own the handle they imported
+    m_mc_shared = info[0].pid == my_pid;
+    m_mc_owned = !m_mc_shared;
+    (void)borrowed;
+    if (m_mc_shared) {
+        HandleTable& t = table();
+        std::lock_guard<std::mutex> lk(t.mu);
+        t.mc_users[mc] += 1;
+    }
     if (!all_ok) {
         if (m_mc_base != nullptr) {
             m_api->MemUnmap(m_mc_va, m_bytes);

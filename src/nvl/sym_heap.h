@@ -68,6 +68,7 @@ private:
     CUmemGenericAllocationHandle m_mc_handle = 0;
     bool m_mc_bound = false;
     bool m_mc_owned = false;
+    bool m_mc_shared = false;  // handle value shared with the other ranks of this process
     CUdeviceptr m_mc_va = 0;
     char* m_mc_base = nullptr;
 };
