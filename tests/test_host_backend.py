@@ -261,6 +261,25 @@ def test_stats_and_backend():
         assert st["calls"] == 1 and st["bytes"] == 64
 
 
+def test_nvl_only_calls_are_refused_by_other_backends():
+    """Buffer registration and the symmetric heap belong to the NVL backend; the host backend
+    answers MEGRAY_INVALID_USAGE instead of pretending."""
+    import ctypes as C
+
+    from megray_b200 import _lib
+
+    def body(comm, rank):
+        lib = _lib.load()
+        x = np.ones(16, np.float32)
+        rc_reg = lib.megray_nvl_register(comm._h, C.c_void_p(x.ctypes.data), x.nbytes)
+        rc_dereg = lib.megray_nvl_deregister(comm._h, C.c_void_p(x.ctypes.data))
+        ptr = lib.megray_nvl_alloc(comm._h, 1024, None)
+        return rc_reg, rc_dereg, ptr
+
+    for rc_reg, rc_dereg, ptr in with_group(2, "shm", body):
+        assert rc_reg == 7 and rc_dereg == 7 and not ptr
+
+
 def test_unbuilt_backends_throw_unknown_backend():
     for b in ("ucx", "rccl"):
         with pytest.raises(mr.MegRayError):
