@@ -2,14 +2,17 @@
 //
 //   warp 0      : TMA producer   (cp.async.bulk.tensor 2D tiles -> 128B-swizzled smem ring)
 //   warp 1      : UMMA issuer    (tcgen05.mma, accumulators in TMEM)
-//   warps 2..5  : epilogue       (tcgen05.ld TMEM -> registers -> fused epilogue -> global)
+//   warps 2..5  : epilogue       (tcgen05.ld TMEM -> registers -> fused epilogue -> swizzled
+//                                 staging boxes -> TMA store; row segments for the push epilogue)
+//   warps 6..9  : communication  (fused all_gather: pull the peers' shards) and, on the wide
+//                                 tile, a second epilogue group
 //
 // Three variants of one kernel template:
 //   single : one CTA per tile, tile 128 x 256 x 64, tcgen05.mma.cta_group::1 (M = 128),
 //            4-stage ring of 48 KB.  Used for grouped (per-expert) row blocks.
 //   pair   : a cluster of two CTAs per 256 x 256 tile, tcgen05.mma.cta_group::2 (M = 256)
 //            issued by the leader CTA; each CTA stages its own 128 rows of A and its own
-//            128 rows of B (so B is read from shared memory once per pair), 7-stage ring
+//            128 rows of B (so B is read from shared memory once per pair), 6-stage ring
 //            of 32 KB per CTA.  Each CTA issues its own TMA loads (no multicast); their
 //            byte counts complete on the leader's barrier, and the leader's commits free
 //            the stage in both CTAs.

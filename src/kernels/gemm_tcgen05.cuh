@@ -83,7 +83,6 @@ struct GemmArgs {
     // reduce_scatter fusion (EPI_PUSH): per-peer output base pointers, rows per peer
     void* const* peer_out;  // device array [n_peers]
     int rows_per_peer;
-    uint32_t* tile_done;    // optional: counter bumped once per finished tile (gpu scope)
     // grouped problems (MoE); null m_block_group = dense
     GroupedArgs grouped;
     FuseArgs fuse;            // zero-initialised = no fused collective
