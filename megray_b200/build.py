@@ -120,6 +120,60 @@ def write_ninja(with_bins: bool) -> str:
     return path
 
 
+def build_sanitized(kind: str = "thread") -> str:
+    """Builds the C++ test runner with the host code under a sanitizer (``thread``, or
+    ``address,undefined``) into ``build/san_<kind>/megray_test`` and returns its path.  The host
+    sources (rendezvous, host backend, factory, options, tracing, C++ tests) are compiled with
+    ``-fsanitize``; the device objects of the normal build are linked as they are.  The runner
+    is meant for CPU ranks: rendezvous, host backend and selection logic."""
+    build(with_bins=True)
+    tag = kind.replace(",", "_")
+    out_dir = os.path.join(BUILD_DIR, "san_" + tag)
+    os.makedirs(out_dir, exist_ok=True)
+    cpp, cu = _sources()
+    cpp += sorted(glob.glob(os.path.join(ROOT, "tests", "cpp", "*.cpp")))
+    inc = f"-I{ROOT}/include -I{ROOT}/src -I{ROOT}/tests/cpp -I{CUDA_HOME}/include"
+    nccl_inc = _nccl_include()
+    defs = "-DMEGRAY_WITH_CUDA -DMEGRAY_WITH_NVL -DMEGRAY_WITH_SHM"
+    if nccl_inc:
+        defs += " -DMEGRAY_WITH_NCCL"
+        if nccl_inc != "/usr/include":
+            inc += f" -I{nccl_inc}"
+    flags = f"-std=c++17 -O1 -g -fno-omit-frame-pointer -fPIC -fsanitize={kind} {defs} {inc}"
+    lines = [
+        "ninja_required_version = 1.3",
+        f"cxxflags = {flags}",
+        "rule cxx",
+        "  command = g++ -MMD -MF $out.d $cxxflags -c $in -o $out",
+        "  depfile = $out.d",
+        "  deps = gcc",
+        "rule link",
+        f"  command = g++ -fsanitize={kind} -o $out $in -L{CUDA_HOME}/lib64 -lcudart -lpthread -ldl -lrt",
+        "",
+    ]
+    objs = []
+    for src in cpp:
+        obj = os.path.join(out_dir, os.path.relpath(src, ROOT).replace(os.sep, "_") + ".o")
+        lines.append(f"build {obj}: cxx {src}")
+        objs.append(obj)
+    for src in cu:  # device objects of the normal build
+        objs.append(os.path.join(BUILD_DIR, os.path.relpath(src, ROOT).replace(os.sep, "_") + ".o"))
+    target = os.path.join(out_dir, "megray_test")
+    lines.append(f"build {target}: link {' '.join(objs)}")
+    lines.append(f"default {target}")
+    path = os.path.join(out_dir, "build.ninja")
+    text = "\n".join(lines) + "\n"
+    if not os.path.exists(path) or open(path).read() != text:
+        with open(path, "w") as f:
+            f.write(text)
+    res = subprocess.run([shutil.which("ninja"), "-f", path, "-C", out_dir], stdout=subprocess.PIPE,
+                         stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout)
+        raise RuntimeError("sanitizer build failed")
+    return target
+
+
 def build(with_bins: bool = False, verbose: bool = False) -> str:
     """Compile everything that is stale; returns the path of libmegray.so."""
     ninja = shutil.which("ninja")
@@ -142,5 +196,11 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--all", action="store_true", help="also build megray_test and megray_bench")
     ap.add_argument("-v", "--verbose", action="store_true")
+    ap.add_argument("--sanitize", default=None, metavar="KIND",
+                    help="build the C++ test runner with the host code under -fsanitize=KIND "
+                         "(thread, or address,undefined) instead")
     a = ap.parse_args()
-    print(build(with_bins=a.all, verbose=a.verbose))
+    if a.sanitize:
+        print(build_sanitized(a.sanitize))
+    else:
+        print(build(with_bins=a.all, verbose=a.verbose))
