@@ -111,6 +111,9 @@ def _declare(lib) -> None:
     d("megray_nvl_set_device_timeout_ms", None, vp, i64)
     d("megray_cpu_reduce_n", i32, P(vp), i32, vp, sz, i32, i32)
     d("megray_cpu_reduce_scale_cast", i32, P(vp), i32, i32, vp, i32, sz, i32, C.c_double)
+    d("megray_oracle_ring_all_reduce", i32, P(vp), P(vp), i32, sz, i32, i32)
+    d("megray_oracle_tree_reduce", i32, P(vp), vp, i32, i32, sz, i32, i32)
+    d("megray_gemm_tile_schedule", i32, C.POINTER(GemmArgs), i32, P(i32), i32)
     d("megray_reduce_n", i32, P(vp), i32, vp, sz, i32, i32, i32, C.c_float, vp)
     d("megray_sgd_bf16", i32, vp, vp, vp, u64, C.c_float, C.c_float, C.c_float, vp)
     d("megray_mse_bf16", i32, vp, vp, vp, vp, u64, C.c_float, vp)

@@ -13,8 +13,6 @@ EPI_STORE, EPI_SWIGLU = 0, 1
 
 def schedule(M, N, K, variant=0, epilogue=EPI_STORE, m_rot=0, sms=148):
     lib = _lib.load()
-    lib.megray_gemm_tile_schedule.argtypes = [C.POINTER(GemmArgs), C.c_int, C.POINTER(C.c_int), C.c_int]
-    lib.megray_gemm_tile_schedule.restype = C.c_int
     a = GemmArgs()
     a.M, a.N, a.K = M, N, K
     a.variant, a.epilogue, a.m_rot = variant, epilogue, m_rot
@@ -64,5 +62,4 @@ def test_grouped_problems_have_no_host_schedule():
     a.M, a.N, a.K = 1024, 1024, 1024
     a.k_begin = 16  # any non-null device address: grouped-K ranges live on the device
     buf = (C.c_int * 16)()
-    lib.megray_gemm_tile_schedule.argtypes = [C.POINTER(GemmArgs), C.c_int, C.POINTER(C.c_int), C.c_int]
     assert lib.megray_gemm_tile_schedule(C.byref(a), 148, buf, 4) == -1

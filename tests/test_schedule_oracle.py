@@ -27,7 +27,7 @@ def tree(arrays, root, dtype_code, op):
     n = len(arrays)
     out = np.empty_like(arrays[0])
     ip = (C.c_void_p * n)(*[a.ctypes.data for a in arrays])
-    assert lib.megray_oracle_tree_reduce(ip, out.ctypes.data, n, root, arrays[0].size, dtype_code, op) == 0
+    assert lib.megray_oracle_tree_reduce(ip, C.c_void_p(out.ctypes.data), n, root, arrays[0].size, dtype_code, op) == 0
     return out
 
 
@@ -107,4 +107,4 @@ def test_bad_arguments():
     a = np.zeros(4, np.float32)
     ip = (C.c_void_p * 1)(a.ctypes.data)
     assert lib.megray_oracle_ring_all_reduce(ip, ip, 0, 4, mr.FLOAT32, mr.SUM) != 0
-    assert lib.megray_oracle_tree_reduce(ip, a.ctypes.data, 1, 1, 4, mr.FLOAT32, mr.SUM) != 0
+    assert lib.megray_oracle_tree_reduce(ip, C.c_void_p(a.ctypes.data), 1, 1, 4, mr.FLOAT32, mr.SUM) != 0
