@@ -21,7 +21,7 @@ sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
-from megray_b200.ops import EPI_SWIGLU, gemm  # noqa: E402
+from megray_b200.ops import EPI_DSWIGLU, EPI_SWIGLU, gemm  # noqa: E402
 
 
 def time_round_robin(fns, warmup, iters):
@@ -47,7 +47,7 @@ def main():
     ap.add_argument("--m", type=int)
     ap.add_argument("--n", type=int)
     ap.add_argument("--k", type=int)
-    ap.add_argument("--layout", default="nt", choices=["nt", "nn", "tn", "tt", "swiglu"])
+    ap.add_argument("--layout", default="nt", choices=["nt", "nn", "tn", "tt", "swiglu", "dswiglu"])
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-cublas", action="store_true")
@@ -64,12 +64,12 @@ def main():
         cases = [(a.layout, a.m, a.n, a.k)]
     else:
         T, d, f = 32768, 8192, 28672
-        cases = [("swiglu", T, f, d), ("nt", T, d, f), ("nn", T, f, d), ("nn", T, d, 2 * f),
+        cases = [("swiglu", T, f, d), ("nt", T, d, f), ("dswiglu", T, f, d), ("nn", T, f, d), ("nn", T, d, 2 * f),
                  ("tt", d, f, T), ("tt", 2 * f, d, T), ("nt", 8192, 8192, 8192)]
     dev = "cuda"
     for layout, M, N, K in cases:
         a_mn = layout in ("tn", "tt")
-        b_mn = layout in ("nn", "tt")
+        b_mn = layout in ("nn", "tt", "dswiglu")
         A = torch.randn((K, M) if a_mn else (M, K), device=dev).to(torch.bfloat16)
         if layout == "swiglu":
             B = torch.randn(2 * N, K, device=dev).to(torch.bfloat16) * 0.02
@@ -77,6 +77,14 @@ def main():
             out2 = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
             fn = lambda v: gemm(A, B, out, epilogue=EPI_SWIGLU, out2=out2, n=N, variant=v)  # noqa: E731
             flops = 2.0 * M * 2 * N * K
+        elif layout == "dswiglu":
+            # backward of the SwiGLU projection: dH = dY @ W_down (NN), epilogue turns it into
+            # [dG | dU] with the saved [G | U]
+            B = torch.randn(K, N, device=dev).to(torch.bfloat16) * 0.02
+            aux = torch.randn(M, 2 * N, device=dev).to(torch.bfloat16)
+            out = torch.empty(M, 2 * N, device=dev, dtype=torch.bfloat16)
+            fn = lambda v: gemm(A, B, out, b_mn=True, epilogue=EPI_DSWIGLU, aux=aux, n=N, variant=v)  # noqa: E731
+            flops = 2.0 * M * N * K
         else:
             B = torch.randn((K, N) if b_mn else (N, K), device=dev).to(torch.bfloat16)
             out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
@@ -86,7 +94,8 @@ def main():
         if not a.no_cublas:
             Af = A.t() if a_mn else A
             Bf = B if b_mn else B.t()
-            ref_out = torch.empty(M, 2 * N, device=dev, dtype=torch.bfloat16) if layout == "swiglu" else out
+            ref_out = torch.empty(M, 2 * N, device=dev, dtype=torch.bfloat16) if layout == "swiglu" else (
+                torch.empty(M, N, device=dev, dtype=torch.bfloat16) if layout == "dswiglu" else out)
             cands.append(lambda: torch.matmul(Af, Bf, out=ref_out))
         ts = time_round_robin(cands, a.warmup, a.iters)
         line = f"{layout:7s} M={M:6d} N={N:6d} K={K:6d} "

@@ -186,6 +186,25 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
+// 32 consecutive bf16 of one row as 16 packed words; columns from `ncols_ok` on read as zero
+__device__ __forceinline__ void load_packed32(const __nv_bfloat16* src, uint32_t (&w)[16], int ncols_ok) {
+    if (ncols_ok >= 32) {
+        const uint4* s4 = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 q = s4[i];
+            w[4 * i] = q.x; w[4 * i + 1] = q.y; w[4 * i + 2] = q.z; w[4 * i + 3] = q.w;
+        }
+    } else {
+        const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t lo16 = 2 * i < ncols_ok ? s16[2 * i] : 0u;
+            const uint32_t hi16 = 2 * i + 1 < ncols_ok ? s16[2 * i + 1] : 0u;
+            w[i] = lo16 | (hi16 << 16);
+        }
+    }
+}
 __device__ __forceinline__ void load_row32(const __nv_bfloat16* src, float (&v)[32], int ncols_ok) {
     if (ncols_ok >= 32) {
         const uint4* s4 = reinterpret_cast<const uint4*>(src);
@@ -401,6 +420,8 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
     } else {
         tmem_ld_32x32b_x32(t_addr, r);
     }
+    uint4 next_g[4], next_u[4];  // EPI_DSWIGLU: the next chunk's saved gate / up values, packed
+    bool have_next = false;
 #pragma unroll 1
     for (int c = 0; c < BN / 32; ++c) {
         const int col = tl.n0 + c * 32;
@@ -425,27 +446,49 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
                                               __uint_as_float(r[2 * i + 1]) + o[2 * i + 1])
                                 : 0u;
         } else if (EPI == EPI_DSWIGLU) {
-            float g[32], u[32];
+            // saved gate / up values of this chunk, packed (two bf16 per word)
+            uint32_t cg[16], cu[16];
             if (lane_ok) {
-                load_row32(p.aux + drow * p.ldaux + col, g, ok);
-                load_row32(p.aux + drow * p.ldaux + p.aux_off + col, u, ok);
+                if (have_next) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        cg[4 * i] = next_g[i].x; cg[4 * i + 1] = next_g[i].y; cg[4 * i + 2] = next_g[i].z; cg[4 * i + 3] = next_g[i].w;
+                        cu[4 * i] = next_u[i].x; cu[4 * i + 1] = next_u[i].y; cu[4 * i + 2] = next_u[i].z; cu[4 * i + 3] = next_u[i].w;
+                    }
+                } else {
+                    load_packed32(p.aux + drow * p.ldaux + col, cg, ok);
+                    load_packed32(p.aux + drow * p.ldaux + p.aux_off + col, cu, ok);
+                }
+            }
+            // the saved [G | U] of the next chunk are fetched while this one is worked on
+            have_next = false;
+            if (row_ok && c + 1 < BN / 32 && ok - 32 >= 32) {
+                const uint4* ng = reinterpret_cast<const uint4*>(p.aux + drow * p.ldaux + col + 32);
+                const uint4* nu = reinterpret_cast<const uint4*>(p.aux + drow * p.ldaux + p.aux_off + col + 32);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    next_g[i] = __ldg(ng + i);
+                    next_u[i] = __ldg(nu + i);
+                }
+                have_next = true;
             }
             if (!zero_tile)
                 tmem_ld_wait(r);
-            if (lane_ok) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float sg = __fdividef(1.f, 1.f + __expf(-g[i]));
-                    const float dh = __uint_as_float(r[i]);
-                    const float silu = g[i] * sg;
-                    u[i] = dh * u[i] * (sg + silu * (1.f - sg));  // dG
-                    g[i] = dh * silu;                              // dU
-                }
-            }
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                pk[i] = lane_ok ? pack_bf16x2(u[2 * i], u[2 * i + 1]) : 0u;
-                pk2[i] = lane_ok ? pack_bf16x2(g[2 * i], g[2 * i + 1]) : 0u;
+                float dgv[2], duv[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const float g = h ? bf16_hi(cg[i]) : bf16_lo(cg[i]);
+                    const float u = h ? bf16_hi(cu[i]) : bf16_lo(cu[i]);
+                    const float sg = __fdividef(1.f, 1.f + __expf(-g));
+                    const float dh = __uint_as_float(r[2 * i + h]);
+                    const float silu = g * sg;
+                    dgv[h] = dh * u * (sg + silu * (1.f - sg));  // dG
+                    duv[h] = dh * silu;                           // dU
+                }
+                pk[i] = lane_ok ? pack_bf16x2(dgv[0], dgv[1]) : 0u;
+                pk2[i] = lane_ok ? pack_bf16x2(duv[0], duv[1]) : 0u;
             }
         }
         if (!zero_tile && c + 1 < BN / 32)
@@ -1243,7 +1286,10 @@ Plan plan_tiles(const GemmArgs& a, KParams* kpp, int sms) {
     if (pl.pair && variant == 0 && !grouped_k) {
         const long tiles_wide = static_cast<long>((a.M + 511) / 512) *
                                 ((a.N + (a.epilogue == EPI_SWIGLU ? 127 : 255)) / (a.epilogue == EPI_SWIGLU ? 128 : 256));
-        pl.wide = a.M >= 1024 && a.K >= 3072 && tiles_wide >= 2L * (sms / 2);
+        // (the dSwiGLU epilogue reads and writes four values per accumulator element; it needs
+        // the next tile's main loop to hide behind: 12.9-13.2 ms on the pair tile against
+        // 13.3-14.0 ms on the wide one for 32768 x 28672 x 8192)
+        pl.wide = a.M >= 1024 && a.K >= 3072 && tiles_wide >= 2L * (sms / 2) && a.epilogue != EPI_DSWIGLU;
     }
     pl.tile_m = pl.wide ? 512 : pl.pair ? 256 : BM;
     const int tile_m = pl.tile_m;
