@@ -17,6 +17,7 @@
 #include <thread>
 #include <vector>
 
+#include "host/shared_region.h"
 #include "megray.h"
 #include "mini_test.h"
 
@@ -409,6 +410,97 @@ TEST(Nvl_SymmetricAllocAndScaledAllReduce) {
         env.release(d_in);
         env.release(d_out);
     });
+}
+
+// ------------------------------------------------------------------ shared region of the host backend
+// (the counterpart of the reference's test/test_shm.cpp: shared memory write / read, and the
+// synchronisation built in it, from one thread and from two)
+TEST(Shm_RegionWriteReadInProcess) {
+    const std::string name = "megray-test-region-" + std::to_string(getpid()) + "-a";
+    auto owner = host::SharedRegion::create(name, 2, 4096, 1024, true);
+    ASSERT_TRUE(owner != nullptr);
+    auto peer = host::SharedRegion::attach(name, true, 1000);
+    ASSERT_TRUE(peer != nullptr);
+    EXPECT_EQ(peer->nranks(), 2u);
+    EXPECT_EQ(peer->slot_bytes(), owner->slot_bytes());
+    for (int i = 0; i < 4096; ++i) owner->slot(1)[i] = static_cast<char>(i * 7);
+    int wrong = 0;
+    for (int i = 0; i < 4096; ++i) wrong += peer->slot(1)[i] != static_cast<char>(i * 7);
+    EXPECT_EQ(wrong, 0);
+    // one mailbox per ordered pair, distinct storage
+    EXPECT_TRUE(owner->mailbox_data(0, 1) != owner->mailbox_data(1, 0));
+    peer->mailbox_data(0, 1)[5] = 42;
+    EXPECT_EQ(owner->mailbox_data(0, 1)[5], 42);
+}
+
+TEST(Shm_RegionWriteReadPosixObject) {
+    const std::string name = "megray-test-region-" + std::to_string(getpid()) + "-b";
+    auto owner = host::SharedRegion::create(name, 3, 1 << 16, 4096, false);
+    ASSERT_TRUE(owner != nullptr);
+    auto peer = host::SharedRegion::attach(name, false, 1000);  // a second mapping of the object
+    ASSERT_TRUE(peer != nullptr);
+    EXPECT_TRUE(static_cast<void*>(peer->slot(0)) != static_cast<void*>(owner->slot(0)));
+    memset(owner->result(), 0x5a, 1 << 16);
+    int wrong = 0;
+    for (int i = 0; i < (1 << 16); ++i) wrong += peer->result()[i] != 0x5a;
+    EXPECT_EQ(wrong, 0);
+    EXPECT_TRUE(host::SharedRegion::attach(name + "-absent", false, 50) == nullptr);
+}
+
+TEST(Shm_BarrierTwoThreads) {
+    const std::string name = "megray-test-region-" + std::to_string(getpid()) + "-c";
+    auto region = host::SharedRegion::create(name, 2, 256, 256, true);
+    ASSERT_TRUE(region != nullptr);
+    std::atomic<int> arrived{0};
+    std::atomic<int> ahead{0};
+    const int rounds = 2000;
+    run_ranks(2, [&](int rank) {
+        auto mine = rank == 0 ? region : host::SharedRegion::attach(name, true, 1000);
+        uint32_t sense = 0;
+        for (int i = 0; i < rounds; ++i) {
+            arrived.fetch_add(1);
+            if (mine->barrier(&sense, 5000) != MEGRAY_OK) throw std::runtime_error("barrier failed");
+            // nobody leaves round i before both ranks have arrived in it
+            if (arrived.load() < 2 * (i + 1)) ahead.fetch_add(1);
+        }
+    });
+    EXPECT_EQ(ahead.load(), 0);
+    EXPECT_EQ(arrived.load(), 2 * rounds);
+}
+
+TEST(Shm_BarrierTimeoutAndAbort) {
+    const std::string name = "megray-test-region-" + std::to_string(getpid()) + "-d";
+    auto region = host::SharedRegion::create(name, 2, 256, 256, true);
+    ASSERT_TRUE(region != nullptr);
+    uint32_t sense = 0;
+    EXPECT_EQ(region->barrier(&sense, 50), MEGRAY_TIMEOUT);  // the second rank never comes
+    region->abort();
+    EXPECT_TRUE(region->aborted());
+    uint32_t sense2 = 0;
+    EXPECT_EQ(region->barrier(&sense2, 50), MEGRAY_ABORTED);
+}
+
+// A message many times the size of the ring mailbox crosses it in pieces, in both directions
+// at once (the reference's RingSender / RingRecver pair, test/test_shm.cpp:57-83).
+TEST(Shm_MailboxCarriesMessagesLargerThanTheRing) {
+    setenv("MEGRAY_HOST_MAILBOX_KB", "4", 1);
+    Server server(2);
+    const size_t len = 1 << 20;
+    run_ranks(2, [&](int rank) {
+        auto comm = get_communicator(2, rank, MEGRAY_SHM);
+        if (comm->init("127.0.0.1", server.port()) != MEGRAY_OK) throw std::runtime_error("init");
+        auto ctx = HostContext::make();
+        std::vector<char> out(len), in(len, 0);
+        for (size_t i = 0; i < len; ++i) out[i] = static_cast<char>((i * 31 + rank) & 0xff);
+        if (comm->group_start() != MEGRAY_OK) throw std::runtime_error("group_start");
+        comm->send(out.data(), len, MEGRAY_CHAR, 1 - rank, ctx);
+        comm->recv(in.data(), len, MEGRAY_CHAR, 1 - rank, ctx);
+        if (comm->group_end() != MEGRAY_OK) throw std::runtime_error("group_end");
+        size_t wrong = 0;
+        for (size_t i = 0; i < len; ++i) wrong += in[i] != static_cast<char>((i * 31 + (1 - rank)) & 0xff);
+        if (wrong) throw std::runtime_error("payload differs");
+    });
+    unsetenv("MEGRAY_HOST_MAILBOX_KB");
 }
 
 // Ranks as threads of one process: a registered cudaMalloc buffer is reached by its plain
