@@ -21,7 +21,7 @@ sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
-from megray_b200.ops import EPI_DSWIGLU, EPI_SWIGLU, gemm  # noqa: E402
+from megray_b200.ops import EPI_DSWIGLU, EPI_SWIGLU, gemm, gemm_split_k  # noqa: E402
 
 
 def time_round_robin(fns, warmup, iters):
@@ -53,6 +53,8 @@ def main():
     ap.add_argument("--no-cublas", action="store_true")
     ap.add_argument("--epilogue", type=int, default=0, help="0 = per-lane stores, 5 = row segments through smem")
     ap.add_argument("--variant", type=int, default=0, help="0 = automatic, 1 = single-CTA 128x256 tile, 2 = CTA-pair 256x256 tile, 3 = CTA-pair 512x256 tile")
+    ap.add_argument("--split-k", default="", help="comma-separated K-range counts to time as extra candidates "
+                                                    "(plain layouts; 1 = no split)")
     ap.add_argument("--variants", default="", help="comma-separated variants to time one after the other on each case")
     a = ap.parse_args()
     variants = [int(v) for v in a.variants.split(",")] if a.variants else [a.variant]
@@ -91,6 +93,10 @@ def main():
             fn = lambda v: gemm(A, B, out, a_mn=a_mn, b_mn=b_mn, variant=v, epilogue=a.epilogue)  # noqa: E731
             flops = 2.0 * M * N * K
         cands = [(lambda v=v: fn(v)) for v in variants]
+        splits = [int(x) for x in a.split_k.split(",")] if a.split_k and layout in ("nt", "nn", "tn", "tt") else []
+        for sk in splits:
+            ws = torch.empty(sk * M, N, device=dev, dtype=torch.bfloat16)
+            cands.append(lambda sk=sk, ws=ws: gemm_split_k(A, B, out, sk, ws, a_mn=a_mn, b_mn=b_mn))
         if not a.no_cublas:
             Af = A.t() if a_mn else A
             Bf = B if b_mn else B.t()
@@ -103,6 +109,8 @@ def main():
             line += f" ours{'' if len(variants) == 1 else f'[v{v}]'} {t:8.3f} ms {flops / t / 1e9:7.1f} TFLOP/s"
             if peak:
                 line += f" ({flops / t / 1e9 / peak:.2f} of measured {peak:.0f})"
+        for sk, t in zip(splits, ts[len(variants):]):
+            line += f" split-k[{sk}] {t:8.3f} ms {flops / t / 1e9:7.1f} TFLOP/s"
         if not a.no_cublas:
             t2 = ts[-1]
             line += f" | cuBLAS {t2:8.3f} ms {flops / t2 / 1e9:7.1f} TFLOP/s | ours/cuBLAS " + \

@@ -29,7 +29,8 @@ from typing import List, Optional
 
 import torch
 
-from ..ops import EPI_DSWIGLU, EPI_SWIGLU, add_rmsnorm, gemm, mse_loss_grad, rmsnorm_bwd, sgd_step
+from ..ops import (EPI_DSWIGLU, EPI_SWIGLU, add_rmsnorm, gemm, gemm_split_k, mse_loss_grad, pick_split_k,
+                   rmsnorm_bwd, sgd_step)
 
 
 @dataclass
@@ -101,6 +102,7 @@ class TPMLPStack:
                      for _ in range(2)]
         self.dy0 = self.tp.shard_buffer() if self.tp is not None else None
         self.x_dev = torch.empty(self.Ts, d, **bf)
+        self._wgrad_ws = None  # partial products of split-K weight-gradient GEMMs
 
     def _full(self, T, d):
         if self.tp is not None:
@@ -144,18 +146,32 @@ class TPMLPStack:
             fl = layer.fl
             if self.tp is None:
                 gemm(dres, layer.w_down, self.dgu, b_mn=True, epilogue=EPI_DSWIGLU, aux=self.gu[l], n=fl)
-                gemm(dres, self.h[l], layer.g_down, a_mn=True, b_mn=True)
+                self._wgrad(dres, self.h[l], layer.g_down)
                 gemm(self.dgu, layer.w_gu, self.dn, b_mn=True)
-                gemm(self.dgu, self.xg[l], layer.g_gu, a_mn=True, b_mn=True)
+                self._wgrad(self.dgu, self.xg[l], layer.g_gu)
             else:
                 self.tp.ag_gemm_dswiglu(dres, self.dyg, layer.w_down, self.gu[l], self.dgu, fl)
-                gemm(self.dyg, self.h[l], layer.g_down, a_mn=True, b_mn=True)
+                self._wgrad(self.dyg, self.h[l], layer.g_down)
                 self.tp.gemm_rs(self.dgu, layer.w_gu, self.partial, self.dn, b_mn=True)
-                gemm(self.dgu, self.xg[l], layer.g_gu, a_mn=True, b_mn=True)
+                self._wgrad(self.dgu, self.xg[l], layer.g_gu)
             out = self.dres[l & 1]
             rmsnorm_bwd(self.dn, self._shard(self.xg[l]), self.inv_rms[l], dres, out)
             dres = out
         return dres
+
+    def _wgrad(self, a_t: torch.Tensor, b_t: torch.Tensor, out: torch.Tensor) -> None:
+        """out[M, N] = a_t^T @ b_t over all tokens (a_t: [T, M], b_t: [T, N]).  The output of a
+        sharded layer has few tiles and the token loop is long, so K is cut into the number of
+        ranges that fills the waves of CTA pairs best (1 = a plain GEMM)."""
+        M, N, K = a_t.shape[1], b_t.shape[1], a_t.shape[0]
+        splits = pick_split_k(M, N, K) if out.is_contiguous() else 1
+        if splits == 1:
+            gemm(a_t, b_t, out, a_mn=True, b_mn=True)
+            return
+        need = splits * M * N
+        if self._wgrad_ws is None or self._wgrad_ws.numel() < need:
+            self._wgrad_ws = torch.empty(need, dtype=torch.bfloat16, device=self.device)
+        gemm_split_k(a_t, b_t, out, splits, self._wgrad_ws[:need].view(splits * M, N), a_mn=True, b_mn=True)
 
     def optimizer_step(self) -> None:
         for layer in self.layers:

@@ -114,3 +114,70 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, **kw) -> to
     if rc != 0:
         raise RuntimeError(f"megray_gemm_bf16 failed (code {rc}) for M={args.M} N={args.N} K={args.K}")
     return (out, out2) if args.epilogue == EPI_SWIGLU else out
+
+
+# ---------------------------------------------------------------------------------- split K
+# A GEMM with few output tiles and a long K loop (the weight gradients of a sharded layer:
+# M x N small, K = all tokens) wastes a large part of its last wave: 224 tiles on 74 CTA pairs take
+# the time of 4 waves for the work of 3.03.  Cutting K into S ranges makes S times as many tiles
+# of 1/S the length, which fill the waves better; each range writes its own partial result (the
+# kernel's grouped-K form) and the N-way reduce kernel sums them.
+
+_split_ranges = {}
+
+
+def pick_split_k(M: int, N: int, K: int, sms: int = 148) -> int:
+    """Number of K ranges (1..8) that minimises the estimated time: waves of 512 x 256 tiles on
+    ``sms // 2`` CTA pairs, plus the bandwidth cost of writing and summing the partial results."""
+    if M % 256 or K < 4096:
+        return 1
+    pairs = max(1, sms // 2)
+    tile_m = 512 if M % 512 == 0 else 256
+    tiles = -(-M // tile_m) * -(-N // 256)
+    tile_s = 2.0 * tile_m * 256 * K / (17.5e12 if tile_m == 512 else 16e12)  # seconds, one full-K tile
+    best, best_t = 1, None
+    for s in range(1, 9):
+        if K // s < 2048:
+            break
+        t = -(-tiles * s // pairs) * tile_s / s
+        if s > 1:
+            t += (2 * s + 1) * M * N * 2 / 5.0e12  # partials written and read back, result written
+        if best_t is None or t < best_t * 0.97:  # a split must pay for itself
+            best, best_t = s, t
+    return best
+
+
+def gemm_split_k(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, splits: int, partial: torch.Tensor = None,
+                 *, a_mn: bool = False, b_mn: bool = False) -> torch.Tensor:
+    """``out = A @ B^T`` computed as ``splits`` partial products over disjoint K ranges (multiples
+    of 64) that are then summed in fp32.  ``out`` must be contiguous; ``partial`` is an optional
+    ``[splits * M, N]`` bf16 workspace."""
+    if splits <= 1:
+        return gemm(a, b, out, a_mn=a_mn, b_mn=b_mn)
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N = b.shape[1] if b_mn else b.shape[0]
+    if splits > 8 or M % 256 or not out.is_contiguous() or out.shape != (M, N):
+        raise ValueError("gemm_split_k: at most 8 ranges, M a multiple of 256, contiguous [M, N] output")
+    per = -(-(-(-K // 64)) // splits) * 64  # ceil(ceil(K / 64) / splits) * 64
+    key = (a.device.index, K, splits)
+    if key not in _split_ranges:
+        begin = [min(K, i * per) for i in range(splits)]
+        end = [min(K, (i + 1) * per) for i in range(splits)]
+        if any(e <= s for s, e in zip(begin, end)):
+            raise ValueError("gemm_split_k: K is too short for this many ranges")
+        _split_ranges[key] = (torch.tensor(begin, dtype=torch.int32, device=a.device),
+                              torch.tensor(end, dtype=torch.int32, device=a.device))
+    k_begin, k_end = _split_ranges[key]
+    if partial is None:
+        partial = torch.empty(splits * M, N, dtype=torch.bfloat16, device=a.device)
+    part = partial[: splits * M]
+    if part.shape[1] != N or not part.is_contiguous():
+        raise ValueError("gemm_split_k: the workspace must be a contiguous [>= splits * M, N] tensor")
+    gemm(a, b, part, a_mn=a_mn, b_mn=b_mn, n=N, k_begin=k_begin, k_end=k_end, groups=splits,
+         variant=3 if M % 512 == 0 else 2)
+    ptrs = (C.c_void_p * splits)(*[part.data_ptr() + i * M * N * 2 for i in range(splits)])
+    rc = _lib.load().megray_reduce_n(ptrs, splits, C.c_void_p(out.data_ptr()), M * N, 10, 10,  # MEGRAY_BFLOAT16
+                                     0, C.c_float(1.0), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f"megray_reduce_n failed ({rc})")
+    return out

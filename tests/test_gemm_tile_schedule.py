@@ -63,3 +63,17 @@ def test_grouped_problems_have_no_host_schedule():
     a.k_begin = 16  # any non-null device address: grouped-K ranges live on the device
     buf = (C.c_int * 16)()
     assert lib.megray_gemm_tile_schedule(C.byref(a), 148, buf, 4) == -1
+
+
+def test_split_k_choice_follows_the_wave_arithmetic():
+    """No GPU: the number of K ranges picked for the weight gradients of the sharded MLP."""
+    from megray_b200.ops.gemm import pick_split_k
+
+    T, d, F = 32768, 8192, 28672
+    # plenty of tiles: no split
+    assert pick_split_k(d, F, T) == 1 and pick_split_k(2 * F, d, T) == 1
+    # 8-way shard: 224 tiles on 74 CTA pairs would take 4 waves for the work of 3.03
+    assert pick_split_k(d, F // 8, T) > 1
+    assert pick_split_k(2 * F // 8, d, T) > 1
+    # short K or ragged M: never
+    assert pick_split_k(d, F // 8, 2048) == 1 and pick_split_k(d + 8, F // 8, T) == 1
