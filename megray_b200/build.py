@@ -98,6 +98,7 @@ def write_ninja(with_bins: bool) -> str:
         for name, srcs in (
             ("megray_test", sorted(glob.glob(os.path.join(ROOT, "tests", "cpp", "*.cpp")))),
             ("megray_bench", sorted(glob.glob(os.path.join(ROOT, "bench", "*.cpp")))),
+            ("all_reduce_threads", [os.path.join(ROOT, "examples", "all_reduce_threads.cpp")]),
         ):
             if not srcs:
                 continue

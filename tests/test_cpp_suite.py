@@ -35,3 +35,11 @@ def test_cpp_suite_on_cpu():
 def test_cpp_suite_with_gpus():
     out = _run()
     assert "0 failed" in out
+
+
+def test_example_program_runs_on_the_host_backend():
+    _binary()  # builds the example along with the test runner
+    exe = os.path.join(ROOT, "build", "all_reduce_threads")
+    out = subprocess.run([exe, "3", "shm"], capture_output=True, text=True, timeout=120,
+                         env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert out.returncode == 0 and "ok" in out.stdout, out.stdout + out.stderr
