@@ -16,6 +16,8 @@
 // also compiles against the reference's own headers and objects (-DMEGRAY_BENCH_REFERENCE):
 // that build is the like-for-like baseline.
 #include <cuda_runtime.h>
+
+#include <chrono>
 #include <getopt.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -53,6 +55,7 @@ struct BenchOptions {
     bool check = false;
     bool heap = false;  // NVL backend: buffers from the symmetric heap (zero-copy / NVSwitch kernels)
     bool reg = false;   // NVL backend: cudaMalloc buffers registered with the communicator (zero-copy)
+    bool host = false;  // shm backend with CPU ranks: host buffers, wall-clock timing, no GPU needed
 };
 
 const char* kAllFuncs[] = {"send_recv", "scatter", "gather", "all_to_all", "all_gather",
@@ -164,10 +167,23 @@ std::vector<Result> run_sizes(const BenchOptions& o, const std::string& func, Ba
     for (size_t s : sizes) max_unit = std::max(max_unit, s);
     for (int r = 0; r < n; ++r) {
         threads.emplace_back([&, r] {
-            CK(cudaSetDevice(r));
-            cudaStream_t stream;
-            CK(cudaStreamCreate(&stream));
-            auto ctx = CudaContext::make(stream);
+#ifndef MEGRAY_BENCH_REFERENCE
+            const bool host = o.host && backend == MEGRAY_SHM;
+#else
+            const bool host = false;
+#endif
+            cudaStream_t stream = nullptr;
+            std::shared_ptr<Context> ctx;
+            if (!host) {
+                CK(cudaSetDevice(r));
+                CK(cudaStreamCreate(&stream));
+                ctx = CudaContext::make(stream);
+            }
+#ifndef MEGRAY_BENCH_REFERENCE
+            else {
+                ctx = HostContext::make();
+            }
+#endif
             std::shared_ptr<Communicator> comm;
             try {
                 comm = get_communicator(static_cast<uint32_t>(n), static_cast<uint32_t>(r), backend);
@@ -195,7 +211,10 @@ std::vector<Result> run_sizes(const BenchOptions& o, const std::string& func, Ba
                 }
             }
 #endif
-            if (!from_heap) {
+            if (host) {
+                in = malloc(max_len * dt.size * (wide_in ? n : 1));
+                out = malloc(max_len * dt.size * (wide_out ? n : 1));
+            } else if (!from_heap) {
                 CK(cudaMalloc(&in, max_len * dt.size * (wide_in ? n : 1)));
                 CK(cudaMalloc(&out, max_len * dt.size * (wide_out ? n : 1)));
             }
@@ -210,11 +229,16 @@ std::vector<Result> run_sizes(const BenchOptions& o, const std::string& func, Ba
                     fprintf(stderr, "buffers could not be registered: staged paths\n");
             }
 #endif
-            CK(cudaMemset(in, r + 1, max_len * dt.size * (wide_in ? n : 1)));
-            CK(cudaMemset(out, 0, max_len * dt.size * (wide_out ? n : 1)));
-            cudaEvent_t e0, e1;
-            CK(cudaEventCreate(&e0));
-            CK(cudaEventCreate(&e1));
+            cudaEvent_t e0 = nullptr, e1 = nullptr;
+            if (host) {
+                memset(in, r + 1, max_len * dt.size * (wide_in ? n : 1));
+                memset(out, 0, max_len * dt.size * (wide_out ? n : 1));
+            } else {
+                CK(cudaMemset(in, r + 1, max_len * dt.size * (wide_in ? n : 1)));
+                CK(cudaMemset(out, 0, max_len * dt.size * (wide_out ? n : 1)));
+                CK(cudaEventCreate(&e0));
+                CK(cudaEventCreate(&e1));
+            }
             const uint32_t root = 0;
             for (size_t si = 0; si < sizes.size(); ++si) {
                 const size_t len = std::max<size_t>(1, sizes[si] / dt.size);
@@ -239,20 +263,32 @@ std::vector<Result> run_sizes(const BenchOptions& o, const std::string& func, Ba
                 const int warm = sizes[si] >= (256u << 20) ? std::max(2, o.warmup / 10) : o.warmup;
                 bool ok = true;
                 for (int i = 0; i < warm && ok; ++i) ok = call() == MEGRAY_OK;
-                CK(cudaStreamSynchronize(stream));
-                bar.wait();
-                CK(cudaEventRecord(e0, stream));
-                for (int i = 0; i < iters && ok; ++i) ok = call() == MEGRAY_OK;
-                CK(cudaEventRecord(e1, stream));
-                CK(cudaStreamSynchronize(stream));
-                float ms = 0.f;
-                CK(cudaEventElapsedTime(&ms, e0, e1));
-                times[si][r] = ms * 1000.0 / iters;
+                if (host) {
+                    // CPU ranks: the calls are synchronous, wall clock between two thread barriers
+                    bar.wait();
+                    const auto t0 = std::chrono::steady_clock::now();
+                    for (int i = 0; i < iters && ok; ++i) ok = call() == MEGRAY_OK;
+                    const auto t1 = std::chrono::steady_clock::now();
+                    times[si][r] = std::chrono::duration<double, std::micro>(t1 - t0).count() / iters;
+                } else {
+                    CK(cudaStreamSynchronize(stream));
+                    bar.wait();
+                    CK(cudaEventRecord(e0, stream));
+                    for (int i = 0; i < iters && ok; ++i) ok = call() == MEGRAY_OK;
+                    CK(cudaEventRecord(e1, stream));
+                    CK(cudaStreamSynchronize(stream));
+                    float ms = 0.f;
+                    CK(cudaEventElapsedTime(&ms, e0, e1));
+                    times[si][r] = ms * 1000.0 / iters;
+                }
                 if (!ok) bad[si]++;
                 if (o.check && ok && func == "all_reduce" && op == MEGRAY_SUM && dt.dtype == MEGRAY_UINT8) {
                     // every input byte is rank+1: the sum is n(n+1)/2 modulo 256
                     std::vector<uint8_t> h(std::min<size_t>(len, 4096));
-                    CK(cudaMemcpy(h.data(), out, h.size(), cudaMemcpyDeviceToHost));
+                    if (host)
+                        memcpy(h.data(), out, h.size());
+                    else
+                        CK(cudaMemcpy(h.data(), out, h.size(), cudaMemcpyDeviceToHost));
                     const uint8_t want = static_cast<uint8_t>(n * (n + 1) / 2);
                     for (uint8_t v : h)
                         if (v != want) bad[si]++;
@@ -267,13 +303,18 @@ std::vector<Result> run_sizes(const BenchOptions& o, const std::string& func, Ba
             }
 #endif
             comm.reset();
-            cudaEventDestroy(e0);
-            cudaEventDestroy(e1);
-            if (!from_heap) {
-                cudaFree(in);
-                cudaFree(out);
+            if (host) {
+                free(in);
+                free(out);
+            } else {
+                cudaEventDestroy(e0);
+                cudaEventDestroy(e1);
+                if (!from_heap) {
+                    cudaFree(in);
+                    cudaFree(out);
+                }
+                cudaStreamDestroy(stream);
             }
-            cudaStreamDestroy(stream);
         });
     }
     for (auto& t : threads) t.join();
@@ -289,6 +330,7 @@ void usage() {
     printf("megray_bench [-d devices] [-e nccl,nvl] [-f all_reduce,...|all] [-s 1K:1G | 8,1024,...]\n"
            "             [-t dtype] [-o sum|max|min] [-w warmup] [-i iters] [-j] [-c] [-H (NVL: symmetric-heap buffers)]\n"
            "             [-R (NVL: register the cudaMalloc buffers with the communicator)]\n"
+           "             [-C (shm backend with CPU ranks: host buffers, wall-clock timing; automatic without GPUs)]\n"
            "             [-I master_ip] [-P port] [-n nodes] [-r node_rank]\n");
 }
 
@@ -300,7 +342,7 @@ int main(int argc, char** argv) {
     std::string backends = "nccl";
     std::string funcs = "all";
     int c;
-    while ((c = getopt(argc, argv, "d:I:P:n:r:e:f:s:w:i:t:o:jcHRh")) != -1) {
+    while ((c = getopt(argc, argv, "d:I:P:n:r:e:f:s:w:i:t:o:jcHRCh")) != -1) {
         switch (c) {
             case 'd': o.devices = atoi(optarg); break;
             case 'I': o.master_ip = optarg; break;
@@ -318,6 +360,7 @@ int main(int argc, char** argv) {
             case 'c': o.check = true; break;
             case 'H': o.heap = true; break;
             case 'R': o.reg = true; break;
+            case 'C': o.host = true; break;
             default: usage(); return c == 'h' ? 0 : 1;
         }
     }
@@ -346,9 +389,16 @@ int main(int argc, char** argv) {
     }
     ReduceOp op = o.op == "max" ? MEGRAY_MAX : o.op == "min" ? MEGRAY_MIN : MEGRAY_SUM;
     int ndev = 0;
-    CK(cudaGetDeviceCount(&ndev));
-    if (ndev < o.devices) {
-        fprintf(stderr, "%d devices wanted, %d present\n", o.devices, ndev);
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        ndev = 0;
+    }
+    bool only_shm = true;
+    for (const auto& b : o.backends) only_shm = only_shm && b == "shm";
+    if (ndev < o.devices && only_shm) o.host = true;  // CPU ranks: the timed CPU baseline
+    if (!o.host && ndev < o.devices) {
+        fprintf(stderr, "%d devices wanted, %d present (the shm backend alone also runs with CPU ranks: -C)\n",
+                o.devices, ndev);
         return 1;
     }
     setenv("NCCL_LAUNCH_MODE", "PARALLEL", 0);  // the reference's NCCL backend insists on it
