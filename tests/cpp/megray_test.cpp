@@ -12,6 +12,7 @@
 #include <unistd.h>
 
 #include <atomic>
+#include <condition_variable>
 #include <memory>
 #include <mutex>
 #include <thread>
@@ -224,6 +225,46 @@ TEST(Communicator_InitEveryBackend) {
         if (rank == 0) ++seen;
     });
     EXPECT_TRUE(seen >= 1);
+}
+
+// init(BcastCallback): no rendezvous server at all; the caller supplies the broadcast (here a
+// board in this process), as the reference's embedding framework does
+// (include/megray/communicator.h:46-47 of the reference).
+TEST(Communicator_InitWithBroadcastCallback) {
+    const int n = 3;
+    struct Board {
+        std::mutex mu;
+        std::condition_variable cv;
+        std::vector<char> data;
+        int generation = 0;  // messages published so far
+        int taken = 0;       // readers that have copied the current message
+    } board;
+    run_ranks(n, [&](int rank) {
+        int seen = 0;  // messages this rank has been through
+        auto bcast = [&board, &seen, rank, n](char* buf, size_t len) {
+            std::unique_lock<std::mutex> lk(board.mu);
+            if (rank == 0) {
+                board.cv.wait(lk, [&] { return board.generation == 0 || board.taken == n - 1; });
+                board.data.assign(buf, buf + len);
+                board.taken = 0;
+                ++board.generation;
+            } else {
+                board.cv.wait(lk, [&] { return board.generation > seen; });
+                memcpy(buf, board.data.data(), len);
+                ++board.taken;
+            }
+            ++seen;
+            board.cv.notify_all();
+        };
+        auto comm = get_communicator(n, rank, MEGRAY_SHM);
+        if (comm->init(bcast) != MEGRAY_OK) throw std::runtime_error("init(callback) failed");
+        std::vector<float> in(10), out(10, 0.f);
+        for (int j = 0; j < 10; ++j) in[j] = cf(rank, j);
+        if (comm->all_reduce(in.data(), out.data(), 10, MEGRAY_FLOAT32, MEGRAY_SUM, HostContext::make()) != MEGRAY_OK)
+            throw std::runtime_error("all_reduce failed");
+        for (int j = 0; j < 10; ++j)
+            if (out[j] != cf(0, j) + cf(1, j) + cf(2, j)) throw std::runtime_error("wrong sum");
+    });
 }
 
 TEST(Communicator_UnknownBackendsThrow) {
