@@ -1,4 +1,5 @@
 #include "host/host_communicator.h"
+#include "megray/trace.h"
 
 #include <sched.h>
 #include <string.h>
@@ -211,6 +212,7 @@ Status HostCommunicator::run(const std::shared_ptr<Context>& ctx, const void* in
 Status HostCommunicator::all_gather(const void* sendbuff, void* recvbuff, size_t sendlen,
                                     DType dtype, std::shared_ptr<Context> ctx) {
     const size_t bytes = sendlen * get_dtype_size(dtype);
+    TraceScope trace("all_gather", bytes, m_rank);
     return run(ctx, sendbuff, bytes, recvbuff, bytes * m_nranks, [&](const char* in, char* out) {
         const size_t cap = m_region->slot_bytes();
         for (size_t off = 0; off < bytes || off == 0; off += cap) {
@@ -233,6 +235,7 @@ Status HostCommunicator::all_reduce(const void* sendbuff, void* recvbuff, size_t
         return MEGRAY_INVALID_ARGUMENT;
     const size_t esz = get_dtype_size(dtype);
     const size_t bytes = len * esz;
+    TraceScope trace("all_reduce", bytes, m_rank);
     return run(ctx, sendbuff, bytes, recvbuff, bytes, [&](const char* in, char* out) {
         const size_t cap_elems = m_region->slot_bytes() / esz;
         std::vector<const void*> srcs(m_nranks);
@@ -263,6 +266,7 @@ Status HostCommunicator::reduce_scatter(const void* sendbuff, void* recvbuff, si
         return MEGRAY_INVALID_ARGUMENT;
     const size_t esz = get_dtype_size(dtype);
     const size_t bytes = recvlen * esz;
+    TraceScope trace("reduce_scatter", bytes, m_rank);
     return run(ctx, sendbuff, bytes * m_nranks, recvbuff, bytes, [&](const char* in, char* out) {
         // each rank publishes, for every destination d, a piece of chunk d
         const size_t cap_elems = std::max<size_t>(1, m_region->slot_bytes() / m_nranks / esz);
@@ -288,6 +292,7 @@ Status HostCommunicator::reduce_scatter(const void* sendbuff, void* recvbuff, si
 Status HostCommunicator::all_to_all(const void* sendbuff, void* recvbuff, size_t len, DType dtype,
                                     std::shared_ptr<Context> ctx) {
     const size_t bytes = len * get_dtype_size(dtype);
+    TraceScope trace("all_to_all", bytes, m_rank);
     return run(ctx, sendbuff, bytes * m_nranks, recvbuff, bytes * m_nranks,
                [&](const char* in, char* out) {
                    const size_t cap = std::max<size_t>(1, m_region->slot_bytes() / m_nranks);
@@ -311,6 +316,7 @@ Status HostCommunicator::broadcast(const void* sendbuff, void* recvbuff, size_t 
     if (root >= m_nranks)
         return MEGRAY_INVALID_ARGUMENT;
     const size_t bytes = len * get_dtype_size(dtype);
+    TraceScope trace("broadcast", bytes, m_rank);
     const bool is_root = m_rank == root;
     return run(ctx, is_root ? sendbuff : nullptr, is_root ? bytes : 0, recvbuff, bytes,
                [&](const char* in, char* out) {
@@ -335,6 +341,7 @@ Status HostCommunicator::reduce(const void* sendbuff, void* recvbuff, size_t len
         return MEGRAY_INVALID_ARGUMENT;
     const size_t esz = get_dtype_size(dtype);
     const size_t bytes = len * esz;
+    TraceScope trace("reduce", bytes, m_rank);
     const bool is_root = m_rank == root;
     return run(ctx, sendbuff, bytes, is_root ? recvbuff : nullptr, is_root ? bytes : 0,
                [&](const char* in, char* out) {
@@ -363,6 +370,7 @@ Status HostCommunicator::gather(const void* sendbuff, void* recvbuff, size_t sen
     if (root >= m_nranks)
         return MEGRAY_INVALID_ARGUMENT;
     const size_t bytes = sendlen * get_dtype_size(dtype);
+    TraceScope trace("gather", bytes, m_rank);
     const bool is_root = m_rank == root;
     return run(ctx, sendbuff, bytes, is_root ? recvbuff : nullptr, is_root ? bytes * m_nranks : 0,
                [&](const char* in, char* out) {
@@ -387,6 +395,7 @@ Status HostCommunicator::scatter(const void* sendbuff, void* recvbuff, size_t re
     if (root >= m_nranks)
         return MEGRAY_INVALID_ARGUMENT;
     const size_t bytes = recvlen * get_dtype_size(dtype);
+    TraceScope trace("scatter", bytes, m_rank);
     const bool is_root = m_rank == root;
     return run(ctx, is_root ? sendbuff : nullptr, is_root ? bytes * m_nranks : 0, recvbuff, bytes,
                [&](const char* in, char* out) {
