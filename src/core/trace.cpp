@@ -100,6 +100,14 @@ size_t trace_dump() {
 TraceScope::TraceScope(const char* op, size_t bytes, uint32_t rank)
         : m_op(op), m_bytes(bytes), m_rank(rank), m_t0_us(0), m_file(trace_enabled()) {
 #ifdef MEGRAY_WITH_CUDA
+    // NVTX binds its entry points on the first call, without synchronisation of its own: rank
+    // threads that make their first call together would race there, so the first call is made
+    // once, alone.
+    static std::once_flag nvtx_bound;
+    std::call_once(nvtx_bound, [] {
+        nvtxRangePushA("megray::init");
+        nvtxRangePop();
+    });
     nvtxRangePushA(op);
 #endif
     if (m_file)
