@@ -81,6 +81,10 @@ def build(ref: str) -> str:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
-    print(build(ap.parse_args().reference))
+    ap.add_argument("--reference", default=os.environ.get("MEGRAY_REFERENCE"),
+                    help="checkout of the reference library (or set MEGRAY_REFERENCE)")
+    a = ap.parse_args()
+    if not a.reference:
+        ap.error("name the reference checkout with --reference or MEGRAY_REFERENCE")
+    print(build(a.reference))
     sys.exit(0)

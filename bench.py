@@ -46,10 +46,31 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--unfused", action="store_true", help="plain collectives instead of the fused kernels")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--reference", default=None,
+                    help="source tree of the reference library (only needed when baseline/_ref is not built yet)")
     return ap.parse_args()
 
 
 from megray_b200.utils.clocks import ClockSampler  # noqa: E402  (no torch / native code behind it)
+
+METRIC = ("TP-MLP tokens/s (bf16, d_model 8192, ffn 28672, SwiGLU, 32768 tokens, 4 pre-norm residual layers, "
+          "fwd+bwd+SGD)")
+
+
+def config_dict(args, world):
+    """The same keys and values in both arms (what differs between them goes under `arm`)."""
+    return {"model": f"tp_mlp_d{args.d_model}_f{args.ffn}_L{args.layers}_swiglu", "global_batch": args.tokens,
+            "seq_len": 4096, "parallelism": f"tp{world}+sp" if world > 1 else "single",
+            "l2": "inputs larger than L2 (weights 1.4 GB/layer, activations > 0.5 GB)"}
+
+
+def loss_file(args, world):
+    """Where the reference arm leaves its loss for this arm to compare with (same box, same
+    configuration, same number of steps)."""
+    import tempfile
+
+    key = f"n{world}_d{args.d_model}_f{args.ffn}_t{args.tokens}_L{args.layers}_w{args.warmup}_k{args.steps}"
+    return os.path.join(tempfile.gettempdir(), f"megray_bench_reference_loss_{key}.json")
 
 
 def relaunch_multi(args) -> int:
@@ -118,7 +139,14 @@ def run_ours(args, rank, world, local_rank):
     launches = lib.megray_launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
-    loss_val = float(loss.item())
+    # the loss of the whole batch: every rank holds the share of its token shard
+    if comm is not None:
+        total = torch.empty_like(loss)
+        comm.all_reduce(loss, total, "sum")
+        torch.cuda.synchronize()
+        loss_val = float(total.item())
+    else:
+        loss_val = float(loss.item())
 
     e2e = None
     if not args.no_e2e:
@@ -145,20 +173,34 @@ def run_ours(args, rank, world, local_rank):
         server.close()
     if rank != 0:
         return 0
+    # Both arms start from the same weights and tokens and take the same number of steps, so
+    # their losses must agree to bf16 accuracy.  The reference arm, when it ran before this one on
+    # this machine, left its loss in a file.
+    loss_check = None
+    try:
+        with open(loss_file(args, world)) as f:
+            ref_loss = float(json.load(f)["loss"])
+        rel = abs(loss_val - ref_loss) / max(abs(ref_loss), 1e-12)
+        loss_check = {"reference_loss": ref_loss, "rel_diff": rel, "ok": rel < 0.01}
+    except (OSError, ValueError, KeyError):
+        pass
     out = {
-        "metric": "TP-MLP tokens/s (bf16, d_model 8192, ffn 28672, SwiGLU, 32768 tokens, 4 pre-norm residual layers, fwd+bwd+SGD)",
+        "metric": METRIC,
         "value": cfg.tokens / (ms / 1000.0), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": f"tp_mlp_d{cfg.d_model}_f{cfg.ffn}_L{cfg.layers}_swiglu", "global_batch": cfg.tokens,
-                   "seq_len": 4096, "parallelism": f"tp{world}+sp" if world > 1 else "single",
-                   "l2": "inputs larger than L2 (weights 1.4 GB/layer, activations > 0.5 GB)",
-                   "fused_collectives": world > 1 and not args.unfused},
+        "config": config_dict(args, world),
+        "arm": {"stack": "tcgen05 GEMM kernels + native NVL collectives of this library",
+                "fused_collectives": world > 1 and not args.unfused},
         "tflops_per_gpu": model.flops_per_step() / world / (ms / 1000.0) / 1e12,
         "gpu_launches": int(launches), "clocks": clocks, "e2e": e2e, "loss": loss_val,
-        "kernel_error_flag": err, "comm_status": status,
+        "loss_check": loss_check, "kernel_error_flag": err, "comm_status": status,
     }
     print(json.dumps(out), flush=True)
+    if loss_check is not None and not loss_check["ok"]:
+        print(f"bench.py: loss {loss_val} differs from the reference arm's {loss_check['reference_loss']} "
+              f"by more than 1 %", file=sys.stderr)
+        return 1
     return 0 if err == 0 and status == 0 else 1
 
 
@@ -175,7 +217,11 @@ def run_reference(args, rank, world, local_rank):
             sys.path.insert(0, os.path.join(ROOT, "baseline"))
             import build_ref
 
-            build_ref.build(os.environ.get("MEGRAY_REFERENCE", "/root/reference"))
+            src = args.reference or os.environ.get("MEGRAY_REFERENCE")
+            if not src:
+                raise RuntimeError("baseline/_ref is not built and neither --reference nor MEGRAY_REFERENCE "
+                                   "names the reference source tree")
+            build_ref.build(src)
         except Exception as e:  # noqa: BLE001
             if rank == 0:
                 print(json.dumps({"impl": "reference", "unavailable":
@@ -247,16 +293,23 @@ def run_reference(args, rank, world, local_rank):
     fl = f // world
     params = []
     for l in range(L):
+        # one globally seeded weight per layer, then this rank's slice: the same numbers as the
+        # library arm's model (megray_b200/models/tp_mlp.py) for every number of ranks
         gen = torch.Generator(device=dev).manual_seed(l)
-        w_gu = torch.empty(2 * fl, d, device=dev, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
-        w_dn = torch.empty(d, fl, device=dev, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
+        w_gate = torch.empty(f, d, device=dev, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
+        w_up = torch.empty(f, d, device=dev, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
+        w_down = torch.empty(d, f, device=dev, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
+        sl = slice(rank * fl, (rank + 1) * fl)
+        w_gu = torch.cat([w_gate[sl], w_up[sl]], 0).contiguous()
+        w_dn = w_down[:, sl].contiguous()
+        del w_gate, w_up, w_down
         params.append((w_gu.requires_grad_(), w_dn.requires_grad_()))
+    torch.cuda.empty_cache()
     opt = torch.optim.SGD([p for pair in params for p in pair], lr=1e-4)
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
     x_dev = torch.randn(T // world, d, device=dev, generator=gen).to(torch.bfloat16)
     x_host = torch.empty(x_dev.shape, dtype=torch.bfloat16, pin_memory=True)
     x_host.copy_(x_dev)
-    x_buf = torch.empty_like(x_dev)
 
     def step(x):
         h = x
@@ -268,11 +321,11 @@ def run_reference(args, rank, world, local_rank):
             act = F.silu(g_) * u_
             yp = act @ w_dn.t()
             h = h + (ReduceScatter.apply(yp) if world > 1 else yp)
-        loss = h.float().pow(2).sum() / (T * d)
+        loss = h.float().pow(2).sum() / (T * d)   # this rank's share of the mean over all tokens
         opt.zero_grad(set_to_none=True)
         loss.backward()
         opt.step()
-        return loss
+        return loss.detach()
 
     def barrier():
         if world > 1:
@@ -280,11 +333,11 @@ def run_reference(args, rank, world, local_rank):
             ref.ref_all_reduce(comm, t.data_ptr(), t.data_ptr(), 1, FLOAT32, 0, stream())
         torch.cuda.synchronize()
 
-    def max_over_ranks(v):
+    def over_ranks(v, op):
         if world == 1:
             return v
         t = torch.tensor([v], device=dev, dtype=torch.float32)
-        ref.ref_all_reduce(comm, t.data_ptr(), t.data_ptr(), 1, FLOAT32, 1, stream())
+        ref.ref_all_reduce(comm, t.data_ptr(), t.data_ptr(), 1, FLOAT32, op, stream())
         torch.cuda.synchronize()
         return float(t.item())
 
@@ -301,34 +354,94 @@ def run_reference(args, rank, world, local_rank):
     e1.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
-    ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    ms = over_ranks(e0.elapsed_time(e1) / args.steps, 1)
+    loss_val = over_ranks(float(loss.item()), 0)   # sum of the ranks' shares
+
+    # What the fp16 wire format costs this arm: the reference has no bf16, so every reduce_scatter
+    # is wrapped in a bf16 -> fp16 cast of its input and an fp16 -> bf16 cast of its result.  Timed
+    # on their own here (same tensors, outside the step) so that the share can be read off.
+    cast_ms = 0.0
+    if world > 1:
+        big = torch.empty(T, d, device=dev, dtype=torch.bfloat16).normal_()
+        small = torch.empty(T // world, d, device=dev, dtype=torch.float16).normal_()
+        for _ in range(2):
+            big.to(torch.float16), small.to(torch.bfloat16)
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        c0.record()
+        for _ in range(5):
+            big.to(torch.float16), small.to(torch.bfloat16)
+        c1.record()
+        torch.cuda.synchronize()
+        cast_ms = c0.elapsed_time(c1) / 5 * 2 * L   # one reduce_scatter forward and one backward per layer
+        del big, small
+
     e2e = None
     if not args.no_e2e:
+        # the same loop shape as the library arm's train_step_async: this step's tokens are copied
+        # from pinned host memory on a copy stream into one of two device buffers, and this step's
+        # loss travels back to pinned host memory asynchronously and is read one call later
+        copy_stream = torch.cuda.Stream()
+        xs = [torch.empty_like(x_dev) for _ in range(2)]
+        loss_host = torch.zeros(2, dtype=torch.float32, pin_memory=True)
+        free, done = [None, None], [None, None]
+        state = {"i": 0}
+
         def e2e_step():
-            x_buf.copy_(x_host, non_blocking=True)
-            return float(step(x_buf).item())
+            k = state["i"] & 1
+            main = torch.cuda.current_stream()
+            with torch.cuda.stream(copy_stream):
+                if free[k] is not None:
+                    copy_stream.wait_event(free[k])
+                xs[k].copy_(x_host, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(copy_stream)
+            main.wait_event(ready)
+            lo = step(xs[k])
+            free[k] = torch.cuda.Event()
+            free[k].record(main)
+            loss_host[k:k + 1].copy_(lo.reshape(1), non_blocking=True)
+            done[k] = torch.cuda.Event()
+            done[k].record(main)
+            state["i"] += 1
+            if done[k ^ 1] is not None:
+                done[k ^ 1].synchronize()
+                return float(loss_host[k ^ 1])
+            return None
+
+        def e2e_flush():
+            k = (state["i"] - 1) & 1
+            done[k].synchronize()
+            return float(loss_host[k])
 
         e2e_step()
+        e2e_flush()
         barrier()
         t0 = time.perf_counter()
         for _ in range(args.steps):
             e2e_step()
+        e2e_flush()
         barrier()
-        e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1000.0 / args.steps)
+        e2e_ms = over_ranks((time.perf_counter() - t0) * 1000.0 / args.steps, 1)
         e2e = {"value": T / (e2e_ms / 1000.0), "unit": "tokens/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": 4}
     if rank == 0:
+        try:
+            with open(loss_file(args, world), "w") as fh:
+                json.dump({"loss": loss_val}, fh)
+        except OSError:
+            pass
         print(json.dumps({
-            "metric": "TP-MLP tokens/s (bf16, d_model 8192, ffn 28672, SwiGLU, 32768 tokens, 4 pre-norm residual layers, fwd+bwd+SGD)",
+            "metric": METRIC,
             "value": T / (ms / 1000.0), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
-            "config": {"model": f"tp_mlp_d{d}_f{f}_L{L}_swiglu", "global_batch": T, "seq_len": 4096,
-                       "parallelism": f"tp{world}+sp" if world > 1 else "single",
-                       "l2": "inputs larger than L2",
-                       "stack": "torch.matmul/autograd/SGD + reference MegRay NCCL backend (fp16 wire format)"},
+            "config": config_dict(args, world),
+            "arm": {"stack": "torch.matmul/autograd/SGD + reference MegRay NCCL backend (fp16 wire format)",
+                    "wire_cast_ms_per_step": cast_ms,
+                    "value_without_wire_casts": T / (max(ms - cast_ms, 1e-9) / 1000.0)},
             "tflops_per_gpu": 18.0 * T * d * f * L / world / (ms / 1000.0) / 1e12,
-            "gpu_launches": 0, "clocks": clocks, "e2e": e2e, "loss": float(loss.item()),
+            "gpu_launches": 0, "clocks": clocks, "e2e": e2e, "loss": loss_val,
         }), flush=True)
     ref.ref_comm_delete.argtypes = [C.c_void_p]
     ref.ref_comm_delete(comm)

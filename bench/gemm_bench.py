@@ -42,6 +42,31 @@ def time_round_robin(fns, warmup, iters):
     return [sorted(t)[len(t) // 2] for t in times]
 
 
+def time_sustained(fn, seconds, index=0):
+    """Runs `fn` back to back for about `seconds` under the clock sampler.  Returns milliseconds per
+    launch (CUDA events around the whole loop) and the sampler's record: at the power cap the
+    clock the kernel settles at tells how much energy one launch costs."""
+    from megray_b200.utils.clocks import ClockSampler
+
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    fn()
+    e1.record()
+    torch.cuda.synchronize()
+    n = max(5, int(seconds * 1000.0 / max(e0.elapsed_time(e1), 1e-3)))
+    sampler = ClockSampler(index).start()
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    rec = sampler.stop()
+    return e0.elapsed_time(e1) / n, rec
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--m", type=int)
@@ -55,6 +80,9 @@ def main():
     ap.add_argument("--variant", type=int, default=0, help="0 = automatic, 1 = single-CTA 128x256 tile, 2 = CTA-pair 256x256 tile, 3 = CTA-pair 512x256 tile")
     ap.add_argument("--split-k", default="", help="comma-separated K-range counts to time as extra candidates "
                                                     "(plain layouts; 1 = no split)")
+    ap.add_argument("--sustain", type=float, default=0.0,
+                    help="also run every candidate back to back for this many seconds and report its time, "
+                         "median SM MHz, maximum power and time x MHz (energy per launch at the power cap)")
     ap.add_argument("--variants", default="", help="comma-separated variants to time one after the other on each case")
     a = ap.parse_args()
     variants = [int(v) for v in a.variants.split(",")] if a.variants else [a.variant]
@@ -116,6 +144,15 @@ def main():
             line += f" | cuBLAS {t2:8.3f} ms {flops / t2 / 1e9:7.1f} TFLOP/s | ours/cuBLAS " + \
                     "/".join(f"{t2 / t:.3f}" for t in ts[:-1])
         print(line, flush=True)
+        if a.sustain > 0:
+            names = [f"ours[v{v}]" for v in variants] + [f"split-k[{sk}]" for sk in splits] + \
+                    ([] if a.no_cublas else ["cuBLAS"])
+            for name, fn_c in zip(names, cands):
+                t, rec = time_sustained(fn_c, a.sustain)
+                mhz = rec.get("sm_mhz") or 0.0
+                print(f"    sustained {a.sustain:.0f} s  {name:12s} {t:8.3f} ms {flops / t / 1e9:7.1f} TFLOP/s  "
+                      f"median {mhz:.0f} MHz  max {rec.get('power_w_max')} W  temp {rec.get('temp_c')}  "
+                      f"reasons {rec.get('reasons')}  time x MHz {t * mhz:9.1f}", flush=True)
         del A, B, out
 
 

@@ -1,14 +1,16 @@
 #!/usr/bin/env python
-"""Measures the algorithm crossover points of the NVL backend and writes the tune table.
+"""Measures the algorithm crossover points of the NVL backend on this machine and writes the
+tune table a communicator loads (MEGRAY_TUNE_FILE, or megray_b200/tune/tune_b200_n<ranks>.json
+when that file exists).
 
-Runs ``build/megray_bench`` (threads as ranks, device-timed, max over ranks) for all_reduce over a
-range of message sizes with the one-shot threshold forced low and high and with several grid
-sizes, picks for each size the fastest setting, and writes a JSON file that a communicator reads
-when ``MEGRAY_TUNE_FILE`` names it:
+For every operation it runs ``build/megray_bench`` (threads as ranks, device-timed, max over
+ranks, float32) over the small and middle sizes with each algorithm forced in turn and keeps, per
+operation, the largest size up to which the flagged-word kernel is the fastest; for all_reduce
+also the size up to which the one-shot kernel beats the single-pass one; and, when the NVSwitch
+multicast object can be set up (``--nvls``: MEGRAY_NVLS=1 in the benchmark processes only), the
+size from which the multimem kernels beat plain peer loads and stores on heap buffers.
 
-    {"oneshot_bytes": ..., "max_ctas": ..., "cta_bytes": ..., "measured": {...}}
-
-    python bench/tune.py --devices 8 --out tune_8gpu.json
+    python bench/tune.py --devices 8 --out megray_b200/tune/tune_b200_n8.json
 """
 import argparse
 import json
@@ -17,44 +19,91 @@ import subprocess
 import sys
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+KINDS = ["all_reduce", "reduce_scatter", "all_gather", "all_to_all", "broadcast", "reduce", "gather", "scatter"]
 
 
-def run(devices, sizes, env):
+def run(devices, funcs, sizes, env, extra=()):
     e = dict(os.environ, **env)
-    cmd = [os.path.join(ROOT, "build", "megray_bench"), "-d", str(devices), "-e", "nvl", "-f", "all_reduce",
-           "-s", ",".join(str(s) for s in sizes), "-t", "float32", "-w", "10", "-i", "30", "-j"]
-    out = subprocess.run(cmd, capture_output=True, text=True, env=e, timeout=600)
+    cmd = [os.path.join(ROOT, "build", "megray_bench"), "-d", str(devices), "-e", "nvl", "-f", ",".join(funcs),
+           "-s", ",".join(str(s) for s in sizes), "-t", "float32", "-w", "10", "-i", "40", "-j", *extra]
+    out = subprocess.run(cmd, capture_output=True, text=True, env=e, timeout=900)
     res = {}
     for line in out.stdout.splitlines():
         if line.startswith("{"):
             d = json.loads(line)
             if d["ok"]:
-                res[d["bytes"]] = d["time_us"]
+                res[(d["op"], d["bytes"])] = (d["time_us"], d.get("algo", "-"))
+    if not res:
+        sys.stderr.write(out.stderr[-2000:])
     return res
+
+
+def crossover(sizes, a, b, func, margin=1.0):
+    """Largest size s such that a is at least as fast as b (times `margin`) at every size <= s."""
+    best = 0
+    for s in sizes:
+        ta, tb = a.get((func, s)), b.get((func, s))
+        if ta is None or tb is None or ta[0] > tb[0] * margin:
+            break
+        best = s
+    return best
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--devices", type=int, default=2)
-    ap.add_argument("--out", default="tune.json")
+    ap.add_argument("--out", default=None)
+    ap.add_argument("--nvls", action="store_true", help="also measure the NVSwitch multimem kernels (heap buffers)")
     a = ap.parse_args()
-    sizes = [1 << k for k in range(10, 25)]
-    one = run(a.devices, sizes, {"MEGRAY_ALGO": "oneshot"})
-    two = run(a.devices, sizes, {"MEGRAY_ALGO": "twoshot"})
-    crossover = 0
-    for s in sizes:
-        if s in one and s in two and one[s] <= two[s]:
-            crossover = s
-    best_cta, best_t = 128 * 1024, None
-    big = [1 << 24, 1 << 26]
-    for cta_bytes in (32 << 10, 64 << 10, 128 << 10, 256 << 10):
-        r = run(a.devices, big, {"MEGRAY_ALGO": "twoshot", "MEGRAY_CTA_BYTES": str(cta_bytes)})
-        t = sum(r.get(s, 1e18) for s in big)
-        if best_t is None or t < best_t:
-            best_cta, best_t = cta_bytes, t
-    table = {"oneshot_bytes": crossover, "max_ctas": 64, "cta_bytes": best_cta, "nvls_min_bytes": 0,
-             "devices": a.devices, "measured": {"oneshot_us": one, "twoshot_us": two}}
-    with open(a.out, "w") as f:
+    out_path = a.out or os.path.join(ROOT, "megray_b200", "tune", f"tune_b200_n{a.devices}.json")
+    table = {"devices": a.devices, "measured": {}}
+
+    # flagged words against what would run otherwise (one-shot / single pass / staged)
+    small = [1 << k for k in range(10, 17)]  # 1 KiB .. 64 KiB per source / destination pair
+    with_ll = run(a.devices, KINDS, small, {"MEGRAY_LL_BYTES": str(64 << 10)})
+    without = run(a.devices, KINDS, small, {"MEGRAY_LL_BYTES": "0"})
+    for k in KINDS:
+        table[f"ll_{k}"] = crossover(small, with_ll, without, k)
+        table["measured"][f"us_ll_vs_other_{k}"] = {str(s): [with_ll.get((k, s), [None])[0], without.get((k, s), [None])[0]]
+                                        for s in small}
+
+    # all_reduce: one-shot (one barrier, staging slots) against single pass (two barriers, no staging)
+    mid = [1 << k for k in range(15, 23)]  # 32 KiB .. 4 MiB
+    one = run(a.devices, ["all_reduce"], mid, {"MEGRAY_LL_BYTES": "0", "MEGRAY_ONESHOT_BYTES": str(1 << 30)})
+    two = run(a.devices, ["all_reduce"], mid, {"MEGRAY_LL_BYTES": "0", "MEGRAY_ONESHOT_BYTES": "0"})
+    table["oneshot_bytes"] = crossover(mid, one, two, "all_reduce")
+    table["measured"]["us_oneshot_vs_single_pass"] = {str(s): [one.get(("all_reduce", s), [None])[0], two.get(("all_reduce", s), [None])[0]]
+                                    for s in mid}
+
+    # grid size of the single-pass kernels at a bandwidth-bound size
+    big = [64 << 20]
+    best_ctas, best_t = 64, None
+    for ctas in (32, 64):
+        r = run(a.devices, ["all_reduce", "all_gather"], big, {"MEGRAY_MAX_CTAS": str(ctas)})
+        t = sum(v[0] for v in r.values()) if len(r) == 2 else None
+        table["measured"][f"us_sum_at_{ctas}_ctas"] = t
+        if t is not None and (best_t is None or t < best_t):
+            best_ctas, best_t = ctas, t
+    table["max_ctas"] = best_ctas
+
+    if a.nvls:
+        sizes = [1 << k for k in range(18, 29, 2)]  # 256 KiB .. 256 MiB
+        env = {"MEGRAY_NVLS": "1", "NCCL_NVLS_ENABLE": "1", "MEGRAY_HEAP_MB": "2048"}
+        mc = run(a.devices, ["all_reduce"], sizes, dict(env), extra=("-H",))
+        p2p = run(a.devices, ["all_reduce"], sizes, dict(env, MEGRAY_NVLS="0"), extra=("-H",))
+        first = 0
+        for s in reversed(sizes):
+            if (("all_reduce", s) in mc and ("all_reduce", s) in p2p and mc[("all_reduce", s)][1] == "nvls" and
+                    mc[("all_reduce", s)][0] <= p2p[("all_reduce", s)][0]):
+                first = s
+            else:
+                break
+        table["nvls_min_bytes"] = first if first else (1 << 62)
+        table["measured"]["us_nvls_vs_p2p"] = {str(s): [mc.get(("all_reduce", s), [None])[0], p2p.get(("all_reduce", s), [None])[0]]
+                                     for s in sizes}
+    table["measured"] = table.pop("measured")  # the raw timings go last: the library reads the first match of a key
+    os.makedirs(os.path.dirname(out_path), exist_ok=True)
+    with open(out_path, "w") as f:
         json.dump(table, f, indent=1)
     print(json.dumps({k: v for k, v in table.items() if k != "measured"}))
 

@@ -78,7 +78,7 @@ int megray_comm_init(void* comm, const char* ip, int port);
 int megray_comm_backend(void* comm);
 int megray_comm_status(void* comm);
 void megray_comm_abort(void* comm);
-/* out[0..8) = calls, bytes, kernels, timeouts, oneshot, twoshot, nvls, copy */
+/* out[0..10) = calls, bytes, kernels, timeouts, oneshot, twoshot, nvls, copy, ll, direct */
 void megray_comm_stats(void* comm, uint64_t* out);
 
 int megray_send(void* comm, const void* buf, size_t len, int dtype, uint32_t peer, int ctx_type, void* stream);
@@ -133,11 +133,14 @@ size_t megray_trace_dump(void);
  * symmetric heap); `shard_src` is this rank's [M/n, K] shard (in the heap, possibly its own rows of
  * gather_buf).  GEMM -> reduce_scatter: D of `args` is ignored; `staging` holds n slots of
  * [M/n, N]; `out` receives this rank's reduced [M/n, N] shard (+ residual).  `flags`: a 256-byte
- * zero-initialised block in the heap, the same block for every call on the same buffers. */
+ * zero-initialised block in the heap, the same block for every call on the same gather buffer.
+ * `counters`: megray_tp_rs_counter_bytes(M/n, N) zero-initialised bytes in the heap (the same
+ * offset on every rank), the same block for every call on the same staging buffer. */
 int megray_tp_ag_gemm(void* comm, const megray_gemm_args* args, void* gather_buf, const void* shard_src,
                       void* flags, void* stream);
 int megray_tp_gemm_rs(void* comm, const megray_gemm_args* args, void* staging, void* out,
-                      const void* residual, void* flags, void* stream);
+                      const void* residual, void* counters, size_t counter_bytes, void* stream);
+size_t megray_tp_rs_counter_bytes(int shard_rows, int n_cols);
 
 /* ---- expert-parallel MoE kernels (src/kernels/moe.cuh) ---------------------------------------- */
 int megray_moe_route(const float* logits, int tokens, int experts, int* idx, float* w, int* counts, void* stream);

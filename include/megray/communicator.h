@@ -44,6 +44,8 @@ struct CommStats {
     uint64_t algo_twoshot = 0;
     uint64_t algo_nvls = 0;
     uint64_t algo_copy = 0;
+    uint64_t algo_ll = 0;       /* small messages as flagged words (no barrier) */
+    uint64_t algo_direct = 0;   /* single-pass kernels on the peers' buffers themselves */
 };
 
 class Communicator {

@@ -65,6 +65,19 @@ public:
     /** Barrier on the stream: later work of every rank starts after earlier work of all ranks. */
     virtual Status stream_barrier(std::shared_ptr<Context> ctx) = 0;
 
+    /** What every collective of this communicator does before its launch, for fused entry points
+     *  of other modules (the GEMM-fused tensor-parallel calls): refuses with the communicator's
+     *  state when it is not initialised, aborted or failed (a kernel wait that ran out earlier),
+     *  and orders `stream` after the communicator's previous launch on another stream. */
+    virtual Status fused_begin(void* stream) = 0;
+    /** Records that a kernel using the communicator's flags was launched on `stream`. */
+    virtual void fused_end(void* stream) = 0;
+    /** How many fused calls have used the counter block at `flags` (symmetric-heap memory),
+     *  this one included.  The count belongs to the communicator and to the allocation: it
+     *  starts again from 1 after sym_free of that memory or for a new communicator, which is
+     *  when the counters themselves are zero again. */
+    virtual uint32_t fused_call_count(const void* flags) = 0;
+
     /** Next flag epoch for kernels of other modules that synchronise through the pad
      *  (`count` consecutive values are reserved). */
     virtual uint32_t reserve_epochs(uint32_t count) = 0;

@@ -17,10 +17,17 @@
  * count), records it in pos_out[t,k] and stores scale * src[t, :] at that row of the buffer of
  * the rank that owns the expert (scale = w[t,k], or 1 if w is NULL).
  *
+ * Layout: routing is top-2.  idx (int32), w (float32, may be NULL) and pos_out (int32) are
+ * row-major [tokens, 2] arrays; src is [tokens, row_elems] bf16; send_base has `experts` entries;
+ * expert e lives on rank e / local_experts, whose buffer is peer_bufs[e / local_experts]
+ * ([capacity_rows, row_elems] bf16).  Tables of any other top-k do not fit this call.
+ * An idx entry outside [0, experts) is not an error of the call: that (token, slot) is dropped,
+ * its pos_out is -1, and no cursor and no buffer is touched for it.
+ *
  * Limits and rules:
- *  - at most MEGRAY_NOALLOC_MAX_EXPERTS experts; a larger `experts` (or nranks > 8, or a row
- *    length that is not a multiple of 8 elements) is refused with return value 6 and a message
- *    on stderr, and nothing is launched;
+ *  - at most MEGRAY_NOALLOC_MAX_EXPERTS experts; a larger `experts` (or nranks > 8, or
+ *    experts > nranks * local_experts, or a row length that is not a multiple of 8 elements) is
+ *    refused with return value 6 and a message on stderr, and nothing is launched;
  *  - the cursor array (MEGRAY_NOALLOC_MAX_EXPERTS * 4 bytes) is part of the library and stays
  *    resident on every GPU that loads it, until the process exits;
  *  - the first call on each device looks the array's device address up (with that device

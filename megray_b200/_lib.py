@@ -120,7 +120,8 @@ def _declare(lib) -> None:
     d("megray_add_rmsnorm_bf16", i32, vp, vp, vp, vp, vp, i32, i32, C.c_float, vp)
     d("megray_rmsnorm_bwd_bf16", i32, vp, vp, vp, vp, vp, i32, i32, vp)
     d("megray_tp_ag_gemm", i32, vp, P(GemmArgs), vp, vp, vp, vp)
-    d("megray_tp_gemm_rs", i32, vp, P(GemmArgs), vp, vp, vp, vp, vp)
+    d("megray_tp_gemm_rs", i32, vp, P(GemmArgs), vp, vp, vp, vp, C.c_size_t, vp)
+    d("megray_tp_rs_counter_bytes", C.c_size_t, i32, i32)
     d("megray_moe_route", i32, vp, i32, i32, vp, vp, vp, vp)
     d("megray_moe_route_bwd", i32, vp, vp, vp, i32, i32, vp, vp)
     d("megray_moe_plan", i32, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp)

@@ -93,6 +93,18 @@ class _Buf:
         self.cuda = x.is_cuda
 
 
+def _require(cond: bool, what: str) -> None:
+    """Length / dtype contracts of include/megray/communicator.h, checked before the native call
+    (which trusts them and would otherwise write past a tensor)."""
+    if not cond:
+        raise ValueError(what)
+
+
+def _same_dtype(a: "_Buf", b: "_Buf", op: str) -> None:
+    if a.ptr is not None and b.ptr is not None:
+        _require(a.dtype == b.dtype, f"{op}: send and recv must have the same dtype")
+
+
 def _ctx(bufs, stream):
     """(ctx_type, stream handle) for the buffers of one call."""
     cuda = [b.cuda for b in bufs if b.cuda is not None]
@@ -239,9 +251,9 @@ class Communicator:
         self._lib.megray_comm_abort(self._h)
 
     def stats(self) -> dict:
-        out = (C.c_uint64 * 8)()
+        out = (C.c_uint64 * 10)()
         self._lib.megray_comm_stats(self._h, out)
-        keys = ["calls", "bytes", "kernels", "timeouts", "oneshot", "twoshot", "nvls", "copy"]
+        keys = ["calls", "bytes", "kernels", "timeouts", "oneshot", "twoshot", "nvls", "copy", "ll", "direct"]
         return dict(zip(keys, [int(v) for v in out]))
 
     # -- operations ------------------------------------------------------------------------
@@ -258,34 +270,53 @@ class Communicator:
     def scatter(self, send, recv, root: int, stream=None) -> None:
         r = _Buf(recv)
         s = _Buf(send, r.dtype)
+        _same_dtype(s, r, "scatter")
+        _require(r.ptr is not None, "scatter: every rank needs a recv buffer")
+        if self.rank == root:
+            _require(s.ptr is not None and s.numel == self.nranks * r.numel,
+                     "scatter: the root's send buffer must hold nranks * recv.numel elements")
         ct, st = _ctx([s, r], stream)
         _check(self._lib.megray_scatter(self._h, s.ptr, r.ptr, r.numel, r.dtype, root, ct, st), "scatter")
 
     def gather(self, send, recv, root: int, stream=None) -> None:
         s = _Buf(send)
         r = _Buf(recv, s.dtype)
+        _same_dtype(s, r, "gather")
+        _require(s.ptr is not None, "gather: every rank needs a send buffer")
+        if self.rank == root:
+            _require(r.ptr is not None and r.numel == self.nranks * s.numel,
+                     "gather: the root's recv buffer must hold nranks * send.numel elements")
         ct, st = _ctx([s, r], stream)
         _check(self._lib.megray_gather(self._h, s.ptr, r.ptr, s.numel, s.dtype, root, ct, st), "gather")
 
     def all_to_all(self, send, recv, stream=None) -> None:
         s, r = _Buf(send), _Buf(recv)
+        _same_dtype(s, r, "all_to_all")
+        _require(s.numel % self.nranks == 0 and r.numel == s.numel,
+                 "all_to_all: send and recv must hold the same multiple of nranks elements")
         ct, st = _ctx([s, r], stream)
         _check(self._lib.megray_all_to_all(self._h, s.ptr, r.ptr, s.numel // self.nranks, s.dtype, ct, st),
                "all_to_all")
 
     def all_gather(self, send, recv, stream=None) -> None:
         s, r = _Buf(send), _Buf(recv)
+        _same_dtype(s, r, "all_gather")
+        _require(r.numel == self.nranks * s.numel, "all_gather: recv must hold nranks * send.numel elements")
         ct, st = _ctx([s, r], stream)
         _check(self._lib.megray_all_gather(self._h, s.ptr, r.ptr, s.numel, s.dtype, ct, st), "all_gather")
 
     def all_reduce(self, send, recv, op="sum", stream=None) -> None:
         s, r = _Buf(send), _Buf(recv)
+        _same_dtype(s, r, "all_reduce")
+        _require(r.numel == s.numel, "all_reduce: send and recv must hold the same number of elements")
         ct, st = _ctx([s, r], stream)
         _check(self._lib.megray_all_reduce(self._h, s.ptr, r.ptr, s.numel, s.dtype, _op(op), ct, st),
                "all_reduce")
 
     def reduce_scatter(self, send, recv, op="sum", stream=None) -> None:
         s, r = _Buf(send), _Buf(recv)
+        _same_dtype(s, r, "reduce_scatter")
+        _require(s.numel == self.nranks * r.numel, "reduce_scatter: send must hold nranks * recv.numel elements")
         ct, st = _ctx([s, r], stream)
         _check(self._lib.megray_reduce_scatter(self._h, s.ptr, r.ptr, r.numel, s.dtype, _op(op), ct, st),
                "reduce_scatter")
@@ -293,12 +324,22 @@ class Communicator:
     def broadcast(self, send, recv, root: int, stream=None) -> None:
         r = _Buf(recv)
         s = _Buf(send, r.dtype)
+        _same_dtype(s, r, "broadcast")
+        _require(r.ptr is not None, "broadcast: every rank needs a recv buffer")
+        if self.rank == root:
+            _require(s.ptr is not None and s.numel == r.numel,
+                     "broadcast: the root's send buffer must hold recv.numel elements")
         ct, st = _ctx([s, r], stream)
         _check(self._lib.megray_broadcast(self._h, s.ptr, r.ptr, r.numel, r.dtype, root, ct, st), "broadcast")
 
     def reduce(self, send, recv, root: int, op="sum", stream=None) -> None:
         s = _Buf(send)
         r = _Buf(recv, s.dtype)
+        _same_dtype(s, r, "reduce")
+        _require(s.ptr is not None, "reduce: every rank needs a send buffer")
+        if self.rank == root:
+            _require(r.ptr is not None and r.numel == s.numel,
+                     "reduce: the root's recv buffer must hold send.numel elements")
         ct, st = _ctx([s, r], stream)
         _check(self._lib.megray_reduce(self._h, s.ptr, r.ptr, s.numel, s.dtype, _op(op), root, ct, st),
                "reduce")
@@ -367,6 +408,7 @@ class Communicator:
     def all_reduce_scaled(self, send, recv, scale: float, op="sum", stream=None) -> None:
         """recv = cast(scale * reduce(send)): input and output dtypes may differ (bf16/fp16/fp32)."""
         s, r = _Buf(send), _Buf(recv)
+        _require(r.numel == s.numel, "all_reduce_scaled: send and recv must hold the same number of elements")
         _, st = _ctx([s, r], stream)
         _check(self._lib.megray_nvl_all_reduce_scaled(self._h, s.ptr, r.ptr, s.numel, s.dtype, r.dtype,
                                                       C.c_float(scale), _op(op), st), "all_reduce_scaled")

@@ -8,9 +8,9 @@ in two forms:
 * fused (``fused=True``): the gather runs as a few CTAs on a side stream and publishes one
   readiness counter per source shard; the GEMM's TMA producer waits for the counter of the
   shard that owns its rows and starts with the local shard, so transfer and math overlap
-  tile by tile.  For GEMM -> reduce_scatter the GEMM epilogue stores each partial tile
-  straight into the owning rank's staging slot over NVLink, and a reduce kernel sums the
-  slots in rank order.
+  tile by tile.  For GEMM -> reduce_scatter the GEMM epilogue stores each partial tile of
+  another rank's rows straight into that rank's staging slot over NVLink; the tiles of the
+  rank's own rows come last and add the staged partials in their epilogue (rank order).
 
 The reference library offers only the bare collectives (all_gather / reduce_scatter,
 include/megray/communicator.h:79-95); composing them with matrix products is left to its user.
@@ -36,14 +36,19 @@ class TensorParallelOps:
         self.fused = fused and self.Ts % 256 == 0
         # SMs the GEMMs may occupy (0 = all); lower it to leave room for kernels of other streams
         self.sm_limit = 0
+        # GEMM tile variant (0 = chosen by the library; 2 = 256-row CTA-pair tile, 3 = 512-row tile)
+        self.variant = 0
         self._lib = _lib.load()
         self._stage = []
         self._parity = 0
         if self.fused:
             # partial-sum staging: n slots of [T/n, d], double-buffered by call parity
+            words = self._lib.megray_tp_rs_counter_bytes(self.Ts, width) // 4
             for _ in range(2):
                 st = comm.sym_empty((tokens, width), torch.bfloat16)
-                st._tp_flags = self._flag_block()
+                # one delivery counter per 32 rows x 256 columns of this rank's shard
+                st._tp_counters = comm.sym_empty((words,), torch.int32)
+                st._tp_counters.zero_()
                 self._stage.append(st)
             self._settle()
 
@@ -94,7 +99,8 @@ class TensorParallelOps:
             self.comm.all_gather(self._shard(xg), xg)
             gemm(xg, w_gu, gu, epilogue=EPI_SWIGLU, out2=h, n=fl, sm_limit=self.sm_limit)
             return
-        args, _, _ = build_gemm_args(xg, w_gu, gu, epilogue=EPI_SWIGLU, out2=h, n=fl, sm_limit=self.sm_limit)
+        args, _, _ = build_gemm_args(xg, w_gu, gu, epilogue=EPI_SWIGLU, out2=h, n=fl, sm_limit=self.sm_limit,
+                                     variant=self.variant)
         self._ag_gemm(self._shard(xg), xg, args)
 
     def ag_gemm_dswiglu(self, dy, dyg, w_down, gu, dgu, fl):
@@ -104,7 +110,7 @@ class TensorParallelOps:
             gemm(dyg, w_down, dgu, b_mn=True, epilogue=EPI_DSWIGLU, aux=gu, n=fl, sm_limit=self.sm_limit)
             return
         args, _, _ = build_gemm_args(dyg, w_down, dgu, b_mn=True, epilogue=EPI_DSWIGLU, aux=gu, n=fl,
-                                     sm_limit=self.sm_limit)
+                                     sm_limit=self.sm_limit, variant=self.variant)
         self._ag_gemm(dy, dyg, args)
 
     # -- GEMM -> reduce_scatter --------------------------------------------------------------
@@ -118,9 +124,10 @@ class TensorParallelOps:
             return
         st = self._stage[self._parity]
         self._parity ^= 1
-        args, _, _ = build_gemm_args(a, b, None, b_mn=b_mn, alloc_out=False, sm_limit=self.sm_limit)
+        args, _, _ = build_gemm_args(a, b, None, b_mn=b_mn, alloc_out=False, sm_limit=self.sm_limit,
+                                     variant=self.variant)
         rc = self._lib.megray_tp_gemm_rs(self.comm._h, C.byref(args), st.data_ptr(), out.data_ptr(),
                                          residual.data_ptr() if residual is not None else None,
-                                         st._tp_flags.data_ptr(), self._stream())
+                                         st._tp_counters.data_ptr(), st._tp_counters.numel() * 4, self._stream())
         if rc != 0:
             raise RuntimeError(f"megray_tp_gemm_rs failed ({rc})")

@@ -9,7 +9,7 @@ import threading
 class ClockSampler:
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_power_cap,temperature.gpu")
 
     def __init__(self, index: int, period_s: float = 0.2):
         self.index, self.period = index, period_s
@@ -50,5 +50,9 @@ class ClockSampler:
         pw = [v for v in (num(r[2]) for r in self.rows) if v is not None]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in self.rows)]
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None,
-                "power_w_max": max(pw) if pw else None, "reasons": reasons, "samples": len(self.rows)}
+        out = {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None,
+               "power_w_max": max(pw) if pw else None, "reasons": reasons, "samples": len(self.rows)}
+        temps = [v for v in (num(r[7]) for r in self.rows if len(r) > 7) if v is not None]
+        if temps:  # die temperature at the first and the last sample, and the highest seen
+            out["temp_c"] = {"first": temps[0], "last": temps[-1], "max": max(temps)}
+        return out

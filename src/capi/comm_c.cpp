@@ -111,6 +111,8 @@ void megray_comm_stats(void* comm, uint64_t* out) {
     out[5] = s.algo_twoshot;
     out[6] = s.algo_nvls;
     out[7] = s.algo_copy;
+    out[8] = s.algo_ll;
+    out[9] = s.algo_direct;
 }
 
 int megray_send(void* comm, const void* buf, size_t len, int dtype, uint32_t peer, int ct, void* st) {

@@ -72,11 +72,15 @@ extern "C" int megray_tp_ag_gemm(void* comm, const megray_gemm_args* a, void* ga
 }
 
 extern "C" int megray_tp_gemm_rs(void* comm, const megray_gemm_args* a, void* staging, void* out,
-                                 const void* residual, void* flags, void* stream) {
+                                 const void* residual, void* counters, size_t counter_bytes, void* stream) {
     if (comm == nullptr || a == nullptr)
         return 6;
     return MegRay::tp_gemm_rs(static_cast<CommBoxView*>(comm)->comm.get(), to_gemm_args(a), staging, out, residual,
-                              flags, static_cast<cudaStream_t>(stream));
+                              counters, counter_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t megray_tp_rs_counter_bytes(int shard_rows, int n_cols) {
+    return MegRay::tp_rs_counter_bytes(shard_rows, n_cols);
 }
 
 extern "C" uint64_t megray_launch_count(void) { return mgk::launch_count(); }

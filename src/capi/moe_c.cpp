@@ -34,10 +34,11 @@ int megray_moe_zero_pads(void* buf, int row_elems, const int* seg_begin, const i
 int megray_moe_dispatch(const void* src, int tokens, int row_elems, const int* idx, const float* w,
                         const int* send_base, int* cursor, const int* pos_in, int* pos_out, void* const* peer_bufs,
                         int nranks, int local_experts, int capacity_rows, void* stream) {
-    if (nranks < 1 || nranks > mgk::moe::kMaxRanks)
+    if (nranks < 1 || nranks > mgk::moe::kMaxRanks || local_experts < 1)
         return 6;
     return rc(mgk::moe::launch_dispatch(src, tokens, row_elems, idx, w, send_base, cursor, pos_in, pos_out,
-                                        bufs(peer_bufs, nranks), local_experts, capacity_rows, S(stream)));
+                                        bufs(peer_bufs, nranks), nranks * local_experts, local_experts,
+                                        capacity_rows, S(stream)));
 }
 int megray_moe_combine(void* out, int tokens, int row_elems, const int* idx, const float* w, const int* pos,
                        void* const* peer_bufs, int nranks, int local_experts, int capacity_rows, void* stream) {

@@ -57,6 +57,10 @@ __device__ __forceinline__ bool cta_barrier(const CommonArgs& c, uint32_t target
 __device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
     return __ldcg(reinterpret_cast<const uint4*>(p));
 }
+// (a peer GPU may have written the byte: read it where its store landed, in L2)
+__device__ __forceinline__ char ld_cg_byte(const char* p) {
+    return static_cast<char>(__ldcg(reinterpret_cast<const unsigned char*>(p)));
+}
 
 // CTA-cooperative byte copy for any alignment.  Vector (16 B) body when source and
 // destination are equally aligned, else 4-byte or 1-byte units.
@@ -70,7 +74,7 @@ __device__ __forceinline__ void cta_copy(char* dst, const char* src, uint64_t nb
         if (head > nbytes)
             head = nbytes;
         for (uint64_t i = tid; i < head; i += nth)
-            dst[i] = src[i];
+            dst[i] = ld_cg_byte(src + i);
         const uint64_t body = (nbytes - head) / 16;
         const uint4* s4 = reinterpret_cast<const uint4*>(src + head);
         uint4* d4 = reinterpret_cast<uint4*>(dst + head);
@@ -98,7 +102,7 @@ __device__ __forceinline__ void cta_copy(char* dst, const char* src, uint64_t nb
             d4[i] = __ldcg(s4 + i);
         const uint64_t done = head + body * 16;
         for (uint64_t k = done + tid; k < nbytes; k += nth)
-            dst[k] = src[k];
+            dst[k] = ld_cg_byte(src + k);
     } else if (((da | sa | nbytes) & 3) == 0) {
         const uint32_t* s = reinterpret_cast<const uint32_t*>(src);
         uint32_t* d = reinterpret_cast<uint32_t*>(dst);
@@ -106,7 +110,7 @@ __device__ __forceinline__ void cta_copy(char* dst, const char* src, uint64_t nb
             d[i] = __ldcg(s + i);
     } else {
         for (uint64_t i = tid; i < nbytes; i += nth)
-            dst[i] = src[i];
+            dst[i] = ld_cg_byte(src + i);
     }
 }
 
@@ -403,6 +407,225 @@ __global__ void __launch_bounds__(512) exchange_family_kernel(const ExchangeArgs
 }
 
 
+// ------------------------------------------------------------------ small messages: flagged words
+__device__ __forceinline__ void st_ll_v4(void* p, uint32_t d0, uint32_t d1, uint32_t flag) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(d0), "r"(flag), "r"(d1), "r"(flag)
+                 : "memory");
+}
+__device__ __forceinline__ uint4 ld_ll_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+
+// 16 bytes of payload starting at p, of which `valid` (1..16) exist; the rest reads as zero.
+__device__ __forceinline__ uint4 load16_any(const char* p, uint32_t valid) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    if (valid == 16 && (a & 15) == 0)
+        return *reinterpret_cast<const uint4*>(p);
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
+    if ((a & 3) == 0 && (valid & 3) == 0) {
+        for (uint32_t i = 0; i < valid / 4; ++i)
+            w[i] = reinterpret_cast<const uint32_t*>(p)[i];
+    } else {
+        for (uint32_t i = 0; i < valid; ++i)
+            w[i >> 2] |= static_cast<uint32_t>(static_cast<unsigned char>(p[i])) << (8 * (i & 3));
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ void store16_any(char* p, const uint4& v, uint32_t valid) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    if (valid == 16 && (a & 15) == 0) {
+        *reinterpret_cast<uint4*>(p) = v;
+        return;
+    }
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    if ((a & 3) == 0 && (valid & 3) == 0) {
+        for (uint32_t i = 0; i < valid / 4; ++i)
+            reinterpret_cast<uint32_t*>(p)[i] = w[i];
+    } else {
+        for (uint32_t i = 0; i < valid; ++i)
+            p[i] = static_cast<char>(w[i >> 2] >> (8 * (i & 3)));
+    }
+}
+
+// Unit u (16 bytes of payload, 32 bytes of flagged words) of a slot, once all its words carry `seq`.
+// Returns false when the wait ran out.
+__device__ __forceinline__ bool ll_wait_unit(const char* slot, uint64_t u, uint32_t seq, const CommonArgs& c,
+                                             uint4* out) {
+    const char* p = slot + u * 32;
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    for (;;) {
+        const uint4 a = ld_ll_v4(p), b = ld_ll_v4(p + 16);
+        if (a.y == seq && a.w == seq && b.y == seq && b.w == seq) {
+            *out = make_uint4(a.x, a.z, b.x, b.z);
+            return true;
+        }
+        if ((++spins & 255) == 0) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0)
+                t0 = now;
+            else if (now - t0 > c.timeout_ns) {
+                if (c.status != nullptr)
+                    atomicCAS(c.status, 0, kStatusTimeout);
+                return false;
+            }
+        }
+    }
+}
+
+template <typename Tin, typename Tout>
+__global__ void __launch_bounds__(512) ll_family_kernel(const LLArgs a) {
+    using A = typename Acc<Tin>::type;
+    constexpr int V = 16 / sizeof(Tin);
+    const CommonArgs& c = a.c;
+    const int n = c.nranks, rank = c.rank;
+    const uint64_t units = (a.bytes + 15) / 16;
+    const uint64_t gtid = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const uint64_t gthreads = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    const char* in = static_cast<const char*>(a.in);
+    char* out = static_cast<char*>(a.out);
+    char* const my_slots = c.peers.heap[rank] + a.slot_off;
+
+    // rooted operations: tell every peer that this rank has started this call
+    if (a.tokens && blockIdx.x == 0 && threadIdx.x < static_cast<unsigned>(n) && static_cast<int>(threadIdx.x) != rank) {
+        uint32_t* tok = reinterpret_cast<uint32_t*>(c.peers.heap[threadIdx.x] + a.token_off) + rank * 2;
+        asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(tok), "r"(a.seq) : "memory");
+    }
+    // send: unit by unit, every destination in turn (starting with rank + 1)
+    if (a.send_mask != 0) {
+        for (uint64_t u = gtid; u < units; u += gthreads) {
+            const uint32_t valid = static_cast<uint32_t>(min(static_cast<uint64_t>(16), a.bytes - u * 16));
+            uint4 v = make_uint4(0, 0, 0, 0);
+            int64_t last_off = -1;
+            for (int jj = 1; jj < n; ++jj) {
+                const int j = (rank + jj) % n;
+                if (!((a.send_mask >> j) & 1u))
+                    continue;
+                if (a.send_off[j] != last_off) {  // (the same payload for every destination is read once)
+                    v = load16_any(in + a.send_off[j] + u * 16, valid);
+                    last_off = a.send_off[j];
+                }
+                char* dst = c.peers.heap[j] + a.slot_off + static_cast<uint64_t>(rank) * kLLSlotBytes + u * 32;
+                st_ll_v4(dst, v.x, v.y, a.seq);
+                st_ll_v4(dst + 16, v.z, v.w, a.seq);
+            }
+        }
+    }
+    // receive
+    bool ok = true;
+    if (!a.reduce) {
+        if (a.self && out != nullptr) {
+            for (uint64_t u = gtid; u < units; u += gthreads) {
+                const uint32_t valid = static_cast<uint32_t>(min(static_cast<uint64_t>(16), a.bytes - u * 16));
+                store16_any(out + a.recv_off[rank] + u * 16, load16_any(in + a.send_off[rank] + u * 16, valid), valid);
+            }
+        }
+        for (int qq = 1; qq < n && ok; ++qq) {
+            const int q = (rank + n - qq) % n;
+            if (!((a.recv_mask >> q) & 1u))
+                continue;
+            const char* slot = my_slots + static_cast<uint64_t>(q) * kLLSlotBytes;
+            for (uint64_t u = gtid; u < units; u += gthreads) {
+                uint4 v;
+                if (!ll_wait_unit(slot, u, a.seq, c, &v)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t valid = static_cast<uint32_t>(min(static_cast<uint64_t>(16), a.bytes - u * 16));
+                store16_any(out + a.recv_off[q] + u * 16, v, valid);
+            }
+        }
+    } else if ((a.recv_mask != 0 || a.self) && out != nullptr) {
+        const bool do_scale = IsFloatAcc<A>::value && a.op == MegRay::MEGRAY_SUM && a.scale != 1.0f;
+        for (uint64_t u = gtid; u < units && ok; u += gthreads) {
+            const uint32_t valid = static_cast<uint32_t>(min(static_cast<uint64_t>(16), a.bytes - u * 16));
+            A acc[V];
+            bool first = true;
+            for (int q = 0; q < n; ++q) {
+                uint4 raw;
+                if (q == rank) {
+                    if (!a.self)
+                        continue;
+                    raw = load16_any(in + a.send_off[rank] + u * 16, valid);
+                } else {
+                    if (!((a.recv_mask >> q) & 1u))
+                        continue;
+                    if (!ll_wait_unit(my_slots + static_cast<uint64_t>(q) * kLLSlotBytes, u, a.seq, c, &raw)) {
+                        ok = false;
+                        break;
+                    }
+                }
+                const Tin* el = reinterpret_cast<const Tin*>(&raw);
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    const A x = widen<Tin>(el[k]);
+                    if (first)
+                        acc[k] = x;
+                    else if (a.op == MegRay::MEGRAY_SUM)
+                        acc[k] = combine<MegRay::MEGRAY_SUM, A>(acc[k], x);
+                    else if (a.op == MegRay::MEGRAY_MAX)
+                        acc[k] = combine<MegRay::MEGRAY_MAX, A>(acc[k], x);
+                    else
+                        acc[k] = combine<MegRay::MEGRAY_MIN, A>(acc[k], x);
+                }
+                first = false;
+            }
+            if (!ok || first)
+                break;
+            Tout o[V];
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                if (do_scale)
+                    acc[k] = static_cast<A>(acc[k] * static_cast<A>(a.scale));
+                o[k] = narrow<Tout, A>(acc[k]);
+            }
+            const uint32_t nel = valid / sizeof(Tin);
+            Tout* dst = reinterpret_cast<Tout*>(out) + u * V;
+            constexpr int OB = V * sizeof(Tout);
+            if (nel == V && (reinterpret_cast<uintptr_t>(dst) & (OB >= 16 ? 15 : 7)) == 0) {
+                if (OB >= 16) {
+#pragma unroll
+                    for (int w = 0; w < OB / 16; ++w)
+                        reinterpret_cast<uint4*>(dst)[w] = reinterpret_cast<const uint4*>(o)[w];
+                } else {
+                    *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
+                }
+            } else {
+                for (uint32_t k = 0; k < nel; ++k)
+                    dst[k] = o[k];
+            }
+        }
+    }
+    // rooted operations: every peer has started this call, so it has finished the previous one on
+    // these slots' other parity, which the next call will overwrite
+    if (a.tokens && blockIdx.x == 0 && threadIdx.x < static_cast<unsigned>(n) && static_cast<int>(threadIdx.x) != rank) {
+        const uint32_t* tok = reinterpret_cast<const uint32_t*>(c.peers.heap[rank] + a.token_off) + threadIdx.x * 2;
+        uint32_t spins = 0;
+        uint64_t t0 = 0;
+        for (;;) {
+            uint32_t v;
+            asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(tok) : "memory");
+            if (v == a.seq)
+                break;
+            if ((++spins & 255) == 0) {
+                const uint64_t now = globaltimer_ns();
+                if (t0 == 0)
+                    t0 = now;
+                else if (now - t0 > c.timeout_ns) {
+                    if (c.status != nullptr)
+                        atomicCAS(c.status, 0, kStatusTimeout);
+                    break;
+                }
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------ direct family
 // multimem (NVLS) loads: the switch combines the 16 bytes at the same heap offset of all ranks.
 template <typename T, int OP>
@@ -441,34 +664,122 @@ __device__ __forceinline__ void mc_st_v2(void* p, const uint2& v) {
     asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
 
-// Reduce elements [b, e) of slice `rank`: load from all inputs, combine in rank order, scale,
-// cast; store into every rank's output (all_reduce) or into `out_local` (reduce_scatter).
+// The buffers of one call as every rank addresses them here, and what the kernel found out
+// about them (shared memory, filled once per CTA after the first barrier).
+struct CallBufs {
+    const char* in[kMaxRanks];
+    char* out[kMaxRanks];
+    uint64_t in_off, out_off;  // heap offsets when in_sym / out_sym
+    int in_sym, out_sym;       // every rank's buffer lies in its heap at one and the same offset
+    int in_vec, out_vec;       // every rank's buffer is 16-byte aligned
+};
+
+__device__ __forceinline__ uint64_t ld_cg_u64(const uint64_t* p) { return __ldcg(reinterpret_cast<const unsigned long long*>(p)); }
+
+// The first barrier of a single-pass kernel.  With `exchange` it also carries this call's buffer
+// addresses: thread q stores this rank's pair into slot [parity][rank] of rank q's pad before the
+// releasing flag store, and reads rank q's pair from its own pad after the acquiring flag load.
+// (Every CTA stores the same pair; any CTA's flag orders its own copy.)
+__device__ __forceinline__ bool first_barrier(const DirectArgs& a, uint32_t target, CallBufs* cb) {
+    const CommonArgs& c = a.c;
+    const int n = c.nranks;
+    __syncthreads();
+    int ok = 1;
+    if (threadIdx.x < static_cast<unsigned>(n)) {
+        const int q = threadIdx.x;
+        if (a.exchange) {
+            uint64_t* theirs = reinterpret_cast<uint64_t*>(c.peers.heap[q] + kExchangeOff) +
+                               (a.parity * kMaxRanks + c.rank) * 2;
+            theirs[0] = reinterpret_cast<uint64_t>(a.in_local);
+            theirs[1] = reinterpret_cast<uint64_t>(a.out_local);
+        }
+        uint32_t* at_peer = reinterpret_cast<uint32_t*>(c.peers.heap[q] + c.flag_off) + blockIdx.x * kMaxRanks + c.rank;
+        st_release_sys(at_peer, target);
+        const uint32_t* mine = reinterpret_cast<const uint32_t*>(c.peers.heap[c.rank] + c.flag_off) +
+                               blockIdx.x * kMaxRanks + q;
+        uint32_t spins = 0;
+        uint64_t t0 = 0;
+        while (static_cast<int32_t>(ld_acquire_sys(mine) - target) < 0) {
+            if ((++spins & 63) == 0) {
+                const uint64_t now = globaltimer_ns();
+                if (t0 == 0)
+                    t0 = now;
+                else if (now - t0 > c.timeout_ns) {
+                    ok = 0;
+                    if (c.status != nullptr)
+                        atomicCAS(c.status, 0, kStatusTimeout);
+                    break;
+                }
+            }
+        }
+        if (a.exchange) {
+            const uint64_t* got = reinterpret_cast<const uint64_t*>(c.peers.heap[c.rank] + kExchangeOff) +
+                                  (a.parity * kMaxRanks + q) * 2;
+            cb->in[q] = ok ? reinterpret_cast<const char*>(ld_cg_u64(got)) : nullptr;
+            cb->out[q] = ok ? reinterpret_cast<char*>(ld_cg_u64(got + 1)) : nullptr;
+        } else {
+            cb->in[q] = a.in_base[q];
+            cb->out[q] = a.out_base[q];
+            if (q == c.rank) {  // buffers that only this rank touches need not be peer-addressable
+                if (a.in_local != nullptr)
+                    cb->in[q] = static_cast<const char*>(a.in_local);
+                if (a.out_local != nullptr)
+                    cb->out[q] = static_cast<char*>(a.out_local);
+            }
+        }
+    }
+    if (__syncthreads_and(ok) == 0)
+        return false;
+    if (threadIdx.x == 0) {
+        uint64_t in_or = 0, out_or = 0;
+        int in_sym = 1, out_sym = 1;
+        const uint64_t in_off0 = static_cast<uint64_t>(cb->in[0] - c.peers.heap[0]);
+        const uint64_t out_off0 = static_cast<uint64_t>(cb->out[0] - c.peers.heap[0]);
+        for (int q = 0; q < n; ++q) {
+            in_or |= reinterpret_cast<uint64_t>(cb->in[q]);
+            out_or |= reinterpret_cast<uint64_t>(cb->out[q]);
+            if (static_cast<uint64_t>(cb->in[q] - c.peers.heap[q]) != in_off0)
+                in_sym = 0;
+            if (static_cast<uint64_t>(cb->out[q] - c.peers.heap[q]) != out_off0)
+                out_sym = 0;
+        }
+        cb->in_off = in_off0;
+        cb->out_off = out_off0;
+        cb->in_sym = in_sym && in_off0 < a.heap_bytes;
+        cb->out_sym = out_sym && out_off0 < a.heap_bytes;
+        cb->in_vec = (in_or & 15) == 0;
+        cb->out_vec = (out_or & 15) == 0;
+    }
+    __syncthreads();
+    return true;
+}
+
+// Reduce `nelem` elements: element i of the range is element i of in[q] + in_byte0 for every rank
+// q; they are combined in rank order, scaled and cast.  The result goes to `single` + i (one
+// destination) or, when `single` is null, to out[q] + out_byte0 + i of every rank.  `vec`: every
+// address involved is 16-byte aligned, so the 16-byte path applies; otherwise element by element.
 template <typename Tin, typename Tout, int OP, bool NVLS>
-__device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, uint64_t elem0, uint64_t b, uint64_t e) {
+__device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, const CallBufs& cb, uint64_t in_byte0,
+                                                    uint64_t out_byte0, uint64_t nelem, char* single, bool vec,
+                                                    bool mc_in, bool mc_out) {
     using A = typename Acc<Tin>::type;
     constexpr int V = 16 / sizeof(Tin);
     constexpr int OB = V * sizeof(Tout);
     const int n = a.c.nranks;
     const bool do_scale = IsFloatAcc<A>::value && OP == MegRay::MEGRAY_SUM && a.scale != 1.0f;
-    const bool to_all = a.kind == DIRECT_ALL_REDUCE;
-    const uint64_t nvec = (e - b) / V;
-    // byte positions relative to the start of every rank's input / output buffer
-    const uint64_t in_byte0 = (elem0 + b) * sizeof(Tin);
-    // all_reduce writes the slice back at the same element positions; reduce_scatter writes the
-    // slice to the start of the local result
-    const uint64_t out_byte0 = to_all ? (elem0 + b) * sizeof(Tout) : b * sizeof(Tout);
+    const uint64_t nvec = vec ? nelem / V : 0;
     // U independent vectors per thread and iteration: all their loads are issued before the
     // first use, which is what keeps enough bytes in flight to fill the links
     constexpr int U = NVLS ? 4 : 2;
     for (uint64_t i0 = threadIdx.x; i0 < nvec; i0 += static_cast<uint64_t>(U) * blockDim.x) {
         A acc[U][V];
-        if (NVLS) {
+        if (NVLS && mc_in) {
             uint4 raw[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const uint64_t i = i0 + static_cast<uint64_t>(u) * blockDim.x;
                 if (i < nvec)
-                    raw[u] = mc_ld_reduce<Tin, OP>(a.mc_base + a.in_off + in_byte0 + i * 16);
+                    raw[u] = mc_ld_reduce<Tin, OP>(a.mc_base + cb.in_off + in_byte0 + i * 16);
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -485,7 +796,7 @@ __device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, uint64_
 #pragma unroll
                 for (int q = 0; q < kMaxRanks; ++q)
                     if (q < n && i < nvec)
-                        raw[u][q] = ld_cg_v4(a.in_base[q] + in_byte0 + i * 16);
+                        raw[u][q] = ld_cg_v4(cb.in[q] + in_byte0 + i * 16);
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -512,8 +823,8 @@ __device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, uint64_
                     acc[u][k] = static_cast<A>(acc[u][k] * static_cast<A>(a.scale));
                 o[k] = narrow<Tout, A>(acc[u][k]);
             }
-            if (!to_all) {
-                char* dst = static_cast<char*>(a.out_local) + out_byte0 + i * OB;
+            if (single != nullptr) {
+                char* dst = single + i * OB;
                 if (OB >= 16) {
 #pragma unroll
                     for (int w = 0; w < OB / 16; ++w)
@@ -521,8 +832,8 @@ __device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, uint64_
                 } else {
                     *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
                 }
-            } else if (NVLS) {
-                char* dst = a.mc_base + a.out_off + out_byte0 + i * OB;
+            } else if (NVLS && mc_out) {
+                char* dst = a.mc_base + cb.out_off + out_byte0 + i * OB;
                 if (OB >= 16) {
 #pragma unroll
                     for (int w = 0; w < OB / 16; ++w)
@@ -534,7 +845,7 @@ __device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, uint64_
 #pragma unroll
                 for (int q = 0; q < kMaxRanks; ++q) {
                     if (q < n) {
-                        char* dst = a.out_base[(a.c.rank + q) % n] + out_byte0 + i * OB;
+                        char* dst = cb.out[(a.c.rank + q) % n] + out_byte0 + i * OB;
                         if (OB >= 16) {
 #pragma unroll
                             for (int w = 0; w < OB / 16; ++w)
@@ -547,85 +858,286 @@ __device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, uint64_
             }
         }
     }
-    // element tail (fewer than V elements): plain peer accesses
-    for (uint64_t i = b + nvec * V + threadIdx.x; i < e; i += blockDim.x) {
-        A acc = widen<Tin>(reinterpret_cast<const Tin*>(a.in_base[0])[elem0 + i]);
+    // what the 16-byte path left (fewer than V elements, or everything when something is
+    // unaligned): plain element accesses
+    for (uint64_t i = nvec * V + threadIdx.x; i < nelem; i += blockDim.x) {
+        A acc = widen<Tin>(__ldcg(reinterpret_cast<const Tin*>(cb.in[0] + in_byte0) + i));
         for (int q = 1; q < n; ++q)
-            acc = combine<OP, A>(acc, widen<Tin>(reinterpret_cast<const Tin*>(a.in_base[q])[elem0 + i]));
+            acc = combine<OP, A>(acc, widen<Tin>(__ldcg(reinterpret_cast<const Tin*>(cb.in[q] + in_byte0) + i)));
         if (do_scale)
             acc = static_cast<A>(acc * static_cast<A>(a.scale));
         const Tout o = narrow<Tout, A>(acc);
-        if (!to_all) {
-            static_cast<Tout*>(a.out_local)[i] = o;
+        if (single != nullptr) {
+            reinterpret_cast<Tout*>(single)[i] = o;
         } else {
             for (int q = 0; q < n; ++q)
-                reinterpret_cast<Tout*>(a.out_base[q])[elem0 + i] = o;
+                reinterpret_cast<Tout*>(cb.out[q] + out_byte0)[i] = o;
+        }
+    }
+}
+
+// Copy [0, nbytes) of `src` to the same range of up to n destinations, reading the source once:
+// every 16-byte vector goes to all destinations before the next one is touched, so all links
+// carry traffic at every moment (dst[j] == nullptr is skipped).
+__device__ __forceinline__ void cta_fanout(char* const* dst, int ndst, const char* src, uint64_t nbytes,
+                                           bool vec) {
+    if (nbytes == 0)
+        return;
+    if (!vec || (nbytes & 15)) {
+        for (int j = 0; j < ndst; ++j)
+            if (dst[j] != nullptr)
+                cta_copy(dst[j], src, nbytes);
+        return;
+    }
+    const uint64_t nv = nbytes / 16;
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    constexpr int U = 4;
+    for (uint64_t i0 = threadIdx.x; i0 < nv; i0 += static_cast<uint64_t>(U) * blockDim.x) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint64_t i = i0 + static_cast<uint64_t>(u) * blockDim.x;
+            if (i < nv)
+                v[u] = __ldcg(s4 + i);
+        }
+#pragma unroll
+        for (int j = 0; j < kMaxRanks; ++j) {
+            if (j < ndst && dst[j] != nullptr) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const uint64_t i = i0 + static_cast<uint64_t>(u) * blockDim.x;
+                    if (i < nv)
+                        reinterpret_cast<uint4*>(dst[j])[i] = v[u];
+                }
+            }
+        }
+    }
+}
+
+// Copy [0, nbytes) of src[j] to dst[j] for up to n pairs, one vector of every pair in flight at
+// a time (all_to_all, scatter: a different source chunk for every destination).
+__device__ __forceinline__ void cta_pairs(char* const* dst, const char* const* src, int npairs, uint64_t nbytes,
+                                          bool vec) {
+    if (nbytes == 0)
+        return;
+    if (!vec || (nbytes & 15)) {
+        for (int j = 0; j < npairs; ++j)
+            if (dst[j] != nullptr)
+                cta_copy(dst[j], src[j], nbytes);
+        return;
+    }
+    const uint64_t nv = nbytes / 16;
+    constexpr int U = 2;
+    for (uint64_t i0 = threadIdx.x; i0 < nv; i0 += static_cast<uint64_t>(U) * blockDim.x) {
+        uint4 v[U][kMaxRanks];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint64_t i = i0 + static_cast<uint64_t>(u) * blockDim.x;
+#pragma unroll
+            for (int j = 0; j < kMaxRanks; ++j)
+                if (j < npairs && dst[j] != nullptr && i < nv)
+                    v[u][j] = __ldcg(reinterpret_cast<const uint4*>(src[j]) + i);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint64_t i = i0 + static_cast<uint64_t>(u) * blockDim.x;
+#pragma unroll
+            for (int j = 0; j < kMaxRanks; ++j)
+                if (j < npairs && dst[j] != nullptr && i < nv)
+                    reinterpret_cast<uint4*>(dst[j])[i] = v[u][j];
         }
     }
 }
 
 template <typename Tin, typename Tout, bool NVLS>
 __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) {
+    __shared__ CallBufs cb;
+    __shared__ int s_ok;
     const CommonArgs& c = a.c;
     const int n = c.nranks, rank = c.rank;
     constexpr uint64_t V = 16 / sizeof(Tin);
     uint32_t epoch = c.epoch;
     // inputs are final / outputs may be overwritten on every rank
-    if (!cta_barrier(c, ++epoch))
+    if (!first_barrier(a, ++epoch, &cb))
         return;
-    if (a.kind == DIRECT_ALL_GATHER) {
-        // this rank's block into slot `rank` of every output
+    const char* const my_in = cb.in[rank];
+    char* const my_out = cb.out[rank];
+    if (a.kind == DIRECT_ALL_GATHER || a.kind == DIRECT_GATHER) {
+        // this rank's block into slot `rank` of every output (all_gather) or of the root's (gather)
         const uint64_t bytes = a.len * sizeof(Tin);
         const uint64_t per_cta = round_up_u64((bytes + gridDim.x - 1) / gridDim.x, 16);
         const uint64_t b = min(bytes, per_cta * blockIdx.x), e = min(bytes, b + per_cta);
-        const char* src = static_cast<const char*>(a.in_local);
-        if (NVLS && ((reinterpret_cast<uintptr_t>(src) | (a.out_off + rank * bytes)) & 15) == 0) {  // (heap-resident output)
-            char* dst = a.mc_base + a.out_off + rank * bytes;
+        const bool vec = cb.out_vec && ((reinterpret_cast<uint64_t>(my_in) | bytes) & 15) == 0;
+        if (a.kind == DIRECT_GATHER) {
+            cta_copy(cb.out[a.root] + rank * bytes + b, my_in + b, e - b);
+        } else if (NVLS && cb.out_sym && vec) {
+            char* dst = a.mc_base + cb.out_off + rank * bytes;
             const uint64_t nv = (e - b) / 16;
             for (uint64_t i = threadIdx.x; i < nv; i += blockDim.x)
-                mc_st_v4(dst + b + i * 16, ld_cg_v4(src + b + i * 16));
-            for (uint64_t k = b + nv * 16 + threadIdx.x; k < e; k += blockDim.x)
-                for (int q = 0; q < n; ++q)
-                    (a.out_base[q] + rank * bytes)[k] = src[k];
+                mc_st_v4(dst + b + i * 16, ld_cg_v4(my_in + b + i * 16));
         } else {
-            for (int qq = 0; qq < n; ++qq) {
-                const int q = (rank + qq) % n;
-                cta_copy(a.out_base[q] + rank * bytes + b, src + b, e - b);
-            }
+            char* dst[kMaxRanks];
+#pragma unroll
+            for (int j = 0; j < kMaxRanks; ++j)
+                dst[j] = j < n ? cb.out[(rank + 1 + j) % n] + rank * bytes + b : nullptr;
+            cta_fanout(dst, n, my_in + b, e - b, vec);
         }
-    } else if (a.kind == DIRECT_ALL_TO_ALL) {
-        // chunk q of the input into slot `rank` of rank q's output, starting with rank+1
+    } else if (a.kind == DIRECT_ALL_TO_ALL || a.kind == DIRECT_SCATTER) {
+        // chunk q of the input into slot `rank` of rank q's output (all_to_all) or into rank q's
+        // output (scatter, root only), starting with rank + 1
         const uint64_t bytes = a.len * sizeof(Tin);
         const uint64_t per_cta = round_up_u64((bytes + gridDim.x - 1) / gridDim.x, 16);
         const uint64_t b = min(bytes, per_cta * blockIdx.x), e = min(bytes, b + per_cta);
-        const char* src = static_cast<const char*>(a.in_local);
-        for (int qq = 1; qq <= n; ++qq) {
-            const int q = (rank + qq) % n;
-            cta_copy(a.out_base[q] + rank * bytes + b, src + q * bytes + b, e - b);
+        if (a.kind == DIRECT_ALL_TO_ALL || rank == a.root) {
+            const uint64_t slot = a.kind == DIRECT_ALL_TO_ALL ? rank * bytes : 0;
+            const bool vec = cb.out_vec && ((reinterpret_cast<uint64_t>(my_in) | bytes) & 15) == 0;
+            char* dst[kMaxRanks];
+            const char* src[kMaxRanks];
+#pragma unroll
+            for (int j = 0; j < kMaxRanks; ++j) {
+                const int q = (rank + 1 + j) % n;
+                dst[j] = j < n ? cb.out[q] + slot + b : nullptr;
+                src[j] = j < n ? my_in + q * bytes + b : nullptr;
+            }
+            cta_pairs(dst, src, n, e - b, vec);
+        }
+    } else if (a.kind == DIRECT_BROADCAST) {
+        const uint64_t S = a.len * sizeof(Tin);
+        const int root = a.root;
+        if (n <= 2) {
+            // nobody to forward to: the root stores its share to the other rank (and to itself)
+            const uint64_t per_cta = round_up_u64((S + gridDim.x - 1) / gridDim.x, 16);
+            const uint64_t b = min(S, per_cta * blockIdx.x), e = min(S, b + per_cta);
+            if (rank == root) {
+                if (n == 2)
+                    cta_copy(cb.out[1 - rank] + b, my_in + b, e - b);
+                if (my_out != my_in)
+                    cta_copy(my_out + b, my_in + b, e - b);
+            }
+        } else {
+            const BcastPlan pl = bcast_plan(S, n, gridDim.x, a.chunk_bytes);
+            const uint64_t sb = pl.per_cta * blockIdx.x;  // this CTA's share of every slice
+            // bytes [lo, hi) of slice v that chunk k of this CTA covers (relative to the slice)
+            auto chunk_range = [&](int v, uint32_t k, uint64_t* lo, uint64_t* hi) {
+                const uint64_t s0 = static_cast<uint64_t>(v) * pl.slice;
+                const uint64_t L = s0 >= S ? 0 : min(pl.slice, S - s0);
+                *lo = min(L, sb + static_cast<uint64_t>(k) * a.chunk_bytes);
+                *hi = min(L, min(sb + pl.per_cta, sb + static_cast<uint64_t>(k + 1) * a.chunk_bytes));
+            };
+            if (rank == root) {
+                for (uint32_t k = 0; k < pl.chunks; ++k) {
+                    for (int v = 0; v < n - 1; ++v) {
+                        const int j = (root + 1 + v) % n;
+                        uint64_t lo, hi;
+                        chunk_range(v, k, &lo, &hi);
+                        if (hi > lo)
+                            cta_copy(cb.out[j] + v * pl.slice + lo, my_in + v * pl.slice + lo, hi - lo);
+                    }
+                    __syncthreads();
+                    if (threadIdx.x < static_cast<unsigned>(n - 1)) {
+                        const int j = (root + 1 + threadIdx.x) % n;
+                        __threadfence_system();
+                        st_release_sys(reinterpret_cast<uint32_t*>(c.peers.heap[j] + kChunkFlagOff) + blockIdx.x,
+                                       a.chunk_base + k + 1);
+                    }
+                }
+                if (my_out != my_in) {
+                    for (int v = 0; v < n - 1; ++v) {
+                        const uint64_t s0 = static_cast<uint64_t>(v) * pl.slice;
+                        const uint64_t L = s0 >= S ? 0 : min(pl.slice, S - s0);
+                        const uint64_t lo = min(L, sb), hi = min(L, sb + pl.per_cta);
+                        if (hi > lo)
+                            cta_copy(my_out + s0 + lo, my_in + s0 + lo, hi - lo);
+                    }
+                }
+            } else {
+                const int v = (rank - root - 1 + n) % n;  // the slice this rank forwards
+                const uint32_t* my_flag =
+                        reinterpret_cast<const uint32_t*>(c.peers.heap[rank] + kChunkFlagOff) + blockIdx.x;
+                for (uint32_t k = 0; k < pl.chunks; ++k) {
+                    if (threadIdx.x == 0) {
+                        const uint32_t target = a.chunk_base + k + 1;
+                        int ok = 1;
+                        uint32_t spins = 0;
+                        uint64_t t0 = 0;
+                        while (static_cast<int32_t>(ld_acquire_sys(my_flag) - target) < 0) {
+                            if ((++spins & 63) == 0) {
+                                const uint64_t now = globaltimer_ns();
+                                if (t0 == 0)
+                                    t0 = now;
+                                else if (now - t0 > c.timeout_ns) {
+                                    ok = 0;
+                                    if (c.status != nullptr)
+                                        atomicCAS(c.status, 0, kStatusTimeout);
+                                    break;
+                                }
+                            }
+                        }
+                        s_ok = ok;
+                    }
+                    __syncthreads();
+                    if (!s_ok)
+                        return;
+                    uint64_t lo, hi;
+                    chunk_range(v, k, &lo, &hi);
+                    if (hi > lo && n > 2) {
+                        char* dst[kMaxRanks];
+                        const char* src = my_out + v * pl.slice + lo;
+                        bool vec = (reinterpret_cast<uint64_t>(src) & 15) == 0;
+#pragma unroll
+                        for (int j = 0; j < kMaxRanks; ++j) {
+                            const int m = (rank + 1 + j) % n;
+                            dst[j] = (j < n - 1 && m != root) ? cb.out[m] + v * pl.slice + lo : nullptr;
+                            if (dst[j] != nullptr && (reinterpret_cast<uint64_t>(dst[j]) & 15))
+                                vec = false;
+                        }
+                        cta_fanout(dst, n - 1, src, hi - lo, vec);
+                    }
+                    __syncthreads();  // s_ok is rewritten in the next round
+                }
+            }
         }
     } else {
-        // slice `rank`: all_reduce splits len into n slices of se elements, reduce_scatter's
-        // slice is the rank-th block of len elements
+        // all_reduce / reduce: len is cut into n slices of se elements and this rank reduces
+        // slice `rank`; reduce_scatter: its slice is the rank-th block of len elements
         uint64_t se, elem0, L;
-        if (a.kind == DIRECT_ALL_REDUCE) {
+        if (a.kind == DIRECT_REDUCE_SCATTER) {
+            elem0 = a.len * rank;
+            L = a.len;
+        } else {
             se = round_up_u64((a.len + n - 1) / n, V);
             elem0 = min(a.len, se * rank);
             L = min(a.len, elem0 + se) - elem0;
-        } else {
-            elem0 = a.len * rank;
-            L = a.len;
         }
         const uint64_t per_cta = round_up_u64((L + gridDim.x - 1) / gridDim.x, V);
         const uint64_t b = min(L, per_cta * blockIdx.x), e = min(L, b + per_cta);
+        const uint64_t in_byte0 = (elem0 + b) * sizeof(Tin);
+        uint64_t out_byte0 = (elem0 + b) * sizeof(Tout);
+        char* single = nullptr;
+        bool vec = cb.in_vec && (in_byte0 & 15) == 0;
+        if (a.kind == DIRECT_REDUCE_SCATTER) {
+            single = my_out + b * sizeof(Tout);
+            vec = vec && (reinterpret_cast<uint64_t>(single) & 15) == 0;
+        } else if (a.kind == DIRECT_REDUCE) {
+            single = cb.out[a.root] + out_byte0;
+            vec = vec && (reinterpret_cast<uint64_t>(single) & 15) == 0;
+        } else {
+            vec = vec && cb.out_vec && (out_byte0 & 15) == 0;
+        }
+        const bool mc_in = NVLS && cb.in_sym && vec;
+        const bool mc_out = NVLS && cb.out_sym && vec && single == nullptr;
         switch (a.op) {
             case MegRay::MEGRAY_SUM:
-                direct_reduce_range<Tin, Tout, MegRay::MEGRAY_SUM, NVLS>(a, elem0, b, e);
+                direct_reduce_range<Tin, Tout, MegRay::MEGRAY_SUM, NVLS>(a, cb, in_byte0, out_byte0, e - b, single, vec,
+                                                                         mc_in, mc_out);
                 break;
             case MegRay::MEGRAY_MAX:
-                direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MAX, NVLS>(a, elem0, b, e);
+                direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MAX, NVLS>(a, cb, in_byte0, out_byte0, e - b, single, vec,
+                                                                         mc_in, mc_out);
                 break;
             default:
-                direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MIN, NVLS>(a, elem0, b, e);
+                direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MIN, NVLS>(a, cb, in_byte0, out_byte0, e - b, single, vec,
+                                                                         mc_in, mc_out);
         }
     }
     // all transfers are complete before any rank uses its output or overwrites its input
@@ -786,6 +1298,17 @@ struct DirectLauncher {
         return cudaGetLastError();
     }
 };
+struct LLLauncher {
+    const LLArgs& a;
+    int ctas, threads;
+    cudaStream_t s;
+    template <typename Tin, typename Tout>
+    cudaError_t operator()() const {
+        ll_family_kernel<Tin, Tout><<<ctas, threads, 0, s>>>(a);
+        count_launch();
+        return cudaGetLastError();
+    }
+};
 struct ReduceNLauncher {
     const ReduceNArgs& a;
     cudaStream_t s;
@@ -819,10 +1342,22 @@ cudaError_t launch_direct(const DirectArgs& a, int ctas, int threads, cudaStream
     if (ctas < 1 || ctas > kMaxCtas || threads < 32 || threads > 512 || a.c.nranks < 1 ||
         a.c.nranks > kMaxRanks)
         return cudaErrorInvalidValue;
-    if (a.mc_base != nullptr && (a.kind == DIRECT_ALL_REDUCE || a.kind == DIRECT_REDUCE_SCATTER) &&
+    if (a.mc_base != nullptr &&
+        (a.kind == DIRECT_ALL_REDUCE || a.kind == DIRECT_REDUCE_SCATTER || a.kind == DIRECT_REDUCE) &&
         !nvls_supports(a.in_dtype, a.out_dtype, a.op))
         return cudaErrorInvalidValue;
+    if (a.kind == DIRECT_BROADCAST && (a.chunk_bytes < 16 || (a.chunk_bytes & 15)))
+        return cudaErrorInvalidValue;
     return dispatch_types(a.in_dtype, a.out_dtype, DirectLauncher{a, ctas, threads, stream});
+}
+
+cudaError_t launch_ll(const LLArgs& a, int ctas, int threads, cudaStream_t stream) {
+    if (ctas < 1 || ctas > kMaxCtas || threads < 32 || threads > 512 || a.c.nranks < 1 || a.c.nranks > kMaxRanks ||
+        a.bytes > kLLMaxBytes || a.seq == 0)
+        return cudaErrorInvalidValue;
+    if (!a.reduce)  // pure data movement: the element type does not matter
+        return LLLauncher{a, ctas, threads, stream}.template operator()<uint8_t, uint8_t>();
+    return dispatch_types(a.in_dtype, a.out_dtype, LLLauncher{a, ctas, threads, stream});
 }
 
 cudaError_t launch_exchange(const ExchangeArgs& a, int ctas, int threads, cudaStream_t stream) {

@@ -44,6 +44,17 @@ constexpr int kMaxRanks = 8;
 constexpr int kMaxCtas = 128;        // flag rows in a signal pad
 constexpr int kPadBytes = 64 * 1024; // signal pad at the start of every rank's heap
 
+// Layout of the first 16 KiB of the pad (byte offsets from the start of a rank's heap):
+constexpr uint64_t kBarrierFlagOff = 0;      // [kMaxCtas][kMaxRanks] u32: per-CTA barrier epochs
+constexpr uint64_t kChunkFlagOff = 4096;     // [kMaxCtas] u32: chunk counters of the pipelined broadcast
+constexpr uint64_t kExchangeOff = 8192;      // [2][kMaxRanks] x 16 bytes: the buffers of the current call
+constexpr uint64_t kTokenOff = 8192 + 512;   // [2][kMaxRanks] x 8 bytes: tokens of the small-message kernel
+// Small-message (flagged word) slots follow the pad: [2 parities][kMaxRanks sources] slots, each
+// holding kLLMaxBytes of payload as 8-byte {data, flag} words.
+constexpr uint64_t kLLMaxBytes = 1024 * 1024;
+constexpr uint64_t kLLSlotBytes = 2 * kLLMaxBytes;
+constexpr uint64_t kLLRegionBytes = 2 * kMaxRanks * kLLSlotBytes;  // 32 MiB
+
 struct PeerTable {
     // peer q's heap base address as mapped in this rank's address space
     char* heap[kMaxRanks];
@@ -109,11 +120,31 @@ struct ExchangeArgs {
 //   reduce_scatter  barrier; load slice r of all inputs, combine, store locally; barrier.
 //   all_gather      barrier; store this rank's block into slot r of all n outputs; barrier.
 //   all_to_all      barrier; store chunk q of this rank's input into slot r of rank q's output; barrier.
+//   broadcast       barrier; the message is cut into n-1 slices, one per non-root rank: the root
+//                   stores slice j into rank j's output chunk by chunk and bumps a chunk counter
+//                   there; rank j forwards each chunk of its slice, as it lands, to the outputs of
+//                   the other non-root ranks.  The root sends the message once, every other rank
+//                   receives it once and forwards 1/(n-1) of it: all links are busy at once.
+//   reduce          barrier; rank r loads slice r of all inputs, combines, stores into the root's
+//                   output; barrier.
+//   gather          barrier; store this rank's block into slot r of the root's output; barrier.
+//   scatter         barrier; the root stores chunk q of its input into rank q's output; barrier.
+//
+// Whose buffers?  Ranks that are threads of one process (the way the reference's tests and its
+// benchmark drive their ranks) can address each other's cudaMalloc memory once peer access is
+// on, so with `exchange` set every rank publishes the addresses of this call's buffers in the
+// peers' pads as part of the first barrier and reads the peers' addresses from its own pad: plain
+// unregistered user buffers then take these kernels.  Without `exchange` the host fills
+// in_base / out_base (symmetric-heap or registered buffers).
 enum DirectKind : int {
     DIRECT_ALL_REDUCE = 0,
     DIRECT_REDUCE_SCATTER = 1,
     DIRECT_ALL_GATHER = 2,
-    DIRECT_ALL_TO_ALL = 3
+    DIRECT_ALL_TO_ALL = 3,
+    DIRECT_BROADCAST = 4,
+    DIRECT_REDUCE = 5,
+    DIRECT_GATHER = 6,
+    DIRECT_SCATTER = 7
 };
 
 struct DirectArgs {
@@ -124,17 +155,73 @@ struct DirectArgs {
     // of buffers registered with the communicator
     const char* in_base[kMaxRanks];
     char* out_base[kMaxRanks];
-    uint64_t in_off;       // heap offset of the input: the multimem address is mc_base + in_off
-    uint64_t out_off;      // heap offset of the output
-    const void* in_local;  // all_gather / all_to_all: this rank's input (any device memory)
-    void* out_local;       // reduce_scatter: this rank's result (any device memory)
-    uint64_t len;          // all_reduce: total elements; others: elements per rank
+    const void* in_local;  // this rank's input when only this rank reads it (any device memory), or,
+                           // with `exchange`, the input this rank publishes
+    void* out_local;       // likewise for the output
+    uint64_t len;          // all_reduce / broadcast / reduce: total elements; others: elements per rank
     float scale;
     MegRay::DType in_dtype;
     MegRay::DType out_dtype;
     MegRay::ReduceOp op;
     char* mc_base;         // non-null: multicast (NVLS) mapping of the heap, use multimem
+    int exchange;          // 1: in_local / out_local are published to the peers and theirs are read
+    int parity;            // exchange: which of the two address slots this launch uses (alternates)
+    int root;              // broadcast, reduce, gather, scatter
+    uint64_t heap_bytes;   // size of every rank's heap (NVLS needs both buffers inside it, same offset)
+    uint32_t chunk_base;   // broadcast: chunk k is announced as chunk_base + k + 1
+    uint32_t chunk_bytes;  // broadcast: bytes of one chunk of a CTA's share of a slice (multiple of 16)
 };
+
+// Small messages: flagged words ("LL").  A sender stores every 4 bytes of payload together with
+// the call's sequence number as one 8-byte word into the receiver's slot; the receiver polls the
+// words themselves until they carry the sequence number.  No barrier and no memory fence stands
+// between the data and its arrival, so a call costs one kernel launch plus one NVLink store
+// latency.  Slots alternate between two parities; a slot is reused two calls later, when its
+// reader has finished (every rank hears from every other rank in every call: through the payload
+// itself, or, for rooted operations, through a token word).
+struct LLArgs {
+    CommonArgs c;
+    uint32_t seq;                    // this call's flag value (never 0)
+    uint64_t slot_off;               // heap offset of this parity's slots; slot of source q at + q * kLLSlotBytes
+    uint64_t token_off;              // heap offset of this parity's token words [kMaxRanks] x 8 bytes
+    const void* in;
+    void* out;
+    uint64_t bytes;                  // payload bytes per (source, destination) pair, <= kLLMaxBytes
+    uint32_t send_mask;              // bit j: this rank sends `bytes` from in + send_off[j] to rank j
+    uint32_t recv_mask;              // bit q: this rank consumes the payload rank q sent
+    int64_t send_off[kMaxRanks];
+    int64_t recv_off[kMaxRanks];     // copy mode: where source q's payload goes in `out`
+    int self;                        // this rank's own part takes part: copy in + send_off[rank] -> out +
+                                     // recv_off[rank], or (reduce) the operand at in + send_off[rank]
+    int reduce;                      // 1: out[0, bytes) = op over the sources (and self) in rank order
+    int tokens;                      // 1: exchange tokens (rooted operations)
+    float scale;
+    MegRay::DType in_dtype;
+    MegRay::DType out_dtype;
+    MegRay::ReduceOp op;
+};
+cudaError_t launch_ll(const LLArgs& args, int ctas, int threads, cudaStream_t stream);
+
+
+// How the pipelined broadcast cuts a message of `bytes` bytes for n ranks and `ctas` CTAs: n - 1
+// slices (one per non-root rank), every CTA owns `per_cta` bytes of each slice and moves them in
+// `chunks` chunks of `chunk_bytes`.  Host and device compute it alike; the host advances the
+// chunk sequence by `chunks` per call.
+struct BcastPlan {
+    uint64_t slice;    // bytes of one slice (multiple of 16)
+    uint64_t per_cta;  // bytes of a slice one CTA moves (multiple of 16)
+    uint32_t chunks;
+};
+__host__ __device__ inline BcastPlan bcast_plan(uint64_t bytes, int n, int ctas, uint32_t chunk_bytes) {
+    BcastPlan p;
+    const uint64_t ns = n > 1 ? static_cast<uint64_t>(n - 1) : 1;
+    p.slice = ((bytes + ns - 1) / ns + 15) / 16 * 16;
+    p.per_cta = ((p.slice + ctas - 1) / ctas + 15) / 16 * 16;
+    p.chunks = static_cast<uint32_t>((p.per_cta + chunk_bytes - 1) / chunk_bytes);
+    if (p.chunks == 0)
+        p.chunks = 1;
+    return p;
+}
 
 // True if the NVSwitch can reduce this dtype/op pair (multimem.ld_reduce): bf16/fp16 all ops,
 // fp32 SUM; the rest takes peer loads.

@@ -124,6 +124,7 @@ struct KParams {
     const int* k_begin;
     const int* k_end;
     int* error_flag;
+    int* comm_status;
     uint64_t wait_limit_ns;
     FuseArgs fuse;
 };
@@ -264,6 +265,26 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
                  : "memory");
 }
 
+// Bounded poll of a flag word until it reaches `target` (wrap-safe).  Warp-uniform result.
+__device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t target, uint64_t limit_ns,
+                                              volatile int* abort_flag) {
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    while (static_cast<int32_t>(ld_acquire_sys(flag) - target) < 0) {
+        poll_pause(spins < 16 ? 64 : 512);
+        if ((++spins & 63) == 0) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0)
+                t0 = now;
+            if (*abort_flag || now - t0 > limit_ns) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
 // ---------------------------------------------------------------- epilogue of one tile
 // `t_addr`: TMEM address of this warp's lane quarter of the accumulator; `row_base`: the first
 // of the warp's 32 rows inside the tile.  TMEM loads run one chunk ahead of the arithmetic and
@@ -325,7 +346,7 @@ __device__ __forceinline__ void emit_box32(const CUtensorMap* map, OutRing& ring
 template <int EPI>
 __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, uint32_t t_addr,
                                               int row_base, int lane, bool zero_tile, uint8_t* stage_warp,
-                                              OutRing& out) {
+                                              OutRing& out, volatile int* abort_flag) {
     const int row_in_tile = row_base + lane;
     if (EPI == EPI_PUSH || EPI == EPI_STORE_ROWS) {
         // The 32 rows of this warp all belong to one owner rank (owners hold whole row blocks).
@@ -337,6 +358,23 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
                 EPI == EPI_PUSH ? static_cast<__nv_bfloat16*>(p.peer_out != nullptr ? p.peer_out[peer]
                                                                                    : p.fuse.rs_peer_out[peer])
                                 : p.D;
+        // GEMM -> reduce_scatter: rows this rank owns are not pushed anywhere.  Their tiles come
+        // last in every rank's order, so by now the other ranks' partial tiles for these 32 rows x
+        // 256 columns have (nearly always) landed in the local staging slots: wait for their
+        // counter, then sum the partials in rank order, with this rank's own partial taken from
+        // the staging rows in shared memory, and write the output shard.
+        const bool own = EPI == EPI_PUSH && p.fuse.rs_out != nullptr && peer == p.fuse.rank;
+        if (own && tl.m0 + row_base < p.M) {
+            int ok = 1;
+            if (lane == 0) {
+                const uint32_t* cnt = p.fuse.rs_count_local +
+                                      static_cast<size_t>(prow0 / 32) * p.fuse.rs_col_tiles + tl.n0 / BN;
+                ok = wait_flag_sys(cnt, p.fuse.rs_target, p.wait_limit_ns, abort_flag) ? 1 : 0;
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok)
+                return;  // the wait ran out: the kernel is winding down, nothing more is written
+        }
         uint32_t ra[32], rb[32];
         if (zero_tile) {
 #pragma unroll
@@ -363,12 +401,64 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
             __syncwarp();
             // 8 lanes write one row's 128 bytes: four rows per store instruction
             const int col = tl.n0 + c * 64 + (lane & 7) * 8;
+            if (!own) {
 #pragma unroll
-            for (int it = 0; it < 8; ++it) {
-                const int rr = it * 4 + (lane >> 3);
-                const uint4 v = *reinterpret_cast<const uint4*>(stage_warp + rr * 128 + (((lane & 7) ^ (rr & 7)) << 4));
-                if (tl.m0 + row_base + rr < p.M && col + 8 <= p.N)
-                    *reinterpret_cast<uint4*>(base + (prow0 + rr) * p.ldd + col) = v;
+                for (int it = 0; it < 8; ++it) {
+                    const int rr = it * 4 + (lane >> 3);
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage_warp + rr * 128 + (((lane & 7) ^ (rr & 7)) << 4));
+                    if (tl.m0 + row_base + rr < p.M && col + 8 <= p.N)
+                        *reinterpret_cast<uint4*>(base + (prow0 + rr) * p.ldd + col) = v;
+                }
+            } else {
+                const FuseArgs& f = p.fuse;
+                const size_t slot_elems = static_cast<size_t>(f.shard_rows) * (f.row_bytes / 2);
+                const __nv_bfloat16* slots = static_cast<const __nv_bfloat16*>(f.rs_stage_local);
+                const __nv_bfloat16* resid = static_cast<const __nv_bfloat16*>(f.rs_residual);
+                __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(f.rs_out);
+                auto add8 = [](float (&acc)[8], const uint4& v) {
+                    acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+                    acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+                };
+                // two row groups at a time: all partials' loads are issued before the first use
+#pragma unroll
+                for (int it0 = 0; it0 < 8; it0 += 2) {
+                    uint4 part[2][8];
+                    uint4 res[2];
+                    bool okr[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int rr = (it0 + u) * 4 + (lane >> 3);
+                        okr[u] = tl.m0 + row_base + rr < p.M && col + 8 <= p.N;
+                        const size_t off = static_cast<size_t>(prow0 + rr) * p.ldd + col;
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            if (q < f.nranks && q != f.rank && okr[u])
+                                part[u][q] = __ldcg(reinterpret_cast<const uint4*>(slots + q * slot_elems + off));
+                        if (resid != nullptr && okr[u])
+                            res[u] = *reinterpret_cast<const uint4*>(resid + off);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int rr = (it0 + u) * 4 + (lane >> 3);
+                        if (!okr[u])
+                            continue;
+                        const uint4 mine =
+                                *reinterpret_cast<const uint4*>(stage_warp + rr * 128 + (((lane & 7) ^ (rr & 7)) << 4));
+                        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            if (q < f.nranks)
+                                add8(acc, q == f.rank ? mine : part[u][q]);
+                        if (resid != nullptr)
+                            add8(acc, res[u]);
+                        uint4 o;
+                        o.x = pack_bf16x2(acc[0], acc[1]);
+                        o.y = pack_bf16x2(acc[2], acc[3]);
+                        o.z = pack_bf16x2(acc[4], acc[5]);
+                        o.w = pack_bf16x2(acc[6], acc[7]);
+                        *reinterpret_cast<uint4*>(dst + static_cast<size_t>(prow0 + rr) * p.ldd + col) = o;
+                    }
+                }
             }
             __syncwarp();
         }
@@ -527,25 +617,6 @@ __device__ __forceinline__ void copy16(char* dst, const char* src, uint64_t nbyt
         d4[i] = __ldcg(s4 + i);
 }
 
-// Bounded poll of a flag word until it reaches `target` (wrap-safe).  Warp-uniform result.
-__device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t target, uint64_t limit_ns,
-                                              volatile int* abort_flag) {
-    uint32_t spins = 0;
-    uint64_t t0 = 0;
-    while (static_cast<int32_t>(ld_acquire_sys(flag) - target) < 0) {
-        if ((++spins & 63) == 0) {
-            const uint64_t now = globaltimer_ns();
-            if (t0 == 0)
-                t0 = now;
-            if (*abort_flag || now - t0 > limit_ns) {
-                *abort_flag = 1;
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
 __device__ __forceinline__ void all_gather_warps(const FuseArgs& f, uint64_t limit_ns,
                                                  volatile int* abort_flag, volatile int* comm_ok) {
     const int tid = threadIdx.x - (NUM_THREADS - COMM_THREADS);
@@ -582,72 +653,6 @@ __device__ __forceinline__ void all_gather_warps(const FuseArgs& f, uint64_t lim
                 __threadfence();
                 st_release_gpu(f.ag_ready + q, f.epoch);
             }
-        }
-    }
-}
-
-// ---------------------------------------------------------------- fused reduce_scatter tail
-// After its last tile every CTA waits until all ranks have delivered all partial tiles of
-// this rank's shard (one counter per source rank, bumped once per 128-row tile), then sums
-// its slice of the n staging slots in rank order (fp32) into the output shard.
-__device__ __forceinline__ void reduce_scatter_tail(const FuseArgs& f, uint64_t limit_ns,
-                                                    volatile int* abort_flag, volatile int* comm_ok) {
-    __syncthreads();
-    const int n = f.nranks;
-    if (threadIdx.x == 0)
-        *comm_ok = 1;
-    __syncthreads();
-    if (static_cast<int>(threadIdx.x) < n) {
-        if (!wait_flag_sys(f.rs_count_local + threadIdx.x, f.rs_target, limit_ns, abort_flag))
-            *comm_ok = 0;
-    }
-    __syncthreads();
-    if (*comm_ok == 0)
-        return;
-    const uint64_t shard_elems = static_cast<uint64_t>(f.shard_rows) * (f.row_bytes / 2);
-    const uint64_t nvec = shard_elems / 8;
-    const uint64_t per_cta = (nvec + gridDim.x - 1) / gridDim.x;
-    const uint64_t b = min(nvec, per_cta * blockIdx.x), e = min(nvec, b + per_cta);
-    const uint4* slots = static_cast<const uint4*>(f.rs_stage_local);
-    const uint4* resid = static_cast<const uint4*>(f.rs_residual);
-    uint4* out = static_cast<uint4*>(f.rs_out);
-    // two vectors per thread and iteration, all slots' loads issued before the first use
-    auto add8 = [](float (&acc)[8], const uint4& v) {
-        acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
-        acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
-    };
-    constexpr int U = 2;
-    for (uint64_t i0 = b + threadIdx.x; i0 < e; i0 += static_cast<uint64_t>(U) * NUM_THREADS) {
-        uint4 raw[U][8];
-        uint4 res[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const uint64_t i = i0 + static_cast<uint64_t>(u) * NUM_THREADS;
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-                if (q < n && i < e)
-                    raw[u][q] = __ldcg(slots + static_cast<uint64_t>(q) * nvec + i);
-            if (resid != nullptr && i < e)
-                res[u] = resid[i];
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const uint64_t i = i0 + static_cast<uint64_t>(u) * NUM_THREADS;
-            if (i >= e)
-                break;
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-                if (q < n)
-                    add8(acc, raw[u][q]);
-            if (resid != nullptr)
-                add8(acc, res[u]);
-            uint4 o;
-            o.x = pack_bf16x2(acc[0], acc[1]);
-            o.y = pack_bf16x2(acc[2], acc[3]);
-            o.z = pack_bf16x2(acc[4], acc[5]);
-            o.w = pack_bf16x2(acc[6], acc[7]);
-            out[i] = o;
         }
     }
 }
@@ -752,6 +757,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         uint32_t spins = 0;
                         uint64_t t0 = 0;
                         while (static_cast<int32_t>(ld_acquire_gpu(f) - p.a_ready_target) < 0) {
+                            poll_pause(spins < 16 ? 64 : 256);
                             if ((++spins & 0x3f) == 0) {
                                 uint64_t now = globaltimer_ns();
                                 if (t0 == 0)
@@ -991,7 +997,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         uint32_t spins = 0;
                         uint64_t t0 = 0;
                         while (g0_tiles[q] < i + 1) {
-                            if ((++spins & 0xff) == 0) {
+                            poll_pause(128);
+                            if ((++spins & 0x3f) == 0) {
                                 const uint64_t now = globaltimer_ns();
                                 if (t0 == 0)
                                     t0 = now;
@@ -1003,7 +1010,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                             }
                         }
                     } else {
-                        got = mbar_wait(tfull0 + 8 * acc, acc_ph, wc);
+                        // one lane sleeps on the barrier for the warp
+                        got = lane == 0 ? mbar_wait(tfull0 + 8 * acc, acc_ph, wc) : true;
                     }
                     if (!__all_sync(0xffffffffu, got))
                         break;
@@ -1019,7 +1027,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     const int sub_row = sub * 256 + static_cast<int>(crank) * BM;  // this CTA's rows of the sub-tile
                     const uint32_t t_addr =
                             tmem_base + (MSUB > 1 ? sub : acc) * BN + (static_cast<uint32_t>(q * 32) << 16);
-                    epilogue_tile<EPI>(p, tl, t_addr, sub_row + q * 32, lane, zero_tile, stage_warp, out);
+                    epilogue_tile<EPI>(p, tl, t_addr, sub_row + q * 32, lane, zero_tile, stage_warp, out, abort_flag);
                     if (!zero_tile) {
                         tc_fence_before();
                         __syncwarp();
@@ -1032,13 +1040,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         }
                     }
                     if (EPI == EPI_PUSH && p.fuse.rs_count_peer[0] != nullptr && tl.m0 + sub_row < p.M) {
-                        // this warp's 32 rows of the partial tile are in the owner's staging slot:
-                        // make them visible system-wide, then count them (4 counts per 128-row block)
+                        // this warp's 32 rows x 256 columns of the partial tile are in the owner's
+                        // staging slot: make them visible system-wide, then count them in the
+                        // owner's counter of that (row group, column tile)
                         __syncwarp();
-                        if (lane == 0) {
-                            const int owner = (tl.m0 + sub_row) / p.rows_per_peer;
+                        const int row0 = tl.m0 + sub_row + q * 32;
+                        const int owner = row0 / p.rows_per_peer;
+                        if (lane == 0 && owner != p.fuse.rank) {
+                            const size_t idx = static_cast<size_t>((row0 - owner * p.rows_per_peer) / 32) *
+                                                       p.fuse.rs_col_tiles + tl.n0 / BN;
                             __threadfence_system();
-                            red_release_sys_add(p.fuse.rs_count_peer[owner] + p.fuse.rank, 1u);
+                            red_release_sys_add(p.fuse.rs_count_peer[owner] + idx, 1u);
                         }
                     }
                 }
@@ -1054,9 +1066,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 tma_store_wait<0>();
         }
     }
-    if (EPI == EPI_PUSH && p.fuse.rs_out != nullptr)
-        reduce_scatter_tail(p.fuse, p.wait_limit_ns, abort_flag, comm_ok);
-
     // ---------------------------------------------------------- teardown
     __syncwarp();
     tc_fence_before();
@@ -1073,6 +1082,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
         if (threadIdx.x == 0 && p.error_flag != nullptr)
             atomicExch(p.error_flag, 1);
+        // a fused collective's wait ran out: the communicator learns of it as MEGRAY_TIMEOUT
+        if (threadIdx.x == 0 && p.comm_status != nullptr)
+            atomicCAS(p.comm_status, 0, 12);
     }
     __syncthreads();
     if (warp == 1) {
@@ -1291,6 +1303,11 @@ Plan plan_tiles(const GemmArgs& a, KParams* kpp, int sms) {
         // 13.3-14.0 ms on the wide one for 32768 x 28672 x 8192)
         pl.wide = a.M >= 1024 && a.K >= 3072 && tiles_wide >= 2L * (sms / 2) && a.epilogue != EPI_DSWIGLU;
     }
+    // GEMM -> reduce_scatter waits, in the tiles of the rows it owns, for the other ranks' tiles of
+    // the same rows.  That cannot deadlock as long as those tiles come strictly earlier in the
+    // other ranks' order, which the row rotation guarantees when a shard is a whole number of tiles.
+    if (pl.wide && a.fuse.rs_out != nullptr && a.fuse.shard_rows % 512 != 0)
+        pl.wide = false;
     pl.tile_m = pl.wide ? 512 : pl.pair ? 256 : BM;
     const int tile_m = pl.tile_m;
     kp.M = a.M;
@@ -1368,6 +1385,7 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     kp.peer_out = a.peer_out;
     kp.rows_per_peer = a.rows_per_peer > 0 ? a.rows_per_peer : a.M;
     kp.error_flag = a.error_flag;
+    kp.comm_status = a.comm_status;
     kp.wait_limit_ns = a.wait_limit_ns ? a.wait_limit_ns : 4000000000ull;
     kp.fuse = a.fuse;
 

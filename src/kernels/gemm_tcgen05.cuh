@@ -49,16 +49,20 @@ struct FuseArgs {
     uint32_t* ag_count;              // [nranks] local, zero between calls
     uint32_t* ag_start_peer[8];      // peer q's start-flag array (this rank writes slot [rank])
     const uint32_t* ag_start_local;  // this rank's start-flag array [nranks]
-    // GEMM -> reduce_scatter (EPI_PUSH): peer_out[p] is rank p's staging slot for this
-    // rank's partial rows; every finished 32-row quarter of a tile bumps rs_count_peer[p][rank]; the tail
-    // waits for rs_count_local[q] >= rs_target for all q and writes
-    // rs_out = sum_q rs_stage_local[q] (+ rs_residual).
+    // GEMM -> reduce_scatter (EPI_PUSH): rs_peer_out[p] is rank p's staging slot for this rank's
+    // partial rows.  Every finished piece of 32 rows x 256 columns that belongs to another rank
+    // bumps that rank's counter [row group of the shard][column tile] (rs_count_peer[p]).  Rows
+    // this rank owns are not pushed: their tiles come last in the tile order, and their epilogue
+    // waits until the counter of its piece reaches rs_target (all other ranks have delivered),
+    // adds the other ranks' staged partials (rs_stage_local, slot q = rank q's rows) and
+    // rs_residual to its own partial in rank order and writes rs_out.
     void* rs_peer_out[8];            // rank p's staging slot for this rank's partial rows
     uint32_t* rs_count_peer[8];      // [0] null = no counting
-    const uint32_t* rs_count_local;  // [nranks]
-    uint32_t rs_target;
+    const uint32_t* rs_count_local;  // [shard_rows / 32][rs_col_tiles]
+    int rs_col_tiles;                // 256-column tiles per row: (N + 255) / 256
+    uint32_t rs_target;              // (nranks - 1) x (calls on these counters so far, this one included)
     const void* rs_stage_local;      // this rank's n staging slots, slot q = rank q's partial rows
-    void* rs_out;                    // null = no tail reduce in this kernel
+    void* rs_out;                    // null = plain push (no reduction in this kernel)
     const void* rs_residual;         // optional: added to the reduced shard
 };
 
@@ -87,6 +91,7 @@ struct GemmArgs {
     GroupedArgs grouped;
     FuseArgs fuse;            // zero-initialised = no fused collective
     int* error_flag;          // device word; non-zero after a wait ran out
+    int* comm_status;         // optional: a communicator's status word, set to MEGRAY_TIMEOUT then
     uint64_t wait_limit_ns;   // 0 = default (4 s)
 };
 

@@ -178,22 +178,28 @@ __global__ void __launch_bounds__(256) dispatch_kernel(const uint4* __restrict__
                                                        const int* __restrict__ idx, const float* __restrict__ w,
                                                        const int* __restrict__ send_base, int* __restrict__ cursor,
                                                        const int* __restrict__ pos_in, int* __restrict__ pos_out,
-                                                       PeerBufs dst, int local_experts, int capacity) {
+                                                       PeerBufs dst, int experts, int local_experts,
+                                                       int capacity) {
     static_assert(kTopK == 2, "the dispatch kernel stores each token to two experts");
     const int lane = threadIdx.x & 31;
     const int wpb = blockDim.x >> 5;
     for (int t = blockIdx.x * wpb + (threadIdx.x >> 5); t < tokens; t += gridDim.x * wpb) {
         const int i0 = t * kTopK;
         const int e0 = idx[i0], e1 = idx[i0 + 1];
+        // an expert id that no rank owns names no cursor and no buffer: the (token, slot) is dropped
+        const bool in0 = static_cast<unsigned>(e0) < static_cast<unsigned>(experts);
+        const bool in1 = static_cast<unsigned>(e1) < static_cast<unsigned>(experts);
         int row0, row1;
         if (pos_in != nullptr) {
             row0 = pos_in[i0];
             row1 = pos_in[i0 + 1];
         } else {
-            row0 = row1 = 0;
+            row0 = row1 = -1;
             if (lane == 0) {
-                row0 = send_base[e0] + atomicAdd(&cursor[e0], 1);
-                row1 = send_base[e1] + atomicAdd(&cursor[e1], 1);
+                if (in0)
+                    row0 = send_base[e0] + atomicAdd(&cursor[e0], 1);
+                if (in1)
+                    row1 = send_base[e1] + atomicAdd(&cursor[e1], 1);
                 pos_out[i0] = row0;
                 pos_out[i0 + 1] = row1;
             }
@@ -201,13 +207,13 @@ __global__ void __launch_bounds__(256) dispatch_kernel(const uint4* __restrict__
             row1 = __shfl_sync(0xffffffffu, row1, 0);
         }
         // a full owner buffer (the plan has raised the overflow flag) drops the row
-        const bool ok0 = row0 >= 0 && row0 < capacity, ok1 = row1 >= 0 && row1 < capacity;
+        const bool ok0 = in0 && row0 >= 0 && row0 < capacity, ok1 = in1 && row1 >= 0 && row1 < capacity;
         if (!ok0 && !ok1)
             continue;
         const float s0 = w != nullptr ? w[i0] : 1.f, s1 = w != nullptr ? w[i0 + 1] : 1.f;
         const uint4* s = src + static_cast<size_t>(t) * row_vecs;
-        uint4* d0 = static_cast<uint4*>(dst.p[e0 / local_experts]) + static_cast<size_t>(ok0 ? row0 : 0) * row_vecs;
-        uint4* d1 = static_cast<uint4*>(dst.p[e1 / local_experts]) + static_cast<size_t>(ok1 ? row1 : 0) * row_vecs;
+        uint4* d0 = ok0 ? static_cast<uint4*>(dst.p[e0 / local_experts]) + static_cast<size_t>(row0) * row_vecs : nullptr;
+        uint4* d1 = ok1 ? static_cast<uint4*>(dst.p[e1 / local_experts]) + static_cast<size_t>(row1) * row_vecs : nullptr;
         auto scaled = [](const uint4& x, float f) {
             uint4 y;
             y.x = pack(lo(x.x) * f, hi(x.x) * f);
@@ -246,17 +252,17 @@ __global__ void __launch_bounds__(256) combine_kernel(uint4* __restrict__ out, i
     for (int t = blockIdx.x * wpb + (threadIdx.x >> 5); t < tokens; t += gridDim.x * wpb) {
         const int e0 = idx[2 * t], e1 = idx[2 * t + 1];
         float w0 = w != nullptr ? w[2 * t] : 1.f, w1 = w != nullptr ? w[2 * t + 1] : 1.f;
-        int p0 = pos[2 * t], p1 = pos[2 * t + 1];
-        if (p0 < 0 || p0 >= capacity) {  // dropped at dispatch: contributes nothing
-            p0 = 0;
+        const int p0 = pos[2 * t], p1 = pos[2 * t + 1];
+        // dropped at dispatch (full owner buffer, or an expert id nobody owns): contributes nothing
+        const unsigned owned = static_cast<unsigned>(kMaxRanks * local_experts);
+        const bool ok0 = p0 >= 0 && p0 < capacity && static_cast<unsigned>(e0) < owned;
+        const bool ok1 = p1 >= 0 && p1 < capacity && static_cast<unsigned>(e1) < owned;
+        if (!ok0)
             w0 = 0.f;
-        }
-        if (p1 < 0 || p1 >= capacity) {
-            p1 = 0;
+        if (!ok1)
             w1 = 0.f;
-        }
-        const uint4* a = static_cast<const uint4*>(src.p[e0 / local_experts]) + static_cast<size_t>(p0) * row_vecs;
-        const uint4* b = static_cast<const uint4*>(src.p[e1 / local_experts]) + static_cast<size_t>(p1) * row_vecs;
+        const uint4* a = ok0 ? static_cast<const uint4*>(src.p[e0 / local_experts]) + static_cast<size_t>(p0) * row_vecs : nullptr;
+        const uint4* b = ok1 ? static_cast<const uint4*>(src.p[e1 / local_experts]) + static_cast<size_t>(p1) * row_vecs : nullptr;
         uint4* o = out + static_cast<size_t>(t) * row_vecs;
         // four vectors of each row per lane and iteration: eight (possibly remote) loads in flight
         constexpr int U = 4;
@@ -265,8 +271,8 @@ __global__ void __launch_bounds__(256) combine_kernel(uint4* __restrict__ out, i
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 if (v0 + 32 * u < row_vecs) {
-                    x[u] = __ldcg(a + v0 + 32 * u);
-                    y[u] = __ldcg(b + v0 + 32 * u);
+                    x[u] = ok0 ? __ldcg(a + v0 + 32 * u) : make_uint4(0, 0, 0, 0);
+                    y[u] = ok1 ? __ldcg(b + v0 + 32 * u) : make_uint4(0, 0, 0, 0);
                 }
             }
 #pragma unroll
@@ -291,7 +297,8 @@ __global__ void __launch_bounds__(256) combine_dw_kernel(const uint4* __restrict
     const int wpb = blockDim.x >> 5;
     const int pairs = tokens * kTopK;
     for (int i = blockIdx.x * wpb + (threadIdx.x >> 5); i < pairs; i += gridDim.x * wpb) {
-        if (pos[i] < 0 || pos[i] >= capacity) {
+        if (pos[i] < 0 || pos[i] >= capacity ||
+            static_cast<unsigned>(idx[i]) >= static_cast<unsigned>(kMaxRanks * local_experts)) {
             if (lane == 0)
                 dw[i] = 0.f;
             continue;
@@ -362,12 +369,13 @@ cudaError_t launch_zero_pads(void* buf, int row_elems, const int* seg_begin, con
 
 cudaError_t launch_dispatch(const void* src, int tokens, int row_elems, const int* idx, const float* w,
                             const int* send_base, int* cursor, const int* pos_in, int* pos_out, PeerBufs dst,
-                            int local_experts, int capacity, cudaStream_t stream) {
-    if (tokens <= 0 || row_elems % 8 || local_experts < 1)
+                            int experts, int local_experts, int capacity, cudaStream_t stream) {
+    if (tokens <= 0 || row_elems % 8 || local_experts < 1 || experts < 1 ||
+        experts > kMaxRanks * local_experts)
         return cudaErrorInvalidValue;
     dispatch_kernel<<<blocks_for(8, tokens), 256, 0, stream>>>(
             static_cast<const uint4*>(src), tokens, row_elems / 8, idx, w, send_base, cursor, pos_in, pos_out, dst,
-            local_experts, capacity);
+            experts, local_experts, capacity);
     count_launch();
     return cudaGetLastError();
 }

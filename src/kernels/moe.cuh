@@ -57,9 +57,12 @@ struct PeerBufs {
 // Dispatch.  For every (token t, slot k): row = pos_in[t,k] if pos_in != null, else
 // send_base[e] + (a unique slot taken from cursor[e], which must be zero before) and pos_out[t,k] =
 // row; then dst[e / local_experts][row, :] = scale * src[t, :], scale = w[t,k] if w != null else 1.
+// `experts` is the number of experts the buffers in `dst` own together; an idx entry outside
+// [0, experts) drops that (token, slot): pos_out = -1 and nothing else is touched for it.
 cudaError_t launch_dispatch(const void* src, int tokens, int row_elems, const int* idx, const float* w,
                             const int* send_base, int* cursor, const int* pos_in, int* pos_out,
-                            PeerBufs dst, int local_experts, int capacity_rows, cudaStream_t stream);
+                            PeerBufs dst, int experts, int local_experts, int capacity_rows,
+                            cudaStream_t stream);
 
 // Combine: out[t, :] = sum_k (w ? w[t,k] : 1) * src[idx[t,k] / local_experts][pos[t,k], :].
 cudaError_t launch_combine(void* out, int tokens, int row_elems, const int* idx, const float* w,

@@ -10,6 +10,7 @@
 #include <mutex>
 
 #include "launch_count.h"
+#include "moe.cuh"
 
 namespace {
 
@@ -33,37 +34,56 @@ __device__ __forceinline__ uint32_t pack(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// One warp per (token, slot): take a row of the expert's segment, remember it, store the row.
+// One warp per token: both of its experts take the next row of their segments, the token's row is
+// read once and stored to both.  idx, w and pos_out are [tokens, 2] (top-2 routing, as in moe.cu).
+// An expert id outside [0, experts) names no cursor and no owner: that (token, slot) is dropped,
+// pos_out = -1, and nothing else is touched.
 __global__ void __launch_bounds__(256)
         dispatch_noalloc_kernel(const uint4* __restrict__ src, int tokens, int row_vecs, const int* __restrict__ idx,
                                 const float* __restrict__ w, const int* __restrict__ send_base,
-                                int* __restrict__ cursor, int* __restrict__ pos_out, Peers dst, int local_experts,
-                                int capacity) {
+                                int* __restrict__ cursor, int* __restrict__ pos_out, Peers dst, int experts,
+                                int local_experts, int capacity) {
+    static_assert(mgk::moe::kTopK == 2, "the kernel stores each token to two experts");
     const int lane = threadIdx.x & 31;
     const int wpb = blockDim.x >> 5;
-    const int pairs = tokens * 2;
-    for (int i = blockIdx.x * wpb + (threadIdx.x >> 5); i < pairs; i += gridDim.x * wpb) {
-        const int e = idx[i];
-        int row = 0;
+    for (int t = blockIdx.x * wpb + (threadIdx.x >> 5); t < tokens; t += gridDim.x * wpb) {
+        const int i0 = 2 * t;
+        const int e0 = idx[i0], e1 = idx[i0 + 1];
+        const bool in0 = static_cast<unsigned>(e0) < static_cast<unsigned>(experts);
+        const bool in1 = static_cast<unsigned>(e1) < static_cast<unsigned>(experts);
+        int row0 = -1, row1 = -1;
         if (lane == 0) {
-            row = send_base[e] + atomicAdd(&cursor[e], 1);
-            pos_out[i] = row;
+            if (in0)
+                row0 = send_base[e0] + atomicAdd(&cursor[e0], 1);
+            if (in1)
+                row1 = send_base[e1] + atomicAdd(&cursor[e1], 1);
+            pos_out[i0] = row0;
+            pos_out[i0 + 1] = row1;
         }
-        row = __shfl_sync(0xffffffffu, row, 0);
-        if (row < 0 || row >= capacity)
-            continue;  // the owner's buffer is full: the row is dropped, as in the regular dispatch
-        const float scale = w != nullptr ? w[i] : 1.f;
-        const uint4* s = src + static_cast<size_t>(i / 2) * row_vecs;
-        uint4* d = static_cast<uint4*>(dst.p[e / local_experts]) + static_cast<size_t>(row) * row_vecs;
+        row0 = __shfl_sync(0xffffffffu, row0, 0);
+        row1 = __shfl_sync(0xffffffffu, row1, 0);
+        // a full owner buffer drops the row, as in the regular dispatch
+        const bool ok0 = in0 && row0 >= 0 && row0 < capacity, ok1 = in1 && row1 >= 0 && row1 < capacity;
+        if (!ok0 && !ok1)
+            continue;
+        const float s0 = w != nullptr ? w[i0] : 1.f, s1 = w != nullptr ? w[i0 + 1] : 1.f;
+        const uint4* s = src + static_cast<size_t>(t) * row_vecs;
+        uint4* d0 = ok0 ? static_cast<uint4*>(dst.p[e0 / local_experts]) + static_cast<size_t>(row0) * row_vecs : nullptr;
+        uint4* d1 = ok1 ? static_cast<uint4*>(dst.p[e1 / local_experts]) + static_cast<size_t>(row1) * row_vecs : nullptr;
+        auto scaled = [](const uint4& x, float f) {
+            uint4 y;
+            y.x = pack(lo(x.x) * f, hi(x.x) * f);
+            y.y = pack(lo(x.y) * f, hi(x.y) * f);
+            y.z = pack(lo(x.z) * f, hi(x.z) * f);
+            y.w = pack(lo(x.w) * f, hi(x.w) * f);
+            return y;
+        };
         for (int v = lane; v < row_vecs; v += 32) {
-            uint4 x = s[v];
-            if (w != nullptr) {
-                x.x = pack(lo(x.x) * scale, hi(x.x) * scale);
-                x.y = pack(lo(x.y) * scale, hi(x.y) * scale);
-                x.z = pack(lo(x.z) * scale, hi(x.z) * scale);
-                x.w = pack(lo(x.w) * scale, hi(x.w) * scale);
-            }
-            d[v] = x;
+            const uint4 x = s[v];
+            if (ok0)
+                d0[v] = w != nullptr ? scaled(x, s0) : x;
+            if (ok1)
+                d1[v] = w != nullptr ? scaled(x, s1) : x;
         }
     }
 }
@@ -108,6 +128,12 @@ extern "C" int megray_moe_dispatch_noalloc(const void* src, int tokens, int row_
                         "elements, 1..8 ranks, non-null inputs and outputs)\n");
         return 6;
     }
+    if (static_cast<long>(experts) > static_cast<long>(nranks) * local_experts) {
+        fprintf(stderr, "megray_moe_dispatch_noalloc: %d experts need %d owners of %d experts each, but only %d "
+                        "peer buffers were given\n",
+                experts, (experts + local_experts - 1) / local_experts, local_experts, nranks);
+        return 6;
+    }
     int* cursor = nullptr;
     cudaError_t e = cursor_address(&cursor);
     if (e != cudaSuccess)
@@ -120,12 +146,12 @@ extern "C" int megray_moe_dispatch_noalloc(const void* src, int tokens, int row_
     Peers dst{};
     for (int q = 0; q < nranks; ++q)
         dst.p[q] = peer_bufs[q];
-    long blocks = (static_cast<long>(tokens) * 2 + 7) / 8;
+    long blocks = (static_cast<long>(tokens) + 7) / 8;
     if (blocks > 148 * 8)
         blocks = 148 * 8;
     dispatch_noalloc_kernel<<<static_cast<int>(blocks), 256, 0, s>>>(
             static_cast<const uint4*>(src), tokens, row_elems / 8, idx, w, send_base, cursor, pos_out, dst,
-            local_experts, capacity_rows);
+            experts, local_experts, capacity_rows);
     mgk::count_launch();
     e = cudaGetLastError();
     return e == cudaSuccess ? 0 : -static_cast<int>(e);

@@ -52,16 +52,20 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta_r
             "r"(cta_rank)
             : "memory");
 }
+// try_wait suspends the thread until the phase completes or a time limit passes; the hint asks
+// for a long limit (nanoseconds), so a thread that waits for a whole tile sleeps in hardware
+// instead of re-issuing the instruction.  It wakes as soon as the phase completes.
+constexpr uint32_t kSuspendHintNs = 10000000u;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
             "{\n"
             " .reg .pred p;\n"
-            " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
             " selp.u32 %0, 1, 0, p;\n"
             "}\n"
             : "=r"(ok)
-            : "r"(bar), "r"(parity)
+            : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
             : "memory");
     return ok != 0;
 }
@@ -70,13 +74,18 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
     asm volatile(
             "{\n"
             " .reg .pred p;\n"
-            " mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+            " mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n"
             " selp.u32 %0, 1, 0, p;\n"
             "}\n"
             : "=r"(ok)
-            : "r"(bar), "r"(parity)
+            : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
             : "memory");
     return ok != 0;
+}
+// Pause between two polls of a flag in global or shared memory (ns, approximate): a poll loop
+// that sleeps leaves the issue slots and the memory pipes to the warps that do the work.
+__device__ __forceinline__ void poll_pause(uint32_t ns) {
+    asm volatile("nanosleep.u32 %0;" ::"r"(ns) : "memory");
 }
 
 // Wait limit shared by all bounded waits of one kernel: `abort_flag` lives in
@@ -96,7 +105,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
         bool ok = kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity);
         if (ok)
             return true;
-        if ((++spins & 0xff) == 0) {
+        // each failed try has already slept up to the hardware's limit: check the clock often
+        if ((++spins & 0x7) == 0) {
             if (*w.abort_flag)
                 return false;
             uint64_t now = globaltimer_ns();

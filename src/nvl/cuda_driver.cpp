@@ -47,6 +47,7 @@ const Api* api() {
         ok &= resolve("cuMemImportFromShareableHandle", g_api.MemImportFromShareableHandle);
         ok &= resolve("cuDeviceGetAttribute", g_api.DeviceGetAttribute);
         ok &= resolve("cuMemGetAddressRange", g_api.MemGetAddressRange);
+        ok &= resolve("cuPointerGetAttributes", g_api.PointerGetAttributes);
         resolve("cuMulticastCreate", g_api.MulticastCreate, false);
         resolve("cuMulticastAddDevice", g_api.MulticastAddDevice, false);
         resolve("cuMulticastBindMem", g_api.MulticastBindMem, false);

@@ -27,6 +27,7 @@ struct Api {
                                              CUmemAllocationHandleType);
     CUresult (*DeviceGetAttribute)(int*, CUdevice_attribute, CUdevice);
     CUresult (*MemGetAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr);
+    CUresult (*PointerGetAttributes)(unsigned int, CUpointer_attribute*, void**, CUdeviceptr);
     CUresult (*MulticastCreate)(CUmemGenericAllocationHandle*, const CUmulticastObjectProp*);
     CUresult (*MulticastAddDevice)(CUmemGenericAllocationHandle, CUdevice);
     CUresult (*MulticastBindMem)(CUmemGenericAllocationHandle, size_t, CUmemGenericAllocationHandle,

@@ -1,25 +1,21 @@
 #include "nvl/fused_tp.h"
 
-#include <map>
-#include <mutex>
-
 #include "megray/fused.h"
 #include "megray/trace.h"
 
 namespace MegRay {
 
 namespace {
-// cumulative count of delivered tile quarters per flag block (what the tail reduce waits for)
-std::mutex g_mu;
-std::map<const void*, uint32_t> g_rs_totals;
-
 struct FlagBlock {
     uint32_t ag_ready[8];
     uint32_t ag_count[8];
     uint32_t ag_start[8];
-    uint32_t rs_count[8];
 };
 }  // namespace
+
+size_t tp_rs_counter_bytes(int shard_rows, int n_cols) {
+    return static_cast<size_t>((shard_rows + 31) / 32) * static_cast<size_t>((n_cols + 255) / 256) * sizeof(uint32_t);
+}
 
 Status tp_ag_gemm(Communicator* comm, mgk::gemm::GemmArgs g, void* gather_buf, const void* shard_src,
                   void* flags, cudaStream_t stream) {
@@ -30,6 +26,7 @@ Status tp_ag_gemm(Communicator* comm, mgk::gemm::GemmArgs g, void* gather_buf, c
     if (g.a_mn || g.M % n || !nvl->in_heap(gather_buf, 1) || !nvl->in_heap(shard_src, 1) ||
         !nvl->in_heap(flags, kTpFlagBytes))
         return MEGRAY_INVALID_ARGUMENT;
+    MEGRAY_CHECK(nvl->fused_begin(stream));
     TraceScope trace("tp_ag_gemm", static_cast<size_t>(g.M) * g.K * 2, comm->rank());
     const int shard_rows = g.M / n;
     const size_t row_bytes = static_cast<size_t>(g.lda) * 2;
@@ -68,39 +65,42 @@ Status tp_ag_gemm(Communicator* comm, mgk::gemm::GemmArgs g, void* gather_buf, c
     g.m_rot = rank * shard_rows;  // own shard first, then in the order the shards arrive
     if (g.wait_limit_ns == 0)
         g.wait_limit_ns = nvl->device_timeout_ns();
+    g.comm_status = nvl->status_word();
     cudaError_t e = mgk::gemm::launch_gemm_bf16(g, stream);
     if (e != cudaSuccess) {
         MEGRAY_ERROR("tp_ag_gemm launch: %s", cudaGetErrorString(e));
         return MEGRAY_CUDA_ERR;
     }
+    nvl->fused_end(stream);
     return MEGRAY_OK;
 }
 
 Status tp_gemm_rs(Communicator* comm, mgk::gemm::GemmArgs g, void* staging, void* out,
-                  const void* residual, void* flags, cudaStream_t stream) {
+                  const void* residual, void* counters, size_t counter_bytes, cudaStream_t stream) {
     NvlInterface* nvl = as_nvl(comm);
     if (nvl == nullptr)
         return MEGRAY_INVALID_USAGE;
     const int n = static_cast<int>(comm->nranks()), rank = static_cast<int>(comm->rank());
-    if (g.M % n || !nvl->in_heap(staging, 1) || !nvl->in_heap(flags, kTpFlagBytes) || out == nullptr)
+    if (g.M % n || out == nullptr)
         return MEGRAY_INVALID_ARGUMENT;
-    TraceScope trace("tp_gemm_rs", static_cast<size_t>(g.M) * g.N * 2, comm->rank());
     const int shard_rows = g.M / n;
     if (shard_rows % 256 || g.N % 8)
         return MEGRAY_INVALID_ARGUMENT;
     const size_t row_bytes = static_cast<size_t>(g.N) * 2;
     const size_t shard_bytes = static_cast<size_t>(shard_rows) * row_bytes;
-    auto* fb = static_cast<FlagBlock*>(flags);
-
-    // each 128-row x 256-column tile is counted four times (once per epilogue warp)
-    const uint32_t per_call = static_cast<uint32_t>(shard_rows / 128) * static_cast<uint32_t>((g.N + 255) / 256) * 4u;
-    uint32_t target;
-    {
-        std::lock_guard<std::mutex> lk(g_mu);
-        uint32_t& total = g_rs_totals[flags];
-        total += per_call;
-        target = total;
+    const size_t need = tp_rs_counter_bytes(shard_rows, g.N);
+    if (counter_bytes < need || !nvl->in_heap(counters, need) || !nvl->in_heap(staging, shard_bytes * n)) {
+        MEGRAY_ERROR("tp_gemm_rs: staging (%zu bytes) and counters (%zu bytes) must lie in the symmetric heap",
+                     shard_bytes * n, need);
+        return MEGRAY_INVALID_ARGUMENT;
     }
+    MEGRAY_CHECK(nvl->fused_begin(stream));
+    TraceScope trace("tp_gemm_rs", static_cast<size_t>(g.M) * g.N * 2, comm->rank());
+    auto* cnt = static_cast<uint32_t*>(counters);
+
+    // every piece of 32 rows x 256 columns of this rank's shard is delivered once by each other
+    // rank in each call; the counters are cumulative over the calls on this block
+    const uint32_t calls = nvl->fused_call_count(counters);
     mgk::gemm::FuseArgs& f = g.fuse;
     f.nranks = n;
     f.rank = rank;
@@ -109,10 +109,11 @@ Status tp_gemm_rs(Communicator* comm, mgk::gemm::GemmArgs g, void* staging, void
     f.epoch = 0;
     for (int p = 0; p < n; ++p) {
         f.rs_peer_out[p] = static_cast<char*>(nvl->peer_ptr(staging, p)) + static_cast<size_t>(rank) * shard_bytes;
-        f.rs_count_peer[p] = static_cast<FlagBlock*>(nvl->peer_ptr(fb, p))->rs_count;
+        f.rs_count_peer[p] = static_cast<uint32_t*>(nvl->peer_ptr(cnt, p));
     }
-    f.rs_count_local = fb->rs_count;
-    f.rs_target = target;
+    f.rs_count_local = cnt;
+    f.rs_col_tiles = (g.N + 255) / 256;
+    f.rs_target = static_cast<uint32_t>(n - 1) * calls;
     f.rs_stage_local = staging;
     f.rs_out = out;
     f.rs_residual = residual;
@@ -124,11 +125,13 @@ Status tp_gemm_rs(Communicator* comm, mgk::gemm::GemmArgs g, void* staging, void
     g.m_rot = ((rank + 1) % n) * shard_rows;  // rows of remote owners first, own rows last
     if (g.wait_limit_ns == 0)
         g.wait_limit_ns = nvl->device_timeout_ns();
+    g.comm_status = nvl->status_word();
     cudaError_t e = mgk::gemm::launch_gemm_bf16(g, stream);
     if (e != cudaSuccess) {
         MEGRAY_ERROR("tp_gemm_rs launch: %s", cudaGetErrorString(e));
         return MEGRAY_CUDA_ERR;
     }
+    nvl->fused_end(stream);
     return MEGRAY_OK;
 }
 

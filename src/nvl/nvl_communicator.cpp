@@ -1,5 +1,6 @@
 #include "nvl/nvl_communicator.h"
 
+#include <dlfcn.h>
 #include <string.h>
 #include <unistd.h>
 
@@ -83,24 +84,52 @@ NvlCommunicator::NvlCommunicator(uint32_t nranks, uint32_t rank) : Communicator(
     m_direct = env_i64("MEGRAY_DIRECT", 1) != 0;
     m_push_exchange = env_i64("MEGRAY_PUSH_EXCHANGE", 1) != 0;
     m_cta_bytes = static_cast<size_t>(env_i64("MEGRAY_CTA_BYTES", 128 * 1024));
-    // measured crossover points (bench/tune.py) override the built-in defaults; explicit
-    // environment settings override the table
-    if (!o.tune_file.empty()) {
-        const std::string t = read_file(o.tune_file);
-        if (t.empty()) {
-            MEGRAY_WARN("tune file %s is missing or empty", o.tune_file.c_str());
-        } else {
-            if (getenv("MEGRAY_ONESHOT_BYTES") == nullptr)
-                m_oneshot_bytes = static_cast<size_t>(json_i64(t, "oneshot_bytes", static_cast<int64_t>(m_oneshot_bytes)));
-            if (o.max_ctas <= 0)
-                m_max_ctas = std::min<int>(kMaxCtas, static_cast<int>(json_i64(t, "max_ctas", m_max_ctas)));
-            if (getenv("MEGRAY_CTA_BYTES") == nullptr)
-                m_cta_bytes = static_cast<size_t>(json_i64(t, "cta_bytes", static_cast<int64_t>(m_cta_bytes)));
-            m_nvls_min_bytes = static_cast<size_t>(json_i64(t, "nvls_min_bytes", 0));
+    // Measured crossover points (bench/tune.py) override the built-in defaults; explicit
+    // environment settings override the table.  The table is the file MEGRAY_TUNE_FILE names, or
+    // tune/tune_b200_n<ranks>.json beside the library's directory when that file exists.
+    std::string tune_path = o.tune_file;
+    if (tune_path.empty() && env_i64("MEGRAY_TUNE_DEFAULT", 1) != 0) {
+        Dl_info info;
+        if (dladdr(reinterpret_cast<const void*>(&as_nvl), &info) != 0 && info.dli_fname != nullptr) {
+            std::string dir(info.dli_fname);
+            const size_t slash = dir.rfind('/');
+            dir = slash == std::string::npos ? std::string(".") : dir.substr(0, slash);
+            tune_path = dir + "/../tune/tune_b200_n" + std::to_string(nranks) + ".json";
         }
+    }
+    const std::string tune_text = tune_path.empty() ? std::string() : read_file(tune_path);
+    if (tune_text.empty()) {
+        if (!o.tune_file.empty())
+            MEGRAY_WARN("tune file %s is missing or empty", o.tune_file.c_str());
+    } else {
+        MEGRAY_INFO("NVL backend: thresholds from %s", tune_path.c_str());
+        const std::string& t = tune_text;
+        if (getenv("MEGRAY_ONESHOT_BYTES") == nullptr)
+            m_oneshot_bytes = static_cast<size_t>(json_i64(t, "oneshot_bytes", static_cast<int64_t>(m_oneshot_bytes)));
+        if (o.max_ctas <= 0)
+            m_max_ctas = std::min<int>(kMaxCtas, static_cast<int>(json_i64(t, "max_ctas", m_max_ctas)));
+        if (getenv("MEGRAY_CTA_BYTES") == nullptr)
+            m_cta_bytes = static_cast<size_t>(json_i64(t, "cta_bytes", static_cast<int64_t>(m_cta_bytes)));
+        m_nvls_min_bytes = static_cast<size_t>(json_i64(t, "nvls_min_bytes", 0));
     }
     if (m_cta_bytes < 1024)
         m_cta_bytes = 1024;
+    // small-message limits (payload bytes per source / destination pair), per operation
+    static const char* const kKindNames[8] = {"all_reduce", "reduce_scatter", "all_gather", "all_to_all",
+                                              "broadcast",  "reduce",         "gather",     "scatter"};
+    static const size_t kLLDefaults[8] = {65536, 65536, 65536, 65536, 65536, 65536, 65536, 65536};
+    const int64_t ll_all = env_i64("MEGRAY_LL_BYTES", -1);
+    for (int k = 0; k < 8; ++k) {
+        int64_t v = static_cast<int64_t>(kLLDefaults[k]);
+        if (!tune_text.empty())
+            v = json_i64(tune_text, (std::string("ll_") + kKindNames[k]).c_str(), v);
+        if (ll_all >= 0)
+            v = ll_all;
+        m_ll_bytes[k] = std::min<size_t>(static_cast<size_t>(std::max<int64_t>(v, 0)), mgk::coll::kLLMaxBytes);
+    }
+    m_bcast_chunk = static_cast<uint32_t>(round_up(static_cast<size_t>(env_i64("MEGRAY_BCAST_CHUNK", 128 * 1024)), 16));
+    if (m_bcast_chunk < 4096)
+        m_bcast_chunk = 4096;
     if (o.algo == "oneshot")
         m_oneshot_bytes = ~static_cast<size_t>(0);
     else if (o.algo == "twoshot")
@@ -113,6 +142,11 @@ NvlCommunicator::~NvlCommunicator() {
         cudaDeviceSynchronize();
     }
     m_p2p.reset();
+    for (void*& b : m_bounce) {
+        if (b != nullptr)
+            cudaFree(b);
+        b = nullptr;
+    }
     if (m_last_event != nullptr)
         cudaEventDestroy(m_last_event);
     if (m_status_host != nullptr)
@@ -196,6 +230,27 @@ Status NvlCommunicator::do_init() {
     CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&m_status_dev), m_status_host, 0));
     CUDA_CHECK(cudaEventCreateWithFlags(&m_last_event, cudaEventDisableTiming));
 
+    // Ranks that are threads of one process address each other's device memory directly once peer
+    // access is on: then ordinary cudaMalloc buffers need neither staging nor registration.
+    {
+        int32_t mine = m_heap.same_process() && env_i64("MEGRAY_EXCHANGE", 1) != 0 ? 1 : 0;
+        for (uint32_t q = 0; q < m_nranks && mine; ++q) {
+            if (q == m_rank)
+                continue;
+            cudaError_t e = cudaDeviceEnablePeerAccess(m_heap.peer_device(q), 0);
+            if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled)
+                mine = 0;
+            (void)cudaGetLastError();
+        }
+        if (drv::api() == nullptr)
+            mine = 0;
+        std::vector<int32_t> all(m_nranks, 0);
+        MEGRAY_CHECK(m_client->allgather(&mine, all.data(), sizeof(int32_t)));
+        m_xchg = true;
+        for (uint32_t q = 0; q < m_nranks; ++q)
+            m_xchg = m_xchg && all[q] != 0;
+    }
+
 #ifdef MEGRAY_WITH_NCCL
     // point-to-point engine
     if (m_nranks > 1 && env_i64("MEGRAY_NVL_P2P", 1) != 0) {
@@ -213,16 +268,22 @@ Status NvlCommunicator::do_init() {
 }
 
 Status NvlCommunicator::begin(const std::shared_ptr<Context>& ctx, cudaStream_t* stream) {
+    if (!ctx || ctx->type() != MEGRAY_CTX_CUDA) {
+        MEGRAY_ERROR("NVL backend needs a CudaContext");
+        return MEGRAY_INVALID_ARGUMENT;
+    }
+    *stream = static_cast<CudaContext*>(ctx.get())->get_stream();
+    return begin_on(*stream);
+}
+
+Status NvlCommunicator::begin_on(cudaStream_t s) {
+    cudaStream_t* stream = &s;
     if (!m_ready) {
         MEGRAY_ERROR("communicator used before init");
         return MEGRAY_INVALID_USAGE;
     }
     if (m_aborted.load())
         return MEGRAY_ABORTED;
-    if (!ctx || ctx->type() != MEGRAY_CTX_CUDA) {
-        MEGRAY_ERROR("NVL backend needs a CudaContext");
-        return MEGRAY_INVALID_ARGUMENT;
-    }
     if (*m_status_host != 0) {  // an earlier kernel gave up waiting
         if (m_error == MEGRAY_OK) {
             m_error = static_cast<Status>(*m_status_host);
@@ -232,7 +293,6 @@ Status NvlCommunicator::begin(const std::shared_ptr<Context>& ctx, cudaStream_t*
     }
     if (m_error != MEGRAY_OK)
         return m_error;
-    *stream = static_cast<CudaContext*>(ctx.get())->get_stream();
     // Launches of one communicator share staging memory and flag epochs: they must
     // run in issue order even when the caller switches streams.
     if (m_has_last && m_last_stream != *stream) {
@@ -249,7 +309,7 @@ void NvlCommunicator::after_launch(cudaStream_t stream) {
     m_has_last = true;
 }
 
-CommonArgs NvlCommunicator::common_args() {
+CommonArgs NvlCommunicator::common_args(uint32_t epochs) {
     CommonArgs c;
     memset(&c, 0, sizeof(c));
     for (uint32_t q = 0; q < m_nranks; ++q)
@@ -257,11 +317,22 @@ CommonArgs NvlCommunicator::common_args() {
     c.nranks = static_cast<int>(m_nranks);
     c.rank = static_cast<int>(m_rank);
     c.epoch = m_epoch;
-    m_epoch += 2;  // a launch uses at most two barriers
+    m_epoch += epochs;  // a launch uses at most two barriers
     c.timeout_ns = m_timeout_ns;
     c.status = m_status_dev;
     c.flag_off = kFlagOff;
     return c;
+}
+
+Status NvlCommunicator::fused_begin(void* stream) { return begin_on(static_cast<cudaStream_t>(stream)); }
+
+void NvlCommunicator::fused_end(void* stream) { after_launch(static_cast<cudaStream_t>(stream)); }
+
+uint32_t NvlCommunicator::fused_call_count(const void* flags) {
+    if (!in_heap(flags, 1))
+        return 0;
+    const size_t off = static_cast<size_t>(static_cast<const char*>(flags) - m_heap.local());
+    return ++m_fused_calls[off];
 }
 
 uint32_t NvlCommunicator::reserve_epochs(uint32_t count) {
@@ -335,8 +406,7 @@ Status NvlCommunicator::direct_launch(int kind, const void* in, void* out, size_
                       bytes >= m_nvls_min_bytes && kind != mgk::coll::DIRECT_ALL_TO_ALL &&
                       (kind == mgk::coll::DIRECT_ALL_GATHER || mgk::coll::nvls_supports(in_dtype, out_dtype, op));
     a.mc_base = nvls ? m_heap.multicast() : nullptr;
-    a.in_off = nvls ? in_off : 0;
-    a.out_off = nvls ? out_off : 0;
+    a.heap_bytes = m_heap.bytes();
     // single-pass kernels are latency-bound per CTA: smaller shares, more CTAs
     const int ctas = static_cast<int>(std::min<size_t>(std::max<size_t>(1, bytes / (32u << 10)),
                                                        static_cast<size_t>(2 * m_max_ctas > kMaxCtas ? kMaxCtas : 2 * m_max_ctas)));
@@ -346,6 +416,146 @@ Status NvlCommunicator::direct_launch(int kind, const void* in, void* out, size_
         m_stats.algo_nvls++;
     else
         m_stats.algo_twoshot++;
+    return MEGRAY_OK;
+}
+
+
+// ------------------------------------------------------------------ small messages (flagged words)
+
+Status NvlCommunicator::ll_launch(mgk::coll::LLArgs& a, cudaStream_t stream) {
+    a.c = common_args(0);  // no barrier: no epochs
+    if (++m_ll_seq == 0)
+        m_ll_seq = 1;
+    a.seq = m_ll_seq;
+    const int parity = m_ll_parity;
+    m_ll_parity ^= 1;
+    a.slot_off = kLLOff + static_cast<size_t>(parity) * kMaxRanks * mgk::coll::kLLSlotBytes;
+    a.token_off = mgk::coll::kTokenOff + static_cast<size_t>(parity) * kMaxRanks * 8;
+    const size_t units = (a.bytes + 15) / 16;
+    const size_t fan = std::max<size_t>(
+            1, std::max<size_t>(__builtin_popcount(a.send_mask), __builtin_popcount(a.recv_mask) + (a.self ? 1 : 0)));
+    const size_t work = units * fan;
+    // latency-bound at the small end (one small CTA), store-bandwidth-bound at the large end
+    const int threads = work <= 128 ? 128 : 256;
+    const int ctas = static_cast<int>(std::min<size_t>(64, std::max<size_t>(1, (work + 1023) / 1024)));
+    MEGRAY_CHECK(check_cuda(mgk::coll::launch_ll(a, ctas, threads, stream)));
+    after_launch(stream);
+    m_stats.algo_ll++;
+    return MEGRAY_OK;
+}
+
+// ------------------------------------------------------------------ single pass on the call's own buffers
+
+bool NvlCommunicator::peer_addressable(const void* p, size_t bytes) {
+    if (p == nullptr || bytes == 0)
+        return true;
+    if (in_heap(p, bytes))
+        return true;
+    const drv::Api* api = drv::api();
+    if (api == nullptr)
+        return false;
+    // cudaMalloc memory of this rank's device: peers that enabled peer access to the device reach it
+    unsigned int mem_type = 0;
+    int ordinal = -1;
+    int legacy = 0;
+    CUdeviceptr start = 0;
+    size_t size = 0;
+    CUpointer_attribute attrs[5] = {CU_POINTER_ATTRIBUTE_MEMORY_TYPE, CU_POINTER_ATTRIBUTE_DEVICE_ORDINAL,
+                                    CU_POINTER_ATTRIBUTE_IS_LEGACY_CUDA_IPC_CAPABLE,
+                                    CU_POINTER_ATTRIBUTE_RANGE_START_ADDR, CU_POINTER_ATTRIBUTE_RANGE_SIZE};
+    void* vals[5] = {&mem_type, &ordinal, &legacy, &start, &size};
+    if (api->PointerGetAttributes(5, attrs, vals, reinterpret_cast<CUdeviceptr>(p)) != CUDA_SUCCESS)
+        return false;
+    const CUdeviceptr at = reinterpret_cast<CUdeviceptr>(p);
+    return mem_type == CU_MEMORYTYPE_DEVICE && ordinal == m_heap.device() && legacy != 0 && at >= start &&
+           at + bytes <= start + size;
+}
+
+void* NvlCommunicator::bounce(int which, size_t bytes) {
+    if (m_bounce_cap[which] >= bytes)
+        return m_bounce[which];
+    // rare: a buffer the peers cannot address (pool or virtual-memory allocations, host memory)
+    cudaDeviceSynchronize();
+    if (m_bounce[which] != nullptr)
+        cudaFree(m_bounce[which]);
+    m_bounce[which] = nullptr;
+    m_bounce_cap[which] = 0;
+    const size_t cap = round_up(bytes, 2u << 20);
+    if (cudaMalloc(&m_bounce[which], cap) != cudaSuccess) {
+        (void)cudaGetLastError();
+        m_bounce[which] = nullptr;
+        return nullptr;
+    }
+    m_bounce_cap[which] = cap;
+    return m_bounce[which];
+}
+
+Status NvlCommunicator::exchange_launch(int kind, const void* in, size_t in_bytes, bool in_shared, void* out,
+                                        size_t out_bytes, bool out_shared, size_t len, DType in_dtype,
+                                        DType out_dtype, float scale, ReduceOp op, uint32_t root,
+                                        cudaStream_t stream) {
+    const void* in_use = in;
+    void* out_use = out;
+    bool copy_back = false;
+    if (in != nullptr && in_shared && !peer_addressable(in, in_bytes)) {
+        void* b = bounce(0, in_bytes);
+        if (b == nullptr)
+            return MEGRAY_CUDA_ERR;
+        MEGRAY_CHECK(check_cuda(cudaMemcpyAsync(b, in, in_bytes, cudaMemcpyDefault, stream)));
+        in_use = b;
+    }
+    if (out != nullptr && out_shared && !peer_addressable(out, out_bytes)) {
+        void* b = bounce(1, out_bytes);
+        if (b == nullptr)
+            return MEGRAY_CUDA_ERR;
+        out_use = b;
+        copy_back = true;
+    }
+    DirectArgs a;
+    memset(&a, 0, sizeof(a));
+    a.c = common_args();
+    a.kind = kind;
+    a.len = len;
+    a.scale = scale;
+    a.in_dtype = in_dtype;
+    a.out_dtype = out_dtype;
+    a.op = op;
+    a.root = static_cast<int>(root);
+    a.exchange = 1;
+    a.parity = m_xchg_parity;
+    m_xchg_parity ^= 1;
+    a.in_local = in_use;
+    a.out_local = out_use;
+    a.heap_bytes = m_heap.bytes();
+    const size_t ein = get_dtype_size(in_dtype);
+    // bytes that cross this rank's links, for sizing the grid
+    size_t work = len * ein;
+    const bool reducing = kind == mgk::coll::DIRECT_ALL_REDUCE || kind == mgk::coll::DIRECT_REDUCE_SCATTER ||
+                          kind == mgk::coll::DIRECT_REDUCE;
+    if (kind == mgk::coll::DIRECT_REDUCE_SCATTER || kind == mgk::coll::DIRECT_ALL_GATHER ||
+        kind == mgk::coll::DIRECT_ALL_TO_ALL || kind == mgk::coll::DIRECT_SCATTER)
+        work *= m_nranks;
+    const bool nvls = m_heap.multicast() != nullptr && work >= m_nvls_min_bytes &&
+                      (kind == mgk::coll::DIRECT_ALL_GATHER ||
+                       (reducing && mgk::coll::nvls_supports(in_dtype, out_dtype, op)));
+    a.mc_base = nvls ? m_heap.multicast() : nullptr;
+    const int max_ctas = 2 * m_max_ctas > kMaxCtas ? kMaxCtas : 2 * m_max_ctas;
+    int ctas = static_cast<int>(std::min<size_t>(std::max<size_t>(1, work / (32u << 10)), static_cast<size_t>(max_ctas)));
+    if (kind == mgk::coll::DIRECT_BROADCAST) {
+        // a CTA moves its share of every slice in chunks; small shares are not worth a CTA
+        const size_t slice = m_nranks > 1 ? (work + m_nranks - 2) / (m_nranks - 1) : work;
+        ctas = static_cast<int>(std::min<size_t>(std::max<size_t>(1, slice / (16u << 10)), static_cast<size_t>(max_ctas)));
+        a.chunk_bytes = m_bcast_chunk;
+        a.chunk_base = m_chunk_seq;
+        m_chunk_seq += mgk::coll::bcast_plan(work, static_cast<int>(m_nranks), ctas, a.chunk_bytes).chunks;
+    }
+    MEGRAY_CHECK(check_cuda(mgk::coll::launch_direct(a, ctas, 512, stream)));
+    after_launch(stream);
+    if (nvls)
+        m_stats.algo_nvls++;
+    m_stats.algo_direct++;
+    if (copy_back)
+        MEGRAY_CHECK(check_cuda(cudaMemcpyAsync(out, out_use, out_bytes, cudaMemcpyDefault, stream)));
     return MEGRAY_OK;
 }
 
@@ -378,6 +588,57 @@ Status NvlCommunicator::reduce_impl(ReduceKind kind, const void* in, void* out, 
 
     const char* inb = static_cast<const char*>(in);
     char* outb = static_cast<char*>(out);
+
+    // Small messages travel as flagged words: one launch, no barrier.
+    {
+        const int k = kind == ReduceKind::AllReduce ? mgk::coll::DIRECT_ALL_REDUCE
+                      : kind == ReduceKind::Reduce  ? mgk::coll::DIRECT_REDUCE
+                                                    : mgk::coll::DIRECT_REDUCE_SCATTER;
+        if (len * ein <= ll_limit(k) && len * ein > 0) {
+            mgk::coll::LLArgs l;
+            memset(&l, 0, sizeof(l));
+            l.in = in;
+            l.out = wants_out ? out : nullptr;
+            l.bytes = len * ein;
+            l.reduce = 1;
+            l.scale = scale;
+            l.in_dtype = in_dtype;
+            l.out_dtype = out_dtype;
+            l.op = op;
+            const uint32_t others = ((1u << n) - 1) & ~(1u << m_rank);
+            if (kind == ReduceKind::AllReduce) {
+                l.send_mask = l.recv_mask = others;
+                l.self = 1;
+            } else if (kind == ReduceKind::ReduceScatter) {
+                l.send_mask = l.recv_mask = others;
+                l.self = 1;
+                for (uint32_t q = 0; q < n; ++q)
+                    l.send_off[q] = static_cast<int64_t>(q * len * ein);
+            } else {
+                l.tokens = 1;
+                if (m_rank == root) {
+                    l.recv_mask = others;
+                    l.self = 1;
+                } else {
+                    l.send_mask = 1u << root;
+                }
+            }
+            return ll_launch(l, stream);
+        }
+    }
+
+    // Ranks of one process: single pass on the buffers as they are.
+    if (m_xchg && m_direct) {
+        if (kind == ReduceKind::AllReduce && (len * ein > m_oneshot_bytes || !m_oneshot_first))
+            return exchange_launch(mgk::coll::DIRECT_ALL_REDUCE, in, len * ein, true, out, len * eout, true, len,
+                                   in_dtype, out_dtype, scale, op, 0, stream);
+        if (kind == ReduceKind::ReduceScatter)
+            return exchange_launch(mgk::coll::DIRECT_REDUCE_SCATTER, in, len * ein * n, true, out, len * eout, false,
+                                   len, in_dtype, out_dtype, scale, op, 0, stream);
+        if (kind == ReduceKind::Reduce)
+            return exchange_launch(mgk::coll::DIRECT_REDUCE, in, len * ein, true, wants_out ? out : nullptr,
+                                   len * eout, true, len, in_dtype, out_dtype, scale, op, root, stream);
+    }
 
     // Buffers inside the symmetric heap (at the same offset on every rank, which is what
     // sym_alloc gives) need no staging: single-pass kernels read and write the peers directly.
@@ -512,6 +773,23 @@ Status NvlCommunicator::all_gather(const void* sendbuff, void* recvbuff, size_t 
     m_stats.bytes += bytes;
     if (bytes == 0)
         return MEGRAY_OK;
+    if (sendbuff == nullptr || recvbuff == nullptr)
+        return MEGRAY_INVALID_ARGUMENT;
+    if (bytes <= ll_limit(mgk::coll::DIRECT_ALL_GATHER)) {
+        mgk::coll::LLArgs l;
+        memset(&l, 0, sizeof(l));
+        l.in = sendbuff;
+        l.out = recvbuff;
+        l.bytes = bytes;
+        l.send_mask = l.recv_mask = ((1u << m_nranks) - 1) & ~(1u << m_rank);
+        l.self = 1;
+        for (uint32_t q = 0; q < m_nranks; ++q)
+            l.recv_off[q] = static_cast<int64_t>(q * bytes);
+        return ll_launch(l, stream);
+    }
+    if (m_xchg && m_direct)
+        return exchange_launch(mgk::coll::DIRECT_ALL_GATHER, sendbuff, bytes, false, recvbuff, bytes * m_nranks, true,
+                               bytes, MEGRAY_UINT8, MEGRAY_UINT8, 1.0f, MEGRAY_SUM, 0, stream);
     if (m_direct && m_nranks > 1 && bytes > m_oneshot_bytes / m_nranks && aligned_heap(recvbuff, bytes * m_nranks) &&
         bytes % 16 == 0)
         return direct_launch(mgk::coll::DIRECT_ALL_GATHER, sendbuff, recvbuff, bytes, MEGRAY_UINT8, MEGRAY_UINT8, 1.0f,
@@ -555,6 +833,23 @@ Status NvlCommunicator::all_to_all(const void* sendbuff, void* recvbuff, size_t 
     m_stats.bytes += bytes;
     if (bytes == 0)
         return MEGRAY_OK;
+    if (sendbuff == nullptr || recvbuff == nullptr)
+        return MEGRAY_INVALID_ARGUMENT;
+    if (bytes <= ll_limit(mgk::coll::DIRECT_ALL_TO_ALL)) {
+        mgk::coll::LLArgs l;
+        memset(&l, 0, sizeof(l));
+        l.in = sendbuff;
+        l.out = recvbuff;
+        l.bytes = bytes;
+        l.send_mask = l.recv_mask = ((1u << m_nranks) - 1) & ~(1u << m_rank);
+        l.self = 1;
+        for (uint32_t q = 0; q < m_nranks; ++q)
+            l.send_off[q] = l.recv_off[q] = static_cast<int64_t>(q * bytes);
+        return ll_launch(l, stream);
+    }
+    if (m_xchg && m_direct)
+        return exchange_launch(mgk::coll::DIRECT_ALL_TO_ALL, sendbuff, bytes * m_nranks, false, recvbuff,
+                               bytes * m_nranks, true, bytes, MEGRAY_UINT8, MEGRAY_UINT8, 1.0f, MEGRAY_SUM, 0, stream);
     if (m_direct && m_nranks > 1 && bytes > m_oneshot_bytes / m_nranks && aligned_heap(recvbuff, bytes * m_nranks) &&
         bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(sendbuff) & 15) == 0)
         return direct_launch(mgk::coll::DIRECT_ALL_TO_ALL, sendbuff, recvbuff, bytes, MEGRAY_UINT8, MEGRAY_UINT8, 1.0f,
@@ -599,6 +894,27 @@ Status NvlCommunicator::broadcast(const void* sendbuff, void* recvbuff, size_t l
     m_stats.bytes += bytes;
     if (bytes == 0)
         return MEGRAY_OK;
+    if (recvbuff == nullptr || (m_rank == root && sendbuff == nullptr))
+        return MEGRAY_INVALID_ARGUMENT;
+    if (bytes <= ll_limit(mgk::coll::DIRECT_BROADCAST)) {
+        mgk::coll::LLArgs l;
+        memset(&l, 0, sizeof(l));
+        l.in = m_rank == root ? sendbuff : nullptr;
+        l.out = recvbuff;
+        l.bytes = bytes;
+        l.tokens = 1;
+        if (m_rank == root) {
+            l.send_mask = ((1u << m_nranks) - 1) & ~(1u << m_rank);
+            l.self = sendbuff != recvbuff ? 1 : 0;
+        } else {
+            l.recv_mask = 1u << root;
+        }
+        return ll_launch(l, stream);
+    }
+    if (m_xchg && m_direct)
+        return exchange_launch(mgk::coll::DIRECT_BROADCAST, m_rank == root ? sendbuff : nullptr, bytes, false,
+                               recvbuff, bytes, true, bytes, MEGRAY_UINT8, MEGRAY_UINT8, 1.0f, MEGRAY_SUM, root,
+                               stream);
     const uint32_t n = m_nranks;
     const bool two_step = bytes > m_oneshot_bytes && n > 2;
     // one step: everyone loads the whole piece from the root's pub buffer
@@ -652,8 +968,29 @@ Status NvlCommunicator::gather(const void* sendbuff, void* recvbuff, size_t send
     m_stats.bytes += bytes;
     if (bytes == 0)
         return MEGRAY_OK;
-    if (m_rank == root && recvbuff == nullptr)
+    if (sendbuff == nullptr || (m_rank == root && recvbuff == nullptr))
         return MEGRAY_INVALID_ARGUMENT;
+    if (bytes <= ll_limit(mgk::coll::DIRECT_GATHER)) {
+        mgk::coll::LLArgs l;
+        memset(&l, 0, sizeof(l));
+        l.in = sendbuff;
+        l.out = m_rank == root ? recvbuff : nullptr;
+        l.bytes = bytes;
+        l.tokens = 1;
+        if (m_rank == root) {
+            l.recv_mask = ((1u << m_nranks) - 1) & ~(1u << m_rank);
+            l.self = 1;
+            for (uint32_t q = 0; q < m_nranks; ++q)
+                l.recv_off[q] = static_cast<int64_t>(q * bytes);
+        } else {
+            l.send_mask = 1u << root;
+        }
+        return ll_launch(l, stream);
+    }
+    if (m_xchg && m_direct)
+        return exchange_launch(mgk::coll::DIRECT_GATHER, sendbuff, bytes, false, m_rank == root ? recvbuff : nullptr,
+                               bytes * m_nranks, true, bytes, MEGRAY_UINT8, MEGRAY_UINT8, 1.0f, MEGRAY_SUM, root,
+                               stream);
     const size_t cap = round_down(m_ws_bytes - 16, 16);
     for (size_t off = 0; off < bytes; off += cap) {
         const size_t piece = std::min(cap, bytes - off);
@@ -692,8 +1029,29 @@ Status NvlCommunicator::scatter(const void* sendbuff, void* recvbuff, size_t rec
     m_stats.bytes += bytes;
     if (bytes == 0)
         return MEGRAY_OK;
-    if (m_rank == root && sendbuff == nullptr)
+    if (recvbuff == nullptr || (m_rank == root && sendbuff == nullptr))
         return MEGRAY_INVALID_ARGUMENT;
+    if (bytes <= ll_limit(mgk::coll::DIRECT_SCATTER)) {
+        mgk::coll::LLArgs l;
+        memset(&l, 0, sizeof(l));
+        l.in = m_rank == root ? sendbuff : nullptr;
+        l.out = recvbuff;
+        l.bytes = bytes;
+        l.tokens = 1;
+        if (m_rank == root) {
+            l.send_mask = ((1u << m_nranks) - 1) & ~(1u << m_rank);
+            l.self = 1;
+            for (uint32_t q = 0; q < m_nranks; ++q)
+                l.send_off[q] = static_cast<int64_t>(q * bytes);
+        } else {
+            l.recv_mask = 1u << root;
+        }
+        return ll_launch(l, stream);
+    }
+    if (m_xchg && m_direct)
+        return exchange_launch(mgk::coll::DIRECT_SCATTER, m_rank == root ? sendbuff : nullptr, bytes * m_nranks, false,
+                               recvbuff, bytes, true, bytes, MEGRAY_UINT8, MEGRAY_UINT8, 1.0f, MEGRAY_SUM, root,
+                               stream);
     const size_t cap = round_down(m_ws_bytes / m_nranks - 16, 16);
     for (size_t off = 0; off < bytes; off += cap) {
         const size_t piece = std::min(cap, bytes - off);
@@ -826,6 +1184,8 @@ Status NvlCommunicator::sym_free(void* ptr) {
         m_allocs.pop_back();
         const size_t at = round_up(prev_top, 1024);
         m_user_top = prev_top;
+        // counter blocks in the released range start from zero for their next owner
+        m_fused_calls.erase(m_fused_calls.lower_bound(at), m_fused_calls.end());
         if (at == off)
             return MEGRAY_OK;
         if (at < off)
@@ -893,8 +1253,11 @@ void NvlCommunicator::drop_registration(Registration& r) {
 }
 
 Status NvlCommunicator::register_buffer(void* ptr, size_t bytes) {
-    if (!m_ready || ptr == nullptr || bytes == 0)
-        return MEGRAY_INVALID_ARGUMENT;
+    if (!m_ready)
+        return MEGRAY_INVALID_USAGE;
+    // A bad argument on one rank must not leave the others waiting in the exchange below: it is
+    // reported to them as "this rank could not export its buffer", and every rank falls back.
+    const bool bad_arg = ptr == nullptr || bytes == 0;
     const drv::Api* api = drv::api();
     std::vector<RegInfo> all(m_nranks);
     RegInfo mine;
@@ -906,7 +1269,7 @@ Status NvlCommunicator::register_buffer(void* ptr, size_t bytes) {
     mine.ok = 1;
     CUdeviceptr alloc_base = 0;
     size_t alloc_size = 0;
-    if (api == nullptr ||
+    if (bad_arg || api == nullptr ||
         api->MemGetAddressRange(&alloc_base, &alloc_size, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS ||
         reinterpret_cast<CUdeviceptr>(ptr) + bytes > alloc_base + alloc_size) {
         mine.ok = 0;  // not one device allocation
@@ -966,7 +1329,7 @@ Status NvlCommunicator::register_buffer(void* ptr, size_t bytes) {
     if (!usable) {
         drop_registration(r);
         MEGRAY_INFO("register_buffer: %p (%zu bytes) stays on the staged paths", ptr, bytes);
-        return MEGRAY_NOT_IMPLEMENTED;
+        return bad_arg ? MEGRAY_INVALID_ARGUMENT : MEGRAY_NOT_IMPLEMENTED;
     }
     m_regs.push_back(std::move(r));
     return MEGRAY_OK;

@@ -13,6 +13,7 @@
 #pragma once
 #include <cuda_runtime_api.h>
 
+#include <map>
 #include <memory>
 #include <vector>
 
@@ -71,6 +72,9 @@ public:
                              DType out_dtype, float scale, ReduceOp op,
                              std::shared_ptr<Context> ctx) override;
     Status stream_barrier(std::shared_ptr<Context> ctx) override;
+    Status fused_begin(void* stream) override;
+    void fused_end(void* stream) override;
+    uint32_t fused_call_count(const void* flags) override;
     uint32_t reserve_epochs(uint32_t count) override;
     size_t fused_flag_offset() override { return kFusedFlagOff; }
     int* status_word() override { return m_status_dev; }
@@ -78,9 +82,10 @@ public:
     void set_device_timeout_ms(int64_t ms) override { m_timeout_ns = static_cast<uint64_t>(ms) * 1000000ull; }
 
     // heap layout (byte offsets, identical on every rank)
-    static constexpr size_t kFlagOff = 0;               // collectives: kMaxCtas x kMaxRanks words
-    static constexpr size_t kFusedFlagOff = 16 * 1024;  // fused kernels: 48 KiB of flags/counters
-    static constexpr size_t kWorkspaceOff = 64 * 1024;  // two staging workspaces follow
+    static constexpr size_t kFlagOff = mgk::coll::kBarrierFlagOff;  // collectives: first 16 KiB of the pad
+    static constexpr size_t kFusedFlagOff = 16 * 1024;              // fused kernels: 48 KiB of flags/counters
+    static constexpr size_t kLLOff = mgk::coll::kPadBytes;          // small-message slots (32 MiB)
+    static constexpr size_t kWorkspaceOff = mgk::coll::kPadBytes + mgk::coll::kLLRegionBytes;  // two staging workspaces
 
 protected:
     Status _send(const void* sendbuff, size_t size, uint32_t rank,
@@ -90,10 +95,11 @@ protected:
 private:
     enum class ReduceKind { AllReduce, Reduce, ReduceScatter };
     Status begin(const std::shared_ptr<Context>& ctx, cudaStream_t* stream);
+    Status begin_on(cudaStream_t stream);  // state checks + cross-stream ordering
     Status reduce_impl(ReduceKind kind, const void* in, void* out, size_t len, DType in_dtype,
                        DType out_dtype, float scale, ReduceOp op, uint32_t root,
                        cudaStream_t stream);
-    mgk::coll::CommonArgs common_args();
+    mgk::coll::CommonArgs common_args(uint32_t epochs = 2);
     size_t workspace_off();  // offset of the workspace this launch uses; flips the parity
     void after_launch(cudaStream_t stream);
     int pick_ctas(size_t bytes) const;
@@ -112,6 +118,18 @@ private:
     void drop_registration(Registration& r);
     Status direct_launch(int kind, const void* in, void* out, size_t len, DType in_dtype, DType out_dtype,
                          float scale, ReduceOp op, cudaStream_t stream);
+    // Single-pass kernel on this call's buffers as they are (ranks of one process: addresses travel
+    // through the pads).  `in_bytes` / `out_bytes`: what this rank reads / writes of its own
+    // buffers; `in_shared` / `out_shared`: the peers' kernels touch that buffer too, so it must be
+    // memory they can address (otherwise it is replaced by a bounce buffer for this call).
+    Status exchange_launch(int kind, const void* in, size_t in_bytes, bool in_shared, void* out, size_t out_bytes,
+                           bool out_shared, size_t len, DType in_dtype, DType out_dtype, float scale, ReduceOp op,
+                           uint32_t root, cudaStream_t stream);
+    // Small-message kernel; `a` comes filled with the operation's send / receive pattern.
+    Status ll_launch(mgk::coll::LLArgs& a, cudaStream_t stream);
+    bool peer_addressable(const void* p, size_t bytes);
+    void* bounce(int which, size_t bytes);
+    size_t ll_limit(int kind) const { return m_ll_bytes[kind]; }
     Status check_cuda(cudaError_t e);
 
     SymmetricHeap m_heap;
@@ -123,6 +141,7 @@ private:
     size_t m_user_top = 0;   // bump pointer
     std::vector<size_t> m_allocs;
     std::vector<Registration> m_regs;
+    std::map<size_t, uint32_t> m_fused_calls;  // heap offset of a fused counter block -> calls so far
     uint32_t m_epoch = 0;
     int m_parity = 0;
     uint64_t m_timeout_ns;
@@ -131,6 +150,22 @@ private:
     size_t m_nvls_min_bytes = 0;
     size_t m_cta_bytes = 128 * 1024;  // message bytes per CTA when sizing a collective's grid
     bool m_direct = true;
+    // Ranks that are threads of one process, with peer access enabled between all their devices:
+    // every collective above the small-message limit runs the single-pass kernels on the user's
+    // buffers (MEGRAY_EXCHANGE=0 turns it off).
+    bool m_xchg = false;
+    int m_xchg_parity = 0;
+    uint32_t m_ll_seq = 0;      // small-message calls so far
+    int m_ll_parity = 0;
+    // all_reduce between the small-message limit and the one-shot limit: one-shot through the
+    // staging slots (one barrier) rather than the single-pass kernel (two)
+    bool m_oneshot_first = true;
+    uint32_t m_chunk_seq = 0;   // chunks announced by pipelined broadcasts so far
+    uint32_t m_bcast_chunk = 128 * 1024;
+    // largest payload per (source, destination) pair that goes as flagged words, per DirectKind
+    size_t m_ll_bytes[8] = {};
+    void* m_bounce[2] = {nullptr, nullptr};
+    size_t m_bounce_cap[2] = {0, 0};
     // all_gather / all_to_all of at most this many bytes per rank (per peer for all_to_all) take
     // the push form (stores into the peers' buffers before the barrier instead of loads from
     // them after it).  Measured: on 2 GPUs 9.0 vs 9.7-10.1 us at 1 KiB and 10.1-10.4 vs

@@ -253,6 +253,13 @@ Status SymmetricHeap::create(Client* client, uint32_t nranks, uint32_t rank, siz
         all_mc = all_mc && info[q].multicast_ok != 0;
     }
     m_bytes = bytes;
+    m_same_process = true;
+    m_devices.assign(nranks, -1);
+    for (uint32_t q = 0; q < nranks; ++q) {
+        m_devices[q] = info[q].device;
+        if (info[q].pid != me.pid)
+            m_same_process = false;
+    }
 
     CUmemGenericAllocationHandle mine = 0;
     DRV_CHECK(m_api->MemCreate(&mine, bytes, &prop, 0));

@@ -40,6 +40,11 @@ public:
      *  reduces over all ranks.  nullptr when multicast is unavailable. */
     char* multicast() const { return m_mc_base; }
     int device() const { return m_device; }
+    /** True when every rank of the group is a thread of this process (they then share one
+     *  address space: a peer's device pointer means the same thing here). */
+    bool same_process() const { return m_same_process; }
+    /** CUDA device ordinal of rank q (meaningful for ranks of this process). */
+    int peer_device(uint32_t q) const { return q < m_devices.size() ? m_devices[q] : -1; }
 
 private:
     struct PeerInfo {
@@ -59,6 +64,8 @@ private:
     const drv::Api* m_api = nullptr;
     uint32_t m_nranks = 0, m_rank = 0;
     int m_device = -1;
+    bool m_same_process = false;
+    std::vector<int> m_devices;
     size_t m_bytes = 0;
     CUdeviceptr m_va = 0;
     std::vector<char*> m_base;

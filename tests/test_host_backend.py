@@ -308,3 +308,36 @@ def test_ranks_as_processes_share_a_posix_shm_region():
     for total, ag in res:
         assert total == 6.0
         assert ag == [0, 0, 0, 1, 1, 1, 2, 2, 2]
+
+
+def test_python_ops_refuse_buffers_that_break_the_length_contract():
+    """The native calls trust the length contracts of include/megray/communicator.h; the Python
+    layer checks them (and the dtypes) first, so a short buffer raises instead of being overrun."""
+    import pytest
+
+    port = mr.get_free_port()
+    server = mr.Server(1, port)
+    comm = mr.Communicator(1, 0, "host").init("127.0.0.1", port)
+    a4, a8 = np.zeros(4, np.float32), np.zeros(8, np.float32)
+    i4 = np.zeros(4, np.int32)
+    with pytest.raises(ValueError):
+        comm.all_reduce(a8, a4)
+    with pytest.raises(ValueError):
+        comm.all_reduce(a4, i4)
+    with pytest.raises(ValueError):
+        comm.all_gather(a4, a8)          # nranks == 1: recv must hold exactly send.numel
+    with pytest.raises(ValueError):
+        comm.reduce_scatter(a8, a4)
+    with pytest.raises(ValueError):
+        comm.all_to_all(a4, a8)
+    with pytest.raises(ValueError):
+        comm.broadcast(a8, a4, 0)
+    with pytest.raises(ValueError):
+        comm.gather(a4, a8, 0)
+    with pytest.raises(ValueError):
+        comm.scatter(a8, a4, 0)
+    with pytest.raises(ValueError):
+        comm.reduce(a4, a8, 0)
+    comm.all_reduce(a4, a4.copy())       # a call that keeps the contract still works
+    comm.close()
+    server.close()

@@ -86,3 +86,13 @@ def test_single_pass_collectives_through_nvswitch_multimem():
 def test_device_wait_limit_reports_timeout_and_keeps_the_gpu_usable():
     out = torchrun("timeout.py")
     assert out.count("RANK_OK") == NPROC, out[-3000:]
+
+
+def test_fused_call_wait_limit_reports_timeout_and_keeps_the_gpu_usable():
+    out = torchrun("fused_timeout.py", nproc=2, env={"MEGRAY_HEAP_MB": "512"})
+    assert out.count("RANK_OK") == 2, out[-3000:]
+
+
+def test_fused_reduce_scatter_on_a_recreated_communicator():
+    out = torchrun("recreate.py", env={"MEGRAY_HEAP_MB": "512"})
+    assert out.count("RANK_OK") == NPROC, out[-3000:]

@@ -62,11 +62,15 @@ def test_no_alloc_dispatch_matches_the_regular_entry_point_twice():
         dst_b = torch.zeros(capacity, H, dtype=torch.bfloat16, device="cuda")
         pos_b = torch.empty(T, 2, dtype=torch.int32, device="cuda")
         peers_b = (C.c_void_p * 1)(dst_b.data_ptr())
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]  # also sees a cudaMalloc made inside the library
         rc = noalloc(src.data_ptr(), T, H, idx.data_ptr(), wp, send_base.data_ptr(), E, pos_b.data_ptr(), peers_b, 1,
                      E, capacity, st)
         assert rc == 0
         assert torch.cuda.memory_allocated() == before
+        if attempt == 1:  # the first call on a device may load the kernel's module; later ones change nothing
+            assert torch.cuda.mem_get_info()[0] >= free_before
         torch.cuda.synchronize()
         ia, ib = idx.flatten().long(), idx.flatten().long()
         pa, pb = pos_a.flatten().long(), pos_b.flatten().long()
@@ -103,3 +107,44 @@ def test_no_alloc_dispatch_refuses_more_experts_than_its_array_holds():
     assert rc == 6
     torch.cuda.synchronize()
     assert float(dst.abs().sum()) == 0.0  # nothing was launched
+
+
+def test_no_alloc_dispatch_drops_an_expert_id_nobody_owns():
+    """A routing table with one expert id outside [0, experts): that (token, slot) is dropped
+    (pos -1), every other row lands as usual, no other row of the buffer is touched.  The same
+    table through the regular entry point behaves alike."""
+    lib, st, src, idx, w, counts, send_base, capacity, T, H, E = _setup(tokens=200)
+    noalloc = _declare(lib)
+    bad = idx.clone()
+    bad[17, 1] = E + 3          # beyond the experts of the call, inside the 256-entry array
+    bad[42, 0] = -5
+    for which in ("noalloc", "regular"):
+        dst = torch.zeros(capacity + 128, H, dtype=torch.bfloat16, device="cuda")
+        pos = torch.full((T, 2), -7, dtype=torch.int32, device="cuda")
+        peers = (C.c_void_p * 1)(dst.data_ptr())
+        if which == "noalloc":
+            rc = noalloc(src.data_ptr(), T, H, bad.data_ptr(), None, send_base.data_ptr(), E, pos.data_ptr(), peers,
+                         1, E, capacity, st)
+        else:
+            cursor = torch.zeros(E, dtype=torch.int32, device="cuda")
+            rc = lib.megray_moe_dispatch(src.data_ptr(), T, H, bad.data_ptr(), None, send_base.data_ptr(),
+                                         cursor.data_ptr(), None, pos.data_ptr(), peers, 1, E, capacity, st)
+        assert rc == 0
+        torch.cuda.synchronize()
+        p = pos.flatten().long()
+        valid = ((bad.flatten() >= 0) & (bad.flatten() < E))
+        assert int((~valid).sum()) == 2
+        assert bool((p[~valid] == -1).all())
+        assert bool((p[valid] >= 0).all()) and bool((p[valid] < capacity).all())
+        assert p[valid].unique().numel() == int(valid.sum())          # every kept pair has a row of its own
+        want = src.float().repeat_interleave(2, 0)[valid]
+        assert torch.equal(dst[p[valid]].float(), want)
+        mask = torch.ones(capacity + 128, dtype=torch.bool, device="cuda")
+        mask[p[valid]] = False
+        assert float(dst[mask].abs().sum()) == 0.0                    # nothing else was written
+    # more experts than the given owners can hold: refused
+    pos = torch.empty(T, 2, dtype=torch.int32, device="cuda")
+    dst = torch.zeros(capacity, H, dtype=torch.bfloat16, device="cuda")
+    peers = (C.c_void_p * 1)(dst.data_ptr())
+    assert noalloc(src.data_ptr(), T, H, idx.data_ptr(), None, send_base.data_ptr(), E, pos.data_ptr(), peers, 1,
+                   E - 1, capacity, st) == 6
