@@ -5,8 +5,10 @@ kernel on a communication stream while backward continues.
 
     torchrun --nproc-per-node N bench/dp_resnet50.py [--backend nvl|nccl] [--no-overlap]
 
-`--backend nccl` runs the same harness over the NCCL wrapper (the baseline path).  Device-timed
-with CUDA events, max over ranks, rank 0 prints one JSON line.
+`--backend nccl` runs the same harness over this library's NCCL wrapper; `--backend reference`
+over the unmodified reference library (baseline/_ref, its NCCL backend: all_reduce then a separate
+scale; the reference has no bf16, so 2-byte gradients are summed as float16).  Device-timed with
+CUDA events, max over ranks, rank 0 prints one JSON line.
 """
 import argparse
 import json
@@ -21,6 +23,50 @@ import torch  # noqa: E402
 import megray_b200 as mr  # noqa: E402
 from megray_b200.models.resnet import resnet50, synthetic_batch  # noqa: E402
 from megray_b200.parallel.data_parallel import GradBucketer  # noqa: E402
+
+
+class ReferenceComm:
+    """The few calls the harness needs, served by the reference library's public interface."""
+
+    def __init__(self, world, rank, port):
+        import ctypes as C
+
+        path = os.path.join(ROOT, "baseline", "_ref", "libmegray_ref.so")
+        if not os.path.exists(path):
+            raise SystemExit("baseline/_ref/libmegray_ref.so is missing: run baseline/build_ref.py first")
+        os.environ.setdefault("NCCL_LAUNCH_MODE", "PARALLEL")
+        self._C = C
+        self.ref = C.CDLL(path, mode=C.RTLD_LOCAL)
+        self.ref.ref_comm_new.restype = C.c_void_p
+        self.ref.ref_comm_init.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
+        self.ref.ref_all_reduce.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_void_p]
+        self.ref.ref_broadcast.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_uint, C.c_void_p]
+        self.ref.ref_comm_delete.argtypes = [C.c_void_p]
+        if rank == 0:
+            assert self.ref.ref_create_server(world, port) == 0
+        self.h = self.ref.ref_comm_new(world, rank)
+        assert self.h and self.ref.ref_comm_init(self.h, b"127.0.0.1", port) == 0
+        self.nranks, self.rank, self.backend = world, rank, -1
+
+    def _stream(self):
+        return self._C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def all_reduce(self, send, recv, op="sum"):
+        code = {"sum": 0, "max": 1, "min": 2}[op]
+        if send.dtype == torch.bfloat16:  # no bf16 in the reference: travel and add as float16
+            tmp = send.to(torch.float16)
+            assert self.ref.ref_all_reduce(self.h, tmp.data_ptr(), tmp.data_ptr(), tmp.numel(), 6, code, self._stream()) == 0
+            recv.copy_(tmp)
+            return
+        dt = {torch.float32: 7, torch.float16: 6}[send.dtype]
+        assert self.ref.ref_all_reduce(self.h, send.data_ptr(), recv.data_ptr(), send.numel(), dt, code, self._stream()) == 0
+
+    def broadcast(self, send, recv, root):
+        nbytes = recv.numel() * recv.element_size()
+        assert self.ref.ref_broadcast(self.h, send.data_ptr(), recv.data_ptr(), nbytes, 1, root, self._stream()) == 0  # uint8
+
+    def close(self):
+        self.ref.ref_comm_delete(self.h)
 
 
 def main():
@@ -39,9 +85,12 @@ def main():
     comm = server = None
     if world > 1:
         port = int(os.environ.get("MASTER_PORT", "29533")) + 3
-        if rank == 0:
-            server = mr.Server(world, port)
-        comm = mr.Communicator(world, rank, a.backend).init("127.0.0.1", port)
+        if a.backend == "reference":
+            comm = ReferenceComm(world, rank, port)
+        else:
+            if rank == 0:
+                server = mr.Server(world, port)
+            comm = mr.Communicator(world, rank, a.backend).init("127.0.0.1", port)
     model = resnet50()
     bucketer = GradBucketer(model, comm, a.bucket_mb, overlap=not a.no_overlap)
     bucketer.broadcast_parameters(0)

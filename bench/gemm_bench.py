@@ -123,7 +123,7 @@ def main():
         cands = [(lambda v=v: fn(v)) for v in variants]
         splits = [int(x) for x in a.split_k.split(",")] if a.split_k and layout in ("nt", "nn", "tn", "tt") else []
         for sk in splits:
-            ws = torch.empty(sk * M, N, device=dev, dtype=torch.bfloat16)
+            ws = torch.empty(sk * M, N, device=dev, dtype=torch.float32)
             cands.append(lambda sk=sk, ws=ws: gemm_split_k(A, B, out, sk, ws, a_mn=a_mn, b_mn=b_mn))
         if not a.no_cublas:
             Af = A.t() if a_mn else A

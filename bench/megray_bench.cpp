@@ -60,6 +60,7 @@ struct BenchOptions {
     bool heap = false;  // NVL backend: buffers from the symmetric heap (zero-copy / NVSwitch kernels)
     bool reg = false;   // NVL backend: cudaMalloc buffers registered with the communicator (zero-copy)
     bool host = false;  // shm backend with CPU ranks: host buffers, wall-clock timing, no GPU needed
+    bool phases = false;  // NVL backend: report where the time of the last call of each case went
 };
 
 const char* kAllFuncs[] = {"send_recv", "scatter", "gather", "all_to_all", "all_gather",
@@ -491,15 +492,29 @@ void run_backend(const BenchOptions& o, const std::string& bname, Backend backen
                                 else if (st1.algo_copy > st0.algo_copy) algo = "staged-copy";
                                 else if (backend == MEGRAY_NCCL) algo = "nccl";
 #endif
+                                std::string phases;
+#ifndef MEGRAY_BENCH_REFERENCE
+                                if (o.phases && backend == MEGRAY_NVL) {
+                                    // rank 0's last kernel: microseconds between its phase boundaries
+                                    uint64_t st[8];
+                                    const int ns = as_nvl(comm.get())->read_phase_stamps(st, 8);
+                                    for (int i = 1; i < ns; ++i) {
+                                        char buf[32];
+                                        snprintf(buf, sizeof(buf), "%s%.2f", i > 1 ? "," : "", (st[i] - st[i - 1]) / 1000.0);
+                                        phases += buf;
+                                    }
+                                }
+#endif
                                 if (o.json)
                                     printf("{\"backend\":\"%s\",\"op\":\"%s\",\"dtype\":\"%s\",\"reduce\":\"%s\",\"nranks\":%d,"
                                            "\"bytes\":%zu,\"time_us\":%.3f,\"speed_gbs\":%.3f,\"busbw_gbs\":%.3f,\"algo\":\"%s\","
-                                           "\"checked\":%s,\"ok\":%s}\n",
+                                           "\"phases_us\":[%s],\"checked\":%s,\"ok\":%s}\n",
                                            bname.c_str(), func.c_str(), dt.name, opname.c_str(), n, size, t_us, speed, busbw,
-                                           algo, o.check ? "true" : "false", total_bad == 0 ? "true" : "false");
+                                           algo, phases.c_str(), o.check ? "true" : "false", total_bad == 0 ? "true" : "false");
                                 else
-                                    printf("%-14s %-8s %-4s %12zu %12.2f %12.3f %12.3f  %-13s%s\n", func.c_str(), dt.name,
-                                           opname.c_str(), size, t_us, speed, busbw, algo, total_bad == 0 ? "" : "  FAILED");
+                                    printf("%-14s %-8s %-4s %12zu %12.2f %12.3f %12.3f  %-13s%s%s%s\n", func.c_str(), dt.name,
+                                           opname.c_str(), size, t_us, speed, busbw, algo, phases.empty() ? "" : "  phases(us) ",
+                                           phases.c_str(), total_bad == 0 ? "" : "  FAILED");
                                 fflush(stdout);
                             }
                             sh.bar.wait();
@@ -537,6 +552,7 @@ void usage() {
            "             [-t dtype,...|all] [-o sum,max,min|all] [-w warmup] [-i iters] [-j] [-c (check results)]\n"
            "             [-H (NVL: symmetric-heap buffers)] [-R (NVL: register the cudaMalloc buffers)]\n"
            "             [-C (shm backend with CPU ranks: host buffers, wall-clock timing; automatic without GPUs)]\n"
+           "             [-p (NVL: time between the phase boundaries of rank 0's last kernel of each case)]\n"
            "             [-I master_ip] [-P port] [-n nodes] [-r node_rank]\n");
 }
 
@@ -549,7 +565,7 @@ int main(int argc, char** argv) {
     std::string funcs = "all";
     std::string dtypes = "float32", ops = "sum";
     int c;
-    while ((c = getopt(argc, argv, "d:I:P:n:r:e:f:s:w:i:t:o:jcHRCh")) != -1) {
+    while ((c = getopt(argc, argv, "d:I:P:n:r:e:f:s:w:i:t:o:jcHRCph")) != -1) {
         switch (c) {
             case 'd': o.devices = atoi(optarg); break;
             case 'I': o.master_ip = optarg; break;
@@ -568,6 +584,7 @@ int main(int argc, char** argv) {
             case 'H': o.heap = true; break;
             case 'R': o.reg = true; break;
             case 'C': o.host = true; break;
+            case 'p': o.phases = true; setenv("MEGRAY_PHASES", "1", 1); break;
             default: usage(); return c == 'h' ? 0 : 1;
         }
     }

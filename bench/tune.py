@@ -59,18 +59,20 @@ def main():
     table = {"devices": a.devices, "measured": {}}
 
     # flagged words against what would run otherwise (one-shot / single pass / staged)
-    small = [1 << k for k in range(10, 17)]  # 1 KiB .. 64 KiB per source / destination pair
-    with_ll = run(a.devices, KINDS, small, {"MEGRAY_LL_BYTES": str(64 << 10)})
-    without = run(a.devices, KINDS, small, {"MEGRAY_LL_BYTES": "0"})
+    small = [1 << k for k in range(10, 21)]  # 1 KiB .. 1 MiB per source / destination pair
+    with_ll = run(a.devices, KINDS, small, {"MEGRAY_LL_BYTES": str(1 << 20), "MEGRAY_TUNE_DEFAULT": "0"})
+    without = run(a.devices, KINDS, small, {"MEGRAY_LL_BYTES": "0", "MEGRAY_TUNE_DEFAULT": "0"})
     for k in KINDS:
-        table[f"ll_{k}"] = crossover(small, with_ll, without, k)
+        table[f"ll_{k}"] = crossover(small, with_ll, without, k, margin=1.02)
         table["measured"][f"us_ll_vs_other_{k}"] = {str(s): [with_ll.get((k, s), [None])[0], without.get((k, s), [None])[0]]
                                         for s in small}
 
     # all_reduce: one-shot (one barrier, staging slots) against single pass (two barriers, no staging)
     mid = [1 << k for k in range(15, 23)]  # 32 KiB .. 4 MiB
-    one = run(a.devices, ["all_reduce"], mid, {"MEGRAY_LL_BYTES": "0", "MEGRAY_ONESHOT_BYTES": str(1 << 30)})
-    two = run(a.devices, ["all_reduce"], mid, {"MEGRAY_LL_BYTES": "0", "MEGRAY_ONESHOT_BYTES": "0"})
+    one = run(a.devices, ["all_reduce"], mid, {"MEGRAY_LL_BYTES": "0", "MEGRAY_ONESHOT_BYTES": str(1 << 30),
+                                               "MEGRAY_TUNE_DEFAULT": "0"})
+    two = run(a.devices, ["all_reduce"], mid, {"MEGRAY_LL_BYTES": "0", "MEGRAY_ONESHOT_BYTES": "0",
+                                               "MEGRAY_TUNE_DEFAULT": "0"})
     table["oneshot_bytes"] = crossover(mid, one, two, "all_reduce")
     table["measured"]["us_oneshot_vs_single_pass"] = {str(s): [one.get(("all_reduce", s), [None])[0], two.get(("all_reduce", s), [None])[0]]
                                     for s in mid}

@@ -109,6 +109,11 @@ int megray_nvl_all_reduce_scaled(void* comm, const void* send, void* recv, size_
                                  int out_dtype, float scale, int op, void* stream);
 int megray_nvl_stream_barrier(void* comm, void* stream);
 void megray_nvl_set_device_timeout_ms(void* comm, int64_t ms);
+/* verifies the guard zones around the staging workspaces; MEGRAY_OUT_OF_BOUNDS (14) if one was written */
+int megray_nvl_check_canaries(void* comm);
+/* send / recv: postpone the caller's stream's wait for the transfer until megray_nvl_p2p_join */
+void megray_nvl_set_p2p_async(void* comm, int on);
+int megray_nvl_p2p_join(void* comm, void* stream);
 
 /* ---- host arithmetic (the oracle) and stand-alone device reduction ----------------------- */
 int megray_cpu_reduce_n(const void* const* in, int n_in, void* out, size_t len, int dtype, int op);
@@ -149,6 +154,10 @@ int megray_moe_route_bwd(const int* idx, const float* w, const float* dw, int to
 int megray_moe_plan(const int* counts_all, int nranks, int rank, int experts, int capacity_rows,
                     int* send_base, int* seg_begin, int* seg_end, int* seg_rows, int* block_group,
                     int* total, void* stream);
+/* The plan with the exchange of the counts inside the launch (NVL communicators): `counts` are this
+ * rank's per-expert counts; no separate all_gather is needed. */
+int megray_moe_plan_exchange(void* comm, const int* counts, int experts, int capacity_rows, int* send_base,
+                             int* seg_begin, int* seg_end, int* seg_rows, int* block_group, int* total, void* stream);
 int megray_moe_zero_pads(void* buf, int row_elems, const int* seg_begin, const int* seg_rows,
                          const int* seg_end, int local_experts, void* stream);
 /* peer_bufs: array of `nranks` device addresses (host array), one buffer per owner rank */

@@ -62,6 +62,29 @@ public:
                                      DType in_dtype, DType out_dtype, float scale, ReduceOp op,
                                      std::shared_ptr<Context> ctx) = 0;
 
+    /**
+     * send / recv run on a stream of the communicator's own, ordered after the work already on the
+     * caller's stream.  By default the caller's stream then waits for the transfer (the calls
+     * complete in stream order, as the interface says).  With set_p2p_async(true) that wait is
+     * postponed to p2p_join(ctx): whatever the caller enqueues in between, native collectives
+     * included, overlaps the transfer, and must not touch the buffers in flight.
+     */
+    virtual void set_p2p_async(bool on) = 0;
+    /** Makes ctx's stream wait for every send / recv issued so far (no-op when none is pending). */
+    virtual Status p2p_join(std::shared_ptr<Context> ctx) = 0;
+
+    /** With MEGRAY_PHASES=1 in the environment the collective kernels stamp %globaltimer (ns) at
+     *  their phase boundaries (block 0 of this rank).  Synchronises the device and copies the
+     *  stamps of the most recent kernel into `out` (at most `max`); returns how many there are.
+     *  Single-pass kernels: start, first barrier passed, data moved, last barrier passed.
+     *  Flagged-word kernel: start, all sent, all received.  Staged reduce kernel: start, pushed,
+     *  barrier, reduced, barrier, gathered. */
+    virtual int read_phase_stamps(uint64_t* out, int max) = 0;
+
+    /** Synchronises the device and verifies the guard zones around the staging workspaces (filled
+     *  with a pattern at init; no kernel may write there).  MEGRAY_OUT_OF_BOUNDS if one was touched. */
+    virtual Status check_canaries() = 0;
+
     /** Barrier on the stream: later work of every rank starts after earlier work of all ranks. */
     virtual Status stream_barrier(std::shared_ptr<Context> ctx) = 0;
 
@@ -77,6 +100,11 @@ public:
      *  starts again from 1 after sym_free of that memory or for a new communicator, which is
      *  when the counters themselves are zero again. */
     virtual uint32_t fused_call_count(const void* flags) = 0;
+
+    /** Reserves the small-message slots of the next call for a kernel of another module (every
+     *  rank must do so in the same order as its other calls): `seq` is the flag value its words
+     *  carry, the slot of source rank q starts at heap + slot_off + q * slot_stride. */
+    virtual void ll_ticket(uint32_t* seq, size_t* slot_off, size_t* slot_stride) = 0;
 
     /** Next flag epoch for kernels of other modules that synchronise through the pad
      *  (`count` consecutive values are reserved). */

@@ -25,7 +25,8 @@ typedef enum {
     MEGRAY_RCCL_ERR = 11,
     MEGRAY_TIMEOUT = 12,  /* a bounded wait (host or device) ran out */
     MEGRAY_ABORTED = 13,  /* the communicator was aborted */
-    MEGRAY_STATUS_COUNT = 14,
+    MEGRAY_OUT_OF_BOUNDS = 14, /* a bounds-checked build caught an access outside the call's buffers */
+    MEGRAY_STATUS_COUNT = 15,
 } Status;
 
 typedef enum {

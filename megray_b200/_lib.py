@@ -109,6 +109,9 @@ def _declare(lib) -> None:
     d("megray_nvl_all_reduce_scaled", i32, vp, vp, vp, sz, i32, i32, C.c_float, i32, vp)
     d("megray_nvl_stream_barrier", i32, vp, vp)
     d("megray_nvl_set_device_timeout_ms", None, vp, i64)
+    d("megray_nvl_check_canaries", i32, vp)
+    d("megray_nvl_set_p2p_async", None, vp, i32)
+    d("megray_nvl_p2p_join", i32, vp, vp)
     d("megray_cpu_reduce_n", i32, P(vp), i32, vp, sz, i32, i32)
     d("megray_cpu_reduce_scale_cast", i32, P(vp), i32, i32, vp, i32, sz, i32, C.c_double)
     d("megray_oracle_ring_all_reduce", i32, P(vp), P(vp), i32, sz, i32, i32)
@@ -125,6 +128,7 @@ def _declare(lib) -> None:
     d("megray_moe_route", i32, vp, i32, i32, vp, vp, vp, vp)
     d("megray_moe_route_bwd", i32, vp, vp, vp, i32, i32, vp, vp)
     d("megray_moe_plan", i32, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp)
+    d("megray_moe_plan_exchange", i32, vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp)
     d("megray_moe_zero_pads", i32, vp, i32, vp, vp, vp, i32, vp)
     d("megray_moe_dispatch", i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, P(vp), i32, i32, i32, vp)
     d("megray_moe_combine", i32, vp, i32, i32, vp, vp, vp, P(vp), i32, i32, i32, vp)

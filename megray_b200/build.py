@@ -175,8 +175,74 @@ def build_sanitized(kind: str = "thread") -> str:
     return target
 
 
+def build_debug_bounds() -> str:
+    """Builds the C++ test runner with the collective kernels compiled under
+    ``-DMEGRAY_DEBUG_BOUNDS`` into ``build/debug_bounds/megray_test`` and returns its path.  In
+    that build every CTA-level copy or reduction first checks its whole range against the call's
+    buffers and the heaps; a range outside them is skipped, recorded, and reported as
+    MEGRAY_OUT_OF_BOUNDS.  All other objects are those of the normal build."""
+    build(with_bins=True)
+    out_dir = os.path.join(BUILD_DIR, "debug_bounds")
+    if os.environ.get("MEGRAY_SKIP_BUILD") == "1" and os.path.exists(os.path.join(out_dir, "megray_test")):
+        return os.path.join(out_dir, "megray_test")
+    os.makedirs(out_dir, exist_ok=True)
+    cpp, cu = _sources()
+    inc = f"-I{ROOT}/include -I{ROOT}/src -I{CUDA_HOME}/include"
+    nccl_inc = _nccl_include()
+    defs = "-DMEGRAY_WITH_CUDA -DMEGRAY_WITH_NVL -DMEGRAY_WITH_SHM"
+    if nccl_inc:
+        defs += " -DMEGRAY_WITH_NCCL"
+        if nccl_inc != "/usr/include":
+            inc += f" -I{nccl_inc}"
+    checked = [s for s in cu if os.path.basename(s) == "collectives.cu"]
+    lines = [
+        "ninja_required_version = 1.3",
+        f"nvccflags = -std=c++17 -O3 {GENCODE} -lineinfo -Xcompiler -fPIC --expt-relaxed-constexpr "
+        f"-DMEGRAY_DEBUG_BOUNDS {defs} {inc}",
+        "rule nvcc",
+        f"  command = {NVCC} -MD -MF $out.d $nvccflags -c $in -o $out",
+        "  depfile = $out.d",
+        "  deps = gcc",
+        "rule link",
+        f"  command = {NVCC} {GENCODE} -o $out $in -L{CUDA_HOME}/lib64 -lcudart -lpthread -ldl -lrt",
+        "",
+    ]
+
+    def normal_obj(src):
+        return os.path.join(BUILD_DIR, os.path.relpath(src, ROOT).replace(os.sep, "_") + ".o")
+
+    objs = []
+    for src in cpp + cu:
+        if src in checked:
+            obj = os.path.join(out_dir, os.path.relpath(src, ROOT).replace(os.sep, "_") + ".o")
+            lines.append(f"build {obj}: nvcc {src}")
+            objs.append(obj)
+        else:
+            objs.append(normal_obj(src))
+    for src in sorted(glob.glob(os.path.join(ROOT, "tests", "cpp", "*.cpp"))):
+        objs.append(normal_obj(src))
+    target = os.path.join(out_dir, "megray_test")
+    lines.append(f"build {target}: link {' '.join(objs)}")
+    lines.append(f"default {target}")
+    path = os.path.join(out_dir, "build.ninja")
+    text = "\n".join(lines) + "\n"
+    if not os.path.exists(path) or open(path).read() != text:
+        with open(path, "w") as f:
+            f.write(text)
+    res = subprocess.run([shutil.which("ninja"), "-f", path, "-C", out_dir], stdout=subprocess.PIPE,
+                         stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout)
+        raise RuntimeError("bounds-checked build failed")
+    return target
+
+
 def build(with_bins: bool = False, verbose: bool = False) -> str:
-    """Compile everything that is stale; returns the path of libmegray.so."""
+    """Compile everything that is stale; returns the path of libmegray.so.  With
+    MEGRAY_SKIP_BUILD=1 in the environment nothing is compiled (a machine that received the
+    binaries ready-made and should spend its time on something else)."""
+    if os.environ.get("MEGRAY_SKIP_BUILD") == "1" and os.path.exists(LIB_PATH):
+        return LIB_PATH
     ninja = shutil.which("ninja")
     if ninja is None:
         raise RuntimeError("ninja not found on PATH")
@@ -200,8 +266,12 @@ if __name__ == "__main__":
     ap.add_argument("--sanitize", default=None, metavar="KIND",
                     help="build the C++ test runner with the host code under -fsanitize=KIND "
                          "(thread, or address,undefined) instead")
+    ap.add_argument("--debug-bounds", action="store_true",
+                    help="build the C++ test runner with range-checked collective kernels instead")
     a = ap.parse_args()
-    if a.sanitize:
+    if a.debug_bounds:
+        print(build_debug_bounds())
+    elif a.sanitize:
         print(build_sanitized(a.sanitize))
     else:
         print(build(with_bins=a.all, verbose=a.verbose))

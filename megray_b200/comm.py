@@ -25,6 +25,7 @@ OK = 0
 STATUS_NAMES = [
     "OK", "SYS_ERROR", "CUDA_ERR", "NCCL_ERR", "UCX_ERR", "ENV_ERROR", "INVALID_ARGUMENT",
     "INVALID_USAGE", "UNEXPECTED_ERR", "NOT_IMPLEMENTED", "HIP_ERR", "RCCL_ERR", "TIMEOUT", "ABORTED",
+    "OUT_OF_BOUNDS",
 ]
 BACKENDS = {"nccl": NCCL, "ucx": UCX, "rccl": RCCL, "shm": SHM, "host": SHM, "nvl": NVL}
 OPS = {"sum": SUM, "max": MAX, "min": MIN}
@@ -420,6 +421,22 @@ class Communicator:
 
     def set_device_timeout_ms(self, ms: int) -> None:
         self._lib.megray_nvl_set_device_timeout_ms(self._h, ms)
+
+    def check_canaries(self) -> None:
+        """Synchronises the device and verifies the guard zones around the staging workspaces;
+        raises MegRayError(OUT_OF_BOUNDS) if a kernel wrote into one."""
+        _check(self._lib.megray_nvl_check_canaries(self._h), "check_canaries")
+
+    def set_p2p_async(self, on: bool = True) -> None:
+        """send / recv run on a stream of the communicator's own.  By default the caller's stream
+        waits for each transfer (stream-ordered, as the interface says); with ``on`` that wait is
+        postponed to :meth:`p2p_join`, so that kernels enqueued in between overlap the transfer."""
+        self._lib.megray_nvl_set_p2p_async(self._h, 1 if on else 0)
+
+    def p2p_join(self, stream=None) -> None:
+        torch = _torch()
+        s = stream if stream is not None else torch.cuda.current_stream()
+        _check(self._lib.megray_nvl_p2p_join(self._h, C.c_void_p(s.cuda_stream)), "p2p_join")
 
 
 def _op(op) -> int:

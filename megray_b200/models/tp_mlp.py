@@ -170,7 +170,7 @@ class TPMLPStack:
             return
         need = splits * M * N
         if self._wgrad_ws is None or self._wgrad_ws.numel() < need:
-            self._wgrad_ws = torch.empty(need, dtype=torch.bfloat16, device=self.device)
+            self._wgrad_ws = torch.empty(need, dtype=torch.float32, device=self.device)
         gemm_split_k(a_t, b_t, out, splits, self._wgrad_ws[:need].view(splits * M, N), a_mn=True, b_mn=True)
 
     def optimizer_step(self) -> None:

@@ -11,6 +11,7 @@ either through TMA without any transposition pass.  Epilogues:
 * ``EPI_SWIGLU``  ``b`` = [W_gate; W_up] stacked ([2F, K]); writes G|U into ``out`` ([M, 2F]) and
                   silu(G) * U into ``out2`` ([M, F])
 * ``EPI_DSWIGLU`` acc = dH ([M, F]); reads saved G|U from ``aux`` and writes dG|dU into ``out``
+* ``EPI_STORE_F32`` D = acc as float32 (``out`` is a float32 tensor): partial products of a K split
 
 There is no GEMM in the reference library; this one exists for the tensor-parallel MLP and
 MoE entry points.  A missing native library or a launch failure raises: nothing here falls
@@ -24,7 +25,7 @@ import torch
 
 from .. import _lib
 
-EPI_STORE, EPI_SWIGLU, EPI_DSWIGLU, EPI_ACCUM, EPI_PUSH, EPI_STORE_ROWS = 0, 1, 2, 3, 4, 5
+EPI_STORE, EPI_SWIGLU, EPI_DSWIGLU, EPI_ACCUM, EPI_PUSH, EPI_STORE_ROWS, EPI_STORE_F32 = 0, 1, 2, 3, 4, 5, 6
 
 _err_flags = {}
 
@@ -38,9 +39,9 @@ def gemm_error_flag(device=None) -> torch.Tensor:
     return _err_flags[key]
 
 
-def _check2d(t: torch.Tensor, name: str) -> None:
-    if t.dtype != torch.bfloat16 or t.dim() != 2 or not t.is_cuda:
-        raise ValueError(f"{name}: expected a 2-D CUDA bf16 tensor")
+def _check2d(t: torch.Tensor, name: str, dtype=torch.bfloat16) -> None:
+    if t.dtype != dtype or t.dim() != 2 or not t.is_cuda:
+        raise ValueError(f"{name}: expected a 2-D CUDA {dtype} tensor")
     if t.stride(1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
         raise ValueError(f"{name}: rows must be contiguous, 16-byte aligned, leading dimension % 8 == 0")
 
@@ -69,12 +70,13 @@ def build_gemm_args(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, 
         aux_off = N if epilogue == EPI_DSWIGLU else 0
     out_cols = 2 * N if epilogue in (EPI_SWIGLU, EPI_DSWIGLU) else N
     out_rows = M * groups if k_begin is not None else M
+    out_dtype = torch.float32 if epilogue == EPI_STORE_F32 else torch.bfloat16
     if out is None and alloc_out:
-        out = torch.empty(out_rows, out_cols, dtype=torch.bfloat16, device=a.device)
+        out = torch.empty(out_rows, out_cols, dtype=out_dtype, device=a.device)
     args = _lib.GemmArgs()
     args.A, args.B = a.data_ptr(), b.data_ptr()
     if out is not None:
-        _check2d(out, "out")
+        _check2d(out, "out", out_dtype)
         args.D, args.ldd = out.data_ptr(), out.stride(0)
     else:
         args.ldd = out_cols
@@ -141,7 +143,7 @@ def pick_split_k(M: int, N: int, K: int, sms: int = 148) -> int:
             break
         t = -(-tiles * s // pairs) * tile_s / s
         if s > 1:
-            t += (2 * s + 1) * M * N * 2 / 5.0e12  # partials written and read back, result written
+            t += (4 * s + 1) * M * N * 2 / 5.0e12  # float32 partials written and read back, result written
         if best_t is None or t < best_t * 0.97:  # a split must pay for itself
             best, best_t = s, t
     return best
@@ -150,8 +152,9 @@ def pick_split_k(M: int, N: int, K: int, sms: int = 148) -> int:
 def gemm_split_k(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, splits: int, partial: torch.Tensor = None,
                  *, a_mn: bool = False, b_mn: bool = False) -> torch.Tensor:
     """``out = A @ B^T`` computed as ``splits`` partial products over disjoint K ranges (multiples
-    of 64) that are then summed in fp32.  ``out`` must be contiguous; ``partial`` is an optional
-    ``[splits * M, N]`` bf16 workspace."""
+    of 64), kept in float32 and summed in float32: the result is rounded to bf16 once, like that of
+    an unsplit product.  ``out`` must be contiguous; ``partial`` is an optional ``[splits * M, N]``
+    float32 workspace."""
     if splits <= 1:
         return gemm(a, b, out, a_mn=a_mn, b_mn=b_mn)
     M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
@@ -169,14 +172,14 @@ def gemm_split_k(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, splits: in
                               torch.tensor(end, dtype=torch.int32, device=a.device))
     k_begin, k_end = _split_ranges[key]
     if partial is None:
-        partial = torch.empty(splits * M, N, dtype=torch.bfloat16, device=a.device)
+        partial = torch.empty(splits * M, N, dtype=torch.float32, device=a.device)
     part = partial[: splits * M]
     if part.shape[1] != N or not part.is_contiguous():
         raise ValueError("gemm_split_k: the workspace must be a contiguous [>= splits * M, N] tensor")
     gemm(a, b, part, a_mn=a_mn, b_mn=b_mn, n=N, k_begin=k_begin, k_end=k_end, groups=splits,
-         variant=3 if M % 512 == 0 else 2)
-    ptrs = (C.c_void_p * splits)(*[part.data_ptr() + i * M * N * 2 for i in range(splits)])
-    rc = _lib.load().megray_reduce_n(ptrs, splits, C.c_void_p(out.data_ptr()), M * N, 10, 10,  # MEGRAY_BFLOAT16
+         variant=3 if M % 512 == 0 else 2, epilogue=EPI_STORE_F32)
+    ptrs = (C.c_void_p * splits)(*[part.data_ptr() + i * M * N * 4 for i in range(splits)])
+    rc = _lib.load().megray_reduce_n(ptrs, splits, C.c_void_p(out.data_ptr()), M * N, 7, 10,  # float32 -> bfloat16
                                      0, C.c_float(1.0), C.c_void_p(torch.cuda.current_stream().cuda_stream))
     if rc != 0:
         raise RuntimeError(f"megray_reduce_n failed ({rc})")

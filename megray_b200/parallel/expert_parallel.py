@@ -3,9 +3,10 @@
 ``ExpertParallelOps`` owns the routing state of one MoE layer on one rank:
 
     route(logits)            top-2 experts and gate weights per token, per-expert counts
-    plan()                   exchange the counts (a tiny all_gather), compute where every rank's
-                             tokens land in each owner's expert-sorted buffer (segments padded to
-                             128 rows), all on the device: no host synchronisation
+    plan()                   one launch: exchange the counts (flagged words through the peers' small-message
+                             slots) and compute where every rank's tokens land in each owner's
+                             expert-sorted buffer (segments padded to 128 rows), all on the device:
+                             no host synchronisation, no separate all_gather
     dispatch(src, dst, w)    every (token, slot) row is stored straight at its final position in the
                              owning GPU's buffer over NVLink: permute + all-to-all-v in one kernel
     combine(out, src, w)     every token loads its two expert rows from the GPUs that hold them and
@@ -89,6 +90,14 @@ class ExpertParallelOps:
                                                self.w.data_ptr(), self.counts.data_ptr(), self._stream()), "moe_route")
 
     def plan(self) -> None:
+        if self.comm is not None and self.comm.backend == 4:  # NVL: counts travel inside the plan launch
+            # (every rank hears from every other one here, which also orders this step after
+            # every rank's previous step: the exchange buffers are re-used)
+            self._check(self._lib.megray_moe_plan_exchange(
+                self.comm._h, self.counts.data_ptr(), self.E, self.capacity, self.send_base.data_ptr(),
+                self.seg_begin.data_ptr(), self.seg_end.data_ptr(), self.seg_rows.data_ptr(),
+                self.block_group.data_ptr(), self.total.data_ptr(), self._stream()), "moe_plan_exchange")
+            return
         if self.comm is not None:
             # also orders this step after every rank's previous step (buffers are re-used)
             self.comm.all_gather(self.counts, self.counts_all.view(-1))

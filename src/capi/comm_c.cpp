@@ -210,6 +210,19 @@ void megray_nvl_set_device_timeout_ms(void* comm, int64_t ms) {
     if (n)
         n->set_device_timeout_ms(ms);
 }
+int megray_nvl_check_canaries(void* comm) {
+    NvlInterface* n = as_nvl(C(comm));
+    return n ? n->check_canaries() : MEGRAY_INVALID_USAGE;
+}
+void megray_nvl_set_p2p_async(void* comm, int on) {
+    NvlInterface* n = as_nvl(C(comm));
+    if (n)
+        n->set_p2p_async(on != 0);
+}
+int megray_nvl_p2p_join(void* comm, void* stream) {
+    NvlInterface* n = as_nvl(C(comm));
+    return n ? n->p2p_join(make_ctx(1, stream)) : MEGRAY_INVALID_USAGE;
+}
 
 int megray_cpu_reduce_n(const void* const* in, int n_in, void* out, size_t len, int dtype, int op) {
     return host::cpu_reduce_n(in, n_in, out, len, static_cast<DType>(dtype), static_cast<ReduceOp>(op));

@@ -1,6 +1,10 @@
 // C entry points of the MoE kernels (see include/megray/c_api.h).
+#include <memory>
+
 #include "kernels/moe.cuh"
 #include "megray/c_api.h"
+#include "megray/communicator.h"
+#include "megray/fused.h"
 
 namespace {
 int rc(cudaError_t e) { return e == cudaSuccess ? 0 : -static_cast<int>(e); }
@@ -11,6 +15,9 @@ mgk::moe::PeerBufs bufs(void* const* p, int n) {
     return b;
 }
 cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
+struct CommBoxView {  // layout of the handle made by megray_comm_new (capi/comm_c.cpp)
+    std::shared_ptr<MegRay::Communicator> comm;
+};
 }  // namespace
 
 extern "C" {
@@ -26,6 +33,34 @@ int megray_moe_plan(const int* counts_all, int nranks, int rank, int experts, in
                     int* seg_begin, int* seg_end, int* seg_rows, int* block_group, int* total, void* stream) {
     mgk::moe::PlanOut o{send_base, seg_begin, seg_end, seg_rows, block_group, total};
     return rc(mgk::moe::launch_plan(counts_all, nranks, rank, experts, capacity_rows, o, S(stream)));
+}
+int megray_moe_plan_exchange(void* comm, const int* counts, int experts, int capacity_rows, int* send_base,
+                             int* seg_begin, int* seg_end, int* seg_rows, int* block_group, int* total, void* stream) {
+    if (comm == nullptr)
+        return 6;
+    MegRay::Communicator* c = static_cast<CommBoxView*>(comm)->comm.get();
+    MegRay::NvlInterface* nvl = MegRay::as_nvl(c);
+    if (nvl == nullptr)
+        return 7;
+    const MegRay::Status st = nvl->fused_begin(stream);
+    if (st != MegRay::MEGRAY_OK)
+        return st;
+    mgk::moe::PlanExchange x{};
+    const int n = static_cast<int>(c->nranks());
+    for (int q = 0; q < n && q < mgk::moe::kMaxRanks; ++q)
+        x.heap[q] = static_cast<char*>(nvl->heap_base(static_cast<uint32_t>(q)));
+    size_t off = 0, stride = 0;
+    nvl->ll_ticket(&x.seq, &off, &stride);
+    x.slot_off = off;
+    x.slot_stride = stride;
+    x.timeout_ns = nvl->device_timeout_ns();
+    x.status = nvl->status_word();
+    mgk::moe::PlanOut o{send_base, seg_begin, seg_end, seg_rows, block_group, total};
+    const int r = rc(mgk::moe::launch_plan_exchange(counts, x, n, static_cast<int>(c->rank()), experts, capacity_rows, o,
+                                                    S(stream)));
+    if (r == 0)
+        nvl->fused_end(stream);
+    return r;
 }
 int megray_moe_zero_pads(void* buf, int row_elems, const int* seg_begin, const int* seg_rows, const int* seg_end,
                          int local_experts, void* stream) {

@@ -19,7 +19,7 @@ const char* status_name(Status s) {
     static const char* kName[MEGRAY_STATUS_COUNT] = {
             "OK",           "SYS_ERROR",        "CUDA_ERR",      "NCCL_ERR",       "UCX_ERR",
             "ENV_ERROR",    "INVALID_ARGUMENT", "INVALID_USAGE", "UNEXPECTED_ERR", "NOT_IMPLEMENTED",
-            "HIP_ERR",      "RCCL_ERR",         "TIMEOUT",       "ABORTED"};
+            "HIP_ERR",      "RCCL_ERR",         "TIMEOUT",       "ABORTED",        "OUT_OF_BOUNDS"};
     if (static_cast<int>(s) < 0 || s >= MEGRAY_STATUS_COUNT)
         return "?";
     return kName[s];

@@ -8,11 +8,16 @@
 
 #include <algorithm>
 #include <atomic>
+#include <condition_variable>
+#include <deque>
+#include <mutex>
+#include <thread>
 
 #include "host/cpu_reduce.h"
 #include "megray/options.h"
 
 #ifdef MEGRAY_WITH_CUDA
+#include <cuda.h>
 #include <cuda_runtime_api.h>
 
 #include "megray/cuda_context.h"
@@ -48,14 +53,212 @@ size_t env_kb(const char* name, size_t dflt_kb) {
 
 }  // namespace
 
+#ifdef MEGRAY_WITH_CUDA
+// Everything the stream-ordered path of one communicator owns.
+struct HostCommunicator::AsyncState {
+    struct Job {
+        AsyncState* owner;
+        std::function<Status()> work;
+        uint32_t seq;
+    };
+    struct Slot {
+        void* pinned = nullptr;
+        size_t bytes = 0;
+        cudaEvent_t done = nullptr;  // recorded after the slot's result left for the device
+        bool used = false;
+    };
+    static constexpr int kSlots = 4;
+    using WaitValueFn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+
+    HostCommunicator* comm;
+    WaitValueFn wait_value = nullptr;
+    volatile uint32_t* done_host = nullptr;  // pinned, mapped: number of the last finished job
+    CUdeviceptr done_dev = 0;
+    uint32_t next_seq = 0;
+    Slot slots[kSlots];
+    int next_slot = 0;
+    std::vector<cudaStream_t> streams;  // every stream a job was enqueued on
+    std::mutex mu;
+    std::condition_variable cv, idle_cv;
+    std::deque<Job*> queue;
+    bool busy = false, stop = false;
+    std::atomic<int> error{0};
+    std::thread worker;
+
+    explicit AsyncState(HostCommunicator* c) : comm(c) {}
+
+    bool start() {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess || fn == nullptr) {
+            (void)cudaGetLastError();
+            return false;
+        }
+        wait_value = reinterpret_cast<WaitValueFn>(fn);
+        void* h = nullptr;
+        if (cudaHostAlloc(&h, 64, cudaHostAllocMapped) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+        memset(h, 0, 64);
+        void* d = nullptr;
+        if (cudaHostGetDevicePointer(&d, h, 0) != cudaSuccess) {
+            (void)cudaGetLastError();
+            cudaFreeHost(h);
+            return false;
+        }
+        done_host = static_cast<volatile uint32_t*>(h);
+        done_dev = reinterpret_cast<CUdeviceptr>(d);
+        worker = std::thread([this] { loop(); });
+        return true;
+    }
+
+    void loop() {
+        for (;;) {
+            Job* job = nullptr;
+            {
+                std::unique_lock<std::mutex> lk(mu);
+                cv.wait(lk, [&] { return stop || !queue.empty(); });
+                if (queue.empty())
+                    return;
+                job = queue.front();
+                queue.pop_front();
+                busy = true;
+            }
+            const Status s = job->work();
+            if (s != MEGRAY_OK) {
+                int expected = 0;
+                error.compare_exchange_strong(expected, static_cast<int>(s));
+            }
+            // the stream that waits for this job goes on, whatever the outcome
+            __atomic_store_n(const_cast<uint32_t*>(done_host), job->seq, __ATOMIC_RELEASE);
+            delete job;
+            {
+                std::lock_guard<std::mutex> lk(mu);
+                busy = false;
+            }
+            idle_cv.notify_all();
+        }
+    }
+
+    static void CUDART_CB hand_over(void* p) {  // runs on a driver thread: must not block
+        Job* job = static_cast<Job*>(p);
+        AsyncState* a = job->owner;
+        {
+            std::lock_guard<std::mutex> lk(a->mu);
+            a->queue.push_back(job);
+        }
+        a->cv.notify_one();
+    }
+
+    void drain() {
+        std::unique_lock<std::mutex> lk(mu);
+        idle_cv.wait(lk, [&] { return queue.empty() && !busy; });
+    }
+
+    ~AsyncState() {
+        for (cudaStream_t s : streams)
+            cudaStreamSynchronize(s);  // every job has been handed over and waited for
+        {
+            std::lock_guard<std::mutex> lk(mu);
+            stop = true;
+        }
+        cv.notify_all();
+        if (worker.joinable())
+            worker.join();
+        for (Slot& sl : slots) {
+            if (sl.done != nullptr)
+                cudaEventDestroy(sl.done);
+            if (sl.pinned != nullptr)
+                cudaFreeHost(sl.pinned);
+        }
+        if (done_host != nullptr)
+            cudaFreeHost(const_cast<uint32_t*>(done_host));
+    }
+};
+#else
+struct HostCommunicator::AsyncState {};
+#endif
+
 HostCommunicator::HostCommunicator(uint32_t nranks, uint32_t rank) : Communicator(nranks, rank) {
     m_timeout_ms = global_options().timeout_ms;
 }
 
 HostCommunicator::~HostCommunicator() {
 #ifdef MEGRAY_WITH_CUDA
+    delete m_async;
     if (m_pinned != nullptr)
         cudaFreeHost(m_pinned);
+#endif
+}
+
+void HostCommunicator::drain_async() {
+#ifdef MEGRAY_WITH_CUDA
+    if (m_async != nullptr) {
+        for (cudaStream_t s : m_async->streams)
+            cudaStreamSynchronize(s);
+        m_async->drain();
+        const int e = m_async->error.load();
+        if (e != 0)
+            fail(static_cast<Status>(e));
+    }
+#endif
+}
+
+Status HostCommunicator::run_stream_ordered(void* stream_v, const void* in, size_t in_bytes, void* out,
+                                            size_t out_bytes, const Body& body) {
+#ifdef MEGRAY_WITH_CUDA
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    AsyncState& a = *m_async;
+    const int e = a.error.load();
+    if (e != 0)
+        return fail(static_cast<Status>(e));
+    AsyncState::Slot& sl = a.slots[a.next_slot];
+    a.next_slot = (a.next_slot + 1) % AsyncState::kSlots;
+    if (sl.used)
+        CUDA_CHECK(cudaEventSynchronize(sl.done));  // (blocks only when four calls are in flight)
+    const size_t need = in_bytes + out_bytes;
+    if (need > sl.bytes) {
+        if (sl.pinned != nullptr)
+            cudaFreeHost(sl.pinned);
+        sl.pinned = nullptr;
+        sl.bytes = 0;
+        CUDA_CHECK(cudaHostAlloc(&sl.pinned, std::max<size_t>(need, 4096), cudaHostAllocDefault));
+        sl.bytes = std::max<size_t>(need, 4096);
+    }
+    if (sl.done == nullptr)
+        CUDA_CHECK(cudaEventCreateWithFlags(&sl.done, cudaEventDisableTiming));
+    char* h_in = static_cast<char*>(sl.pinned);
+    char* h_out = h_in + in_bytes;
+    if (std::find(a.streams.begin(), a.streams.end(), stream) == a.streams.end())
+        a.streams.push_back(stream);
+    if (in_bytes)
+        CUDA_CHECK(cudaMemcpyAsync(h_in, in, in_bytes, cudaMemcpyDeviceToHost, stream));
+    auto* job = new AsyncState::Job;
+    job->owner = &a;
+    job->seq = ++a.next_seq;
+    const char* hin = in_bytes ? h_in : nullptr;
+    char* hout = out_bytes ? h_out : nullptr;
+    job->work = [body, hin, hout] { return body(hin, hout); };
+    cudaError_t ce = cudaLaunchHostFunc(stream, AsyncState::hand_over, job);
+    if (ce != cudaSuccess) {
+        delete job;
+        CUDA_CHECK(ce);
+    }
+    if (a.wait_value(stream, a.done_dev, job->seq, CU_STREAM_WAIT_VALUE_GEQ) != CUDA_SUCCESS) {
+        // the job is on its way: wait for it the blocking way
+        CUDA_CHECK(cudaStreamSynchronize(stream));
+        a.drain();
+    }
+    if (out_bytes)
+        CUDA_CHECK(cudaMemcpyAsync(out, h_out, out_bytes, cudaMemcpyHostToDevice, stream));
+    CUDA_CHECK(cudaEventRecord(sl.done, stream));
+    sl.used = true;
+    return MEGRAY_OK;
+#else
+    (void)stream_v; (void)in; (void)in_bytes; (void)out; (void)out_bytes; (void)body;
+    return MEGRAY_INVALID_ARGUMENT;
 #endif
 }
 
@@ -74,6 +277,13 @@ void HostCommunicator::abort() {
 }
 
 Status HostCommunicator::status() {
+#ifdef MEGRAY_WITH_CUDA
+    if (m_async != nullptr && m_error == MEGRAY_OK) {
+        const int e = m_async->error.load();
+        if (e != 0)
+            fail(static_cast<Status>(e));
+    }
+#endif
     if (m_aborted.load() || (m_region && m_region->aborted()))
         return m_error != MEGRAY_OK ? m_error : MEGRAY_ABORTED;
     return m_error;
@@ -162,6 +372,7 @@ Status HostCommunicator::check_ready(const std::shared_ptr<Context>& ctx) const 
 Status HostCommunicator::barrier() {
     if (!m_region)
         return MEGRAY_INVALID_USAGE;
+    drain_async();
     return fail(sync_step());
 }
 
@@ -170,14 +381,32 @@ Status HostCommunicator::run(const std::shared_ptr<Context>& ctx, const void* in
     MEGRAY_CHECK(check_ready(ctx));
     m_stats.calls++;
     m_stats.bytes += std::max(in_bytes, out_bytes);
-    if (ctx->type() == MEGRAY_CTX_DEFAULT)
+    if (ctx->type() == MEGRAY_CTX_DEFAULT) {
+        drain_async();  // jobs of CUDA contexts use the same barrier state
         return fail(body(static_cast<const char*>(in), static_cast<char*>(out)));
+    }
 #ifdef MEGRAY_WITH_CUDA
     cudaStream_t stream = static_cast<CudaContext*>(ctx.get())->get_stream();
     if (in == nullptr)
         in_bytes = 0;
     if (out == nullptr)
         out_bytes = 0;
+    if (m_async == nullptr && !m_async_tried) {
+        m_async_tried = true;
+        static const bool wanted = [] {
+            const char* e = getenv("MEGRAY_HOST_STREAM_ORDERED");
+            return e == nullptr || atoi(e) != 0;
+        }();
+        if (wanted) {
+            m_async = new AsyncState(this);
+            if (!m_async->start()) {
+                delete m_async;
+                m_async = nullptr;
+            }
+        }
+    }
+    if (m_async != nullptr)
+        return run_stream_ordered(stream, in, in_bytes, out, out_bytes, body);
     const size_t need = in_bytes + out_bytes;
     if (need > m_pinned_bytes) {
         if (m_pinned != nullptr)
@@ -213,7 +442,7 @@ Status HostCommunicator::all_gather(const void* sendbuff, void* recvbuff, size_t
                                     DType dtype, std::shared_ptr<Context> ctx) {
     const size_t bytes = sendlen * get_dtype_size(dtype);
     TraceScope trace("all_gather", bytes, m_rank);
-    return run(ctx, sendbuff, bytes, recvbuff, bytes * m_nranks, [&](const char* in, char* out) {
+    return run(ctx, sendbuff, bytes, recvbuff, bytes * m_nranks, [=](const char* in, char* out) {
         const size_t cap = m_region->slot_bytes();
         for (size_t off = 0; off < bytes || off == 0; off += cap) {
             const size_t piece = std::min(cap, bytes - off);
@@ -236,7 +465,7 @@ Status HostCommunicator::all_reduce(const void* sendbuff, void* recvbuff, size_t
     const size_t esz = get_dtype_size(dtype);
     const size_t bytes = len * esz;
     TraceScope trace("all_reduce", bytes, m_rank);
-    return run(ctx, sendbuff, bytes, recvbuff, bytes, [&](const char* in, char* out) {
+    return run(ctx, sendbuff, bytes, recvbuff, bytes, [=](const char* in, char* out) {
         const size_t cap_elems = m_region->slot_bytes() / esz;
         std::vector<const void*> srcs(m_nranks);
         for (size_t e0 = 0; e0 < len || e0 == 0; e0 += cap_elems) {
@@ -267,7 +496,7 @@ Status HostCommunicator::reduce_scatter(const void* sendbuff, void* recvbuff, si
     const size_t esz = get_dtype_size(dtype);
     const size_t bytes = recvlen * esz;
     TraceScope trace("reduce_scatter", bytes, m_rank);
-    return run(ctx, sendbuff, bytes * m_nranks, recvbuff, bytes, [&](const char* in, char* out) {
+    return run(ctx, sendbuff, bytes * m_nranks, recvbuff, bytes, [=](const char* in, char* out) {
         // each rank publishes, for every destination d, a piece of chunk d
         const size_t cap_elems = std::max<size_t>(1, m_region->slot_bytes() / m_nranks / esz);
         std::vector<const void*> srcs(m_nranks);
@@ -294,7 +523,7 @@ Status HostCommunicator::all_to_all(const void* sendbuff, void* recvbuff, size_t
     const size_t bytes = len * get_dtype_size(dtype);
     TraceScope trace("all_to_all", bytes, m_rank);
     return run(ctx, sendbuff, bytes * m_nranks, recvbuff, bytes * m_nranks,
-               [&](const char* in, char* out) {
+               [=](const char* in, char* out) {
                    const size_t cap = std::max<size_t>(1, m_region->slot_bytes() / m_nranks);
                    for (size_t off = 0; off < bytes || off == 0; off += cap) {
                        const size_t piece = std::min(cap, bytes - off);
@@ -319,7 +548,7 @@ Status HostCommunicator::broadcast(const void* sendbuff, void* recvbuff, size_t 
     TraceScope trace("broadcast", bytes, m_rank);
     const bool is_root = m_rank == root;
     return run(ctx, is_root ? sendbuff : nullptr, is_root ? bytes : 0, recvbuff, bytes,
-               [&](const char* in, char* out) {
+               [=](const char* in, char* out) {
                    const size_t cap = m_region->slot_bytes();
                    for (size_t off = 0; off < bytes || off == 0; off += cap) {
                        const size_t piece = std::min(cap, bytes - off);
@@ -344,7 +573,7 @@ Status HostCommunicator::reduce(const void* sendbuff, void* recvbuff, size_t len
     TraceScope trace("reduce", bytes, m_rank);
     const bool is_root = m_rank == root;
     return run(ctx, sendbuff, bytes, is_root ? recvbuff : nullptr, is_root ? bytes : 0,
-               [&](const char* in, char* out) {
+               [=](const char* in, char* out) {
                    const size_t cap_elems = m_region->slot_bytes() / esz;
                    std::vector<const void*> srcs(m_nranks);
                    for (size_t e0 = 0; e0 < len || e0 == 0; e0 += cap_elems) {
@@ -373,7 +602,7 @@ Status HostCommunicator::gather(const void* sendbuff, void* recvbuff, size_t sen
     TraceScope trace("gather", bytes, m_rank);
     const bool is_root = m_rank == root;
     return run(ctx, sendbuff, bytes, is_root ? recvbuff : nullptr, is_root ? bytes * m_nranks : 0,
-               [&](const char* in, char* out) {
+               [=](const char* in, char* out) {
                    const size_t cap = m_region->slot_bytes();
                    for (size_t off = 0; off < bytes || off == 0; off += cap) {
                        const size_t piece = std::min(cap, bytes - off);
@@ -398,7 +627,7 @@ Status HostCommunicator::scatter(const void* sendbuff, void* recvbuff, size_t re
     TraceScope trace("scatter", bytes, m_rank);
     const bool is_root = m_rank == root;
     return run(ctx, is_root ? sendbuff : nullptr, is_root ? bytes * m_nranks : 0, recvbuff, bytes,
-               [&](const char* in, char* out) {
+               [=](const char* in, char* out) {
                    const size_t cap = std::max<size_t>(1, m_region->slot_bytes() / m_nranks);
                    for (size_t off = 0; off < bytes || off == 0; off += cap) {
                        const size_t piece = std::min(cap, bytes - off);
@@ -530,6 +759,7 @@ Status HostCommunicator::group_start() {
 }
 
 Status HostCommunicator::group_end() {
+    drain_async();  // stream-ordered jobs use the same barrier state and mailboxes
     m_grouping = false;
     std::vector<P2POp> ops;
     ops.swap(m_queued);

@@ -92,6 +92,22 @@ private:
     Status m_error = MEGRAY_OK;
     void* m_pinned = nullptr;  // staging for CUDA contexts (grow-only)
     size_t m_pinned_bytes = 0;
+
+    // CUDA contexts, stream-ordered: a call enqueues (1) the copy of its input into a pinned
+    // staging slot, (2) a host function that hands the job to this communicator's worker thread
+    // and returns at once, (3) a stream wait on a pinned word that the worker sets when the job is
+    // done, (4) the copy of the result to the device; the caller never blocks.  The worker runs the
+    // jobs in order (the barriers inside a job wait for the other ranks' workers, with the host
+    // time limit).  The same semantics as the reference's shared-memory all_reduce (stream
+    // callbacks around a CPU reducer thread, reference src/shm/all_reduce.cpp:88-124), without
+    // callbacks that spin.
+    struct AsyncState;
+    AsyncState* m_async = nullptr;
+    bool m_async_tried = false;
+    Status run_stream_ordered(void* stream, const void* in, size_t in_bytes, void* out, size_t out_bytes,
+                              const Body& body);
+    void drain_async();  // wait until the worker has finished everything handed to it
+    friend struct AsyncState;
 };
 
 }  // namespace MegRay

@@ -22,6 +22,57 @@ __device__ __forceinline__ uint64_t round_up_u64(uint64_t v, uint64_t a) {
     return (v + a - 1) / a * a;
 }
 
+// ------------------------------------------------------------------ phase stamps
+__device__ __forceinline__ void stamp(const CommonArgs& c, int i) {
+    if (c.phases && blockIdx.x == 0 && threadIdx.x == 0 && i < kMaxPhases)
+        reinterpret_cast<uint64_t*>(c.peers.heap[c.rank] + kPhaseOff)[i] = globaltimer_ns();
+}
+
+// ------------------------------------------------------------------ range guard
+// In a build with MEGRAY_DEBUG_BOUNDS every CTA-level primitive asks the guard before it touches
+// a range.  Allowed: any rank's heap, this call's local buffers, and (single-pass kernels on
+// exchanged addresses) the peers' buffers.  In an ordinary build the guard is empty and free.
+struct Guard {
+#ifdef MEGRAY_DEBUG_BOUNDS
+    const CommonArgs* c;
+    const char* peer_in[kMaxRanks];
+    const char* peer_out[kMaxRanks];
+    __device__ __forceinline__ bool inside(const char* p, uint64_t n, const char* lo, uint64_t len) const {
+        return lo != nullptr && len != 0 && p >= lo && p + n <= lo + len;
+    }
+    __device__ bool ok(const void* ptr, uint64_t n, int line) const {
+        if (n == 0)
+            return true;
+        const char* p = static_cast<const char*>(ptr);
+        bool fine = inside(p, n, static_cast<const char*>(c->guard_in), c->guard_in_bytes) ||
+                    inside(p, n, static_cast<const char*>(c->guard_out), c->guard_out_bytes);
+        for (int q = 0; q < c->nranks && !fine; ++q)
+            fine = inside(p, n, c->peers.heap[q], c->heap_bytes) ||
+                   inside(p, n, peer_in[q], c->guard_peer_in_bytes) ||
+                   inside(p, n, peer_out[q], c->guard_peer_out_bytes);
+        if (!fine && c->status != nullptr && atomicCAS(c->status, 0, kStatusOutOfBounds) == 0) {
+            uint64_t* rec = reinterpret_cast<uint64_t*>(c->peers.heap[c->rank] + kDebugOff);
+            rec[0] = reinterpret_cast<uint64_t>(ptr);
+            rec[1] = n;
+            rec[2] = static_cast<uint64_t>(static_cast<uint32_t>(line)) | (static_cast<uint64_t>(c->rank) << 32);
+        }
+        return fine;
+    }
+#else
+    __device__ __forceinline__ bool ok(const void*, uint64_t, int) const { return true; }
+#endif
+};
+__device__ __forceinline__ Guard make_guard(const CommonArgs& c) {
+    Guard g;
+#ifdef MEGRAY_DEBUG_BOUNDS
+    g.c = &c;
+    for (int q = 0; q < kMaxRanks; ++q)
+        g.peer_in[q] = g.peer_out[q] = nullptr;
+#endif
+    return g;
+}
+#define GUARD_OK(g, p, n) (g).ok((p), (n), __LINE__)
+
 // ------------------------------------------------------------------ barrier
 // One flag word per (CTA, peer) in every rank's pad.  Returns false when a wait ran out.
 __device__ __forceinline__ bool cta_barrier(const CommonArgs& c, uint32_t target) {
@@ -64,11 +115,14 @@ __device__ __forceinline__ char ld_cg_byte(const char* p) {
 
 // CTA-cooperative byte copy for any alignment.  Vector (16 B) body when source and
 // destination are equally aligned, else 4-byte or 1-byte units.
-__device__ __forceinline__ void cta_copy(char* dst, const char* src, uint64_t nbytes) {
+// `tid` of `nth` threads take part (the whole CTA in cta_copy below).
+__device__ __forceinline__ void cta_copy_part(const Guard& g, char* dst, const char* src, uint64_t nbytes,
+                                              unsigned tid, unsigned nth) {
     if (nbytes == 0)
         return;
+    if (!GUARD_OK(g, dst, nbytes) || !GUARD_OK(g, src, nbytes))
+        return;
     const uintptr_t da = reinterpret_cast<uintptr_t>(dst), sa = reinterpret_cast<uintptr_t>(src);
-    const unsigned tid = threadIdx.x, nth = blockDim.x;
     if (((da ^ sa) & 15) == 0) {
         uint64_t head = (16 - (da & 15)) & 15;
         if (head > nbytes)
@@ -112,6 +166,19 @@ __device__ __forceinline__ void cta_copy(char* dst, const char* src, uint64_t nb
         for (uint64_t i = tid; i < nbytes; i += nth)
             dst[i] = ld_cg_byte(src + i);
     }
+}
+
+__device__ __forceinline__ void cta_copy(const Guard& g, char* dst, const char* src, uint64_t nbytes) {
+    cta_copy_part(g, dst, src, nbytes, threadIdx.x, blockDim.x);
+}
+
+// Named barriers (ids 1..15; id 0 is __syncthreads): `count` threads in all, some of which only
+// arrive and go on, while the others wait for them.
+__device__ __forceinline__ void named_bar_arrive(int id, int count) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
 // ------------------------------------------------------------------ arithmetic
@@ -179,9 +246,12 @@ struct IsFloatAcc<double> {
 // out[0..n) = cast(scale * op over k of slot_k[0..n)), slots `slot_stride` bytes apart.
 // `slots` and `out` are 16-byte aligned (staging memory); n is in elements.
 template <typename Tin, typename Tout, int OP>
-__device__ __forceinline__ void cta_reduce_slots(const char* slots, uint64_t slot_stride, int nslots,
-                                                 char* out, uint64_t n, float scale) {
+__device__ __forceinline__ void cta_reduce_slots(const Guard& g, const char* slots, uint64_t slot_stride,
+                                                 int nslots, char* out, uint64_t n, float scale) {
     using A = typename Acc<Tin>::type;
+    if (n == 0 || !GUARD_OK(g, out, n * sizeof(Tout)) ||
+        !GUARD_OK(g, slots, (nslots - 1) * slot_stride + n * sizeof(Tin)))
+        return;
     constexpr int V = 16 / sizeof(Tin);
     const unsigned tid = threadIdx.x, nth = blockDim.x;
     const uint64_t nvec = n / V;
@@ -238,6 +308,8 @@ __device__ __forceinline__ void cta_reduce_slots(const char* slots, uint64_t slo
 template <typename Tin, typename Tout>
 __global__ void __launch_bounds__(512) reduce_family_kernel(const ReduceArgs a) {
     const CommonArgs& c = a.c;
+    const Guard g = make_guard(c);
+    stamp(c, 0);
     const int n = c.nranks, rank = c.rank;
     constexpr uint64_t V = 16 / sizeof(Tin);
     const uint64_t esz_in = sizeof(Tin), esz_out = sizeof(Tout);
@@ -253,7 +325,7 @@ __global__ void __launch_bounds__(512) reduce_family_kernel(const ReduceArgs a) 
         const uint64_t b = min(a.len, per_cta * blockIdx.x), e = min(a.len, b + per_cta);
         for (int jj = 0; jj < n; ++jj) {
             const int j = (rank + jj) % n;
-            cta_copy(c.peers.heap[j] + a.stage_off + rank * slot_stride + b * esz_in, in + b * esz_in,
+            cta_copy(g, c.peers.heap[j] + a.stage_off + rank * slot_stride + b * esz_in, in + b * esz_in,
                      (e - b) * esz_in);
         }
         if (!cta_barrier(c, ++epoch))
@@ -262,17 +334,17 @@ __global__ void __launch_bounds__(512) reduce_family_kernel(const ReduceArgs a) 
         const char* slots = my_heap + a.stage_off + b * esz_in;
         switch (a.op) {
             case MegRay::MEGRAY_SUM:
-                cta_reduce_slots<Tin, Tout, MegRay::MEGRAY_SUM>(slots, slot_stride, n, red, e - b, a.scale);
+                cta_reduce_slots<Tin, Tout, MegRay::MEGRAY_SUM>(g, slots, slot_stride, n, red, e - b, a.scale);
                 break;
             case MegRay::MEGRAY_MAX:
-                cta_reduce_slots<Tin, Tout, MegRay::MEGRAY_MAX>(slots, slot_stride, n, red, e - b, a.scale);
+                cta_reduce_slots<Tin, Tout, MegRay::MEGRAY_MAX>(g, slots, slot_stride, n, red, e - b, a.scale);
                 break;
             default:
-                cta_reduce_slots<Tin, Tout, MegRay::MEGRAY_MIN>(slots, slot_stride, n, red, e - b, a.scale);
+                cta_reduce_slots<Tin, Tout, MegRay::MEGRAY_MIN>(g, slots, slot_stride, n, red, e - b, a.scale);
         }
         __syncthreads();
         if (out != nullptr)
-            cta_copy(out + b * esz_out, red, (e - b) * esz_out);
+            cta_copy(g, out + b * esz_out, red, (e - b) * esz_out);
         return;
     }
 
@@ -296,11 +368,13 @@ __global__ void __launch_bounds__(512) reduce_family_kernel(const ReduceArgs a) 
         const int j = (rank + 1 + jj) % n;
         uint64_t b, e;
         sub_range(j, &b, &e);
-        cta_copy(c.peers.heap[j] + a.stage_off + rank * slot_stride + b * esz_in,
+        cta_copy(g, c.peers.heap[j] + a.stage_off + rank * slot_stride + b * esz_in,
                  in + (static_cast<uint64_t>(j) * a.in_pitch_elems + b) * esz_in, (e - b) * esz_in);
     }
+    stamp(c, 1);
     if (!cta_barrier(c, ++epoch))
         return;
+    stamp(c, 2);
 
     // phase R: combine the n slots of my slice, in rank order
     uint64_t b, e;
@@ -310,23 +384,25 @@ __global__ void __launch_bounds__(512) reduce_family_kernel(const ReduceArgs a) 
         const char* slots = my_heap + a.stage_off + b * esz_in;
         switch (a.op) {
             case MegRay::MEGRAY_SUM:
-                cta_reduce_slots<Tin, Tout, MegRay::MEGRAY_SUM>(slots, slot_stride, n, red, e - b, a.scale);
+                cta_reduce_slots<Tin, Tout, MegRay::MEGRAY_SUM>(g, slots, slot_stride, n, red, e - b, a.scale);
                 break;
             case MegRay::MEGRAY_MAX:
-                cta_reduce_slots<Tin, Tout, MegRay::MEGRAY_MAX>(slots, slot_stride, n, red, e - b, a.scale);
+                cta_reduce_slots<Tin, Tout, MegRay::MEGRAY_MAX>(g, slots, slot_stride, n, red, e - b, a.scale);
                 break;
             default:
-                cta_reduce_slots<Tin, Tout, MegRay::MEGRAY_MIN>(slots, slot_stride, n, red, e - b, a.scale);
+                cta_reduce_slots<Tin, Tout, MegRay::MEGRAY_MIN>(g, slots, slot_stride, n, red, e - b, a.scale);
         }
     }
     if (a.out_is_slice) {  // reduce_scatter: done after a local copy
         __syncthreads();
         if (out != nullptr)
-            cta_copy(out + b * esz_out, red, (e - b) * esz_out);
+            cta_copy(g, out + b * esz_out, red, (e - b) * esz_out);
         return;
     }
+    stamp(c, 3);
     if (!cta_barrier(c, ++epoch))
         return;
+    stamp(c, 4);
 
     // phase G: reduced slices from every rank's `red` into my output
     if (a.do_gather && out != nullptr) {
@@ -334,15 +410,18 @@ __global__ void __launch_bounds__(512) reduce_family_kernel(const ReduceArgs a) 
             const int q = (rank + qq) % n;
             uint64_t qb, qe;
             sub_range(q, &qb, &qe);
-            cta_copy(out + (static_cast<uint64_t>(q) * se + qb) * esz_out,
+            cta_copy(g, out + (static_cast<uint64_t>(q) * se + qb) * esz_out,
                      c.peers.heap[q] + a.red_off + qb * esz_out, (qe - qb) * esz_out);
         }
     }
+    stamp(c, 5);
 }
 
 // ------------------------------------------------------------------ exchange family
 __global__ void __launch_bounds__(512) exchange_family_kernel(const ExchangeArgs a) {
     const CommonArgs& c = a.c;
+    const Guard g = make_guard(c);
+    stamp(c, 0);
     const int n = c.nranks, rank = c.rank;
     char* const my_heap = c.peers.heap[rank];
     const char* in = static_cast<const char*>(a.in);
@@ -361,13 +440,13 @@ __global__ void __launch_bounds__(512) exchange_family_kernel(const ExchangeArgs
         sub_range(a.chunk_bytes, &b, &e);
         for (int jj = 0; jj < n; ++jj) {
             const int j = (rank + 1 + jj) % n;
-            cta_copy(c.peers.heap[j] + a.pub_off + rank * chunk_stride + b,
+            cta_copy(g, c.peers.heap[j] + a.pub_off + rank * chunk_stride + b,
                      in + static_cast<uint64_t>(a.push_chunk[j]) * a.in_pitch + b, e - b);
         }
         if (!cta_barrier(c, ++epoch))
             return;
         for (int q = 0; q < n; ++q)
-            cta_copy(out + static_cast<uint64_t>(q) * a.out_pitch + b, my_heap + a.pub_off + q * chunk_stride + b,
+            cta_copy(g, out + static_cast<uint64_t>(q) * a.out_pitch + b, my_heap + a.pub_off + q * chunk_stride + b,
                      e - b);
         return;
     }
@@ -378,14 +457,14 @@ __global__ void __launch_bounds__(512) exchange_family_kernel(const ExchangeArgs
             const int j = (rank + 1 + jj) % n;
             uint64_t b, e;
             sub_range(a.pull_bytes[j], &b, &e);
-            cta_copy(c.peers.heap[j] + a.pub_off + b, in + static_cast<uint64_t>(j) * a.in_pitch + b,
+            cta_copy(g, c.peers.heap[j] + a.pub_off + b, in + static_cast<uint64_t>(j) * a.in_pitch + b,
                      e - b);
         }
     } else if (a.push_root < 0) {
         uint64_t b, e;
         sub_range(a.chunk_bytes, &b, &e);
         for (int k = 0; k < a.publish_chunks; ++k)
-            cta_copy(my_heap + a.pub_off + k * chunk_stride + b,
+            cta_copy(g, my_heap + a.pub_off + k * chunk_stride + b,
                      in + static_cast<uint64_t>(k) * a.in_pitch + b, e - b);
     }
     if (!cta_barrier(c, ++epoch))
@@ -400,7 +479,7 @@ __global__ void __launch_bounds__(512) exchange_family_kernel(const ExchangeArgs
             continue;
         uint64_t b, e;
         sub_range(a.pull_bytes[q], &b, &e);
-        cta_copy(out + static_cast<uint64_t>(a.dst_chunk[q]) * a.out_pitch + b,
+        cta_copy(g, out + static_cast<uint64_t>(a.dst_chunk[q]) * a.out_pitch + b,
                  c.peers.heap[q] + a.pub_off + static_cast<uint64_t>(a.src_chunk[q]) * chunk_stride + b,
                  e - b);
     }
@@ -490,6 +569,33 @@ __global__ void __launch_bounds__(512) ll_family_kernel(const LLArgs a) {
     const char* in = static_cast<const char*>(a.in);
     char* out = static_cast<char*>(a.out);
     char* const my_slots = c.peers.heap[rank] + a.slot_off;
+    const Guard g = make_guard(c);
+    stamp(c, 0);
+#ifdef MEGRAY_DEBUG_BOUNDS
+    {
+        // every range this kernel will touch, checked once: the slots it writes and reads, the
+        // parts of `in` it sends and of `out` it fills
+        bool fine = true;
+        for (int j = 0; j < n && fine; ++j) {
+            if ((a.send_mask >> j) & 1u)
+                fine = GUARD_OK(g, c.peers.heap[j] + a.slot_off + static_cast<uint64_t>(rank) * kLLSlotBytes, units * 32) &&
+                       GUARD_OK(g, in + a.send_off[j], a.bytes);
+            if (fine && ((a.recv_mask >> j) & 1u)) {
+                fine = GUARD_OK(g, my_slots + static_cast<uint64_t>(j) * kLLSlotBytes, units * 32);
+                if (fine && !a.reduce && out != nullptr)
+                    fine = GUARD_OK(g, out + a.recv_off[j], a.bytes);
+            }
+        }
+        if (fine && a.self)
+            fine = GUARD_OK(g, in + a.send_off[rank], a.bytes) &&
+                   (out == nullptr || GUARD_OK(g, out + (a.reduce ? 0 : a.recv_off[rank]),
+                                               a.reduce ? a.bytes / sizeof(Tin) * sizeof(Tout) : a.bytes));
+        if (fine && a.reduce && out != nullptr)
+            fine = GUARD_OK(g, out, a.bytes / sizeof(Tin) * sizeof(Tout));
+        if (!fine)
+            return;
+    }
+#endif
 
     // rooted operations: tell every peer that this rank has started this call
     if (a.tokens && blockIdx.x == 0 && threadIdx.x < static_cast<unsigned>(n) && static_cast<int>(threadIdx.x) != rank) {
@@ -516,6 +622,7 @@ __global__ void __launch_bounds__(512) ll_family_kernel(const LLArgs a) {
             }
         }
     }
+    stamp(c, 1);
     // receive
     bool ok = true;
     if (!a.reduce) {
@@ -601,6 +708,7 @@ __global__ void __launch_bounds__(512) ll_family_kernel(const LLArgs a) {
             }
         }
     }
+    stamp(c, 2);
     // rooted operations: every peer has started this call, so it has finished the previous one on
     // these slots' other parity, which the next call will overwrite
     if (a.tokens && blockIdx.x == 0 && threadIdx.x < static_cast<unsigned>(n) && static_cast<int>(threadIdx.x) != rank) {
@@ -759,10 +867,22 @@ __device__ __forceinline__ bool first_barrier(const DirectArgs& a, uint32_t targ
 // destination) or, when `single` is null, to out[q] + out_byte0 + i of every rank.  `vec`: every
 // address involved is 16-byte aligned, so the 16-byte path applies; otherwise element by element.
 template <typename Tin, typename Tout, int OP, bool NVLS>
-__device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, const CallBufs& cb, uint64_t in_byte0,
-                                                    uint64_t out_byte0, uint64_t nelem, char* single, bool vec,
-                                                    bool mc_in, bool mc_out) {
+__device__ __forceinline__ void direct_reduce_range(const Guard& g, const DirectArgs& a, const CallBufs& cb,
+                                                    uint64_t in_byte0, uint64_t out_byte0, uint64_t nelem,
+                                                    char* single, bool vec, bool mc_in, bool mc_out) {
     using A = typename Acc<Tin>::type;
+#ifdef MEGRAY_DEBUG_BOUNDS
+    if (nelem == 0)
+        return;
+    for (int q = 0; q < a.c.nranks; ++q) {
+        if (!GUARD_OK(g, cb.in[q] + in_byte0, nelem * sizeof(Tin)))
+            return;
+        if (single == nullptr && !GUARD_OK(g, cb.out[q] + out_byte0, nelem * sizeof(Tout)))
+            return;
+    }
+    if (single != nullptr && !GUARD_OK(g, single, nelem * sizeof(Tout)))
+        return;
+#endif
     constexpr int V = 16 / sizeof(Tin);
     constexpr int OB = V * sizeof(Tout);
     const int n = a.c.nranks;
@@ -879,14 +999,21 @@ __device__ __forceinline__ void direct_reduce_range(const DirectArgs& a, const C
 // Copy [0, nbytes) of `src` to the same range of up to n destinations, reading the source once:
 // every 16-byte vector goes to all destinations before the next one is touched, so all links
 // carry traffic at every moment (dst[j] == nullptr is skipped).
-__device__ __forceinline__ void cta_fanout(char* const* dst, int ndst, const char* src, uint64_t nbytes,
-                                           bool vec) {
+__device__ __forceinline__ void cta_fanout(const Guard& g, char* const* dst, int ndst, const char* src,
+                                           uint64_t nbytes, bool vec) {
     if (nbytes == 0)
         return;
+#ifdef MEGRAY_DEBUG_BOUNDS
+    if (!GUARD_OK(g, src, nbytes))
+        return;
+    for (int j = 0; j < ndst; ++j)
+        if (dst[j] != nullptr && !GUARD_OK(g, dst[j], nbytes))
+            return;
+#endif
     if (!vec || (nbytes & 15)) {
         for (int j = 0; j < ndst; ++j)
             if (dst[j] != nullptr)
-                cta_copy(dst[j], src, nbytes);
+                cta_copy(g, dst[j], src, nbytes);
         return;
     }
     const uint64_t nv = nbytes / 16;
@@ -916,14 +1043,19 @@ __device__ __forceinline__ void cta_fanout(char* const* dst, int ndst, const cha
 
 // Copy [0, nbytes) of src[j] to dst[j] for up to n pairs, one vector of every pair in flight at
 // a time (all_to_all, scatter: a different source chunk for every destination).
-__device__ __forceinline__ void cta_pairs(char* const* dst, const char* const* src, int npairs, uint64_t nbytes,
-                                          bool vec) {
+__device__ __forceinline__ void cta_pairs(const Guard& g, char* const* dst, const char* const* src, int npairs,
+                                          uint64_t nbytes, bool vec) {
     if (nbytes == 0)
         return;
+#ifdef MEGRAY_DEBUG_BOUNDS
+    for (int j = 0; j < npairs; ++j)
+        if (dst[j] != nullptr && (!GUARD_OK(g, dst[j], nbytes) || !GUARD_OK(g, src[j], nbytes)))
+            return;
+#endif
     if (!vec || (nbytes & 15)) {
         for (int j = 0; j < npairs; ++j)
             if (dst[j] != nullptr)
-                cta_copy(dst[j], src[j], nbytes);
+                cta_copy(g, dst[j], src[j], nbytes);
         return;
     }
     const uint64_t nv = nbytes / 16;
@@ -957,9 +1089,18 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
     const int n = c.nranks, rank = c.rank;
     constexpr uint64_t V = 16 / sizeof(Tin);
     uint32_t epoch = c.epoch;
+    stamp(c, 0);
     // inputs are final / outputs may be overwritten on every rank
     if (!first_barrier(a, ++epoch, &cb))
         return;
+    stamp(c, 1);
+    Guard g = make_guard(c);
+#ifdef MEGRAY_DEBUG_BOUNDS
+    for (int q = 0; q < n; ++q) {
+        g.peer_in[q] = cb.in[q];
+        g.peer_out[q] = cb.out[q];
+    }
+#endif
     const char* const my_in = cb.in[rank];
     char* const my_out = cb.out[rank];
     if (a.kind == DIRECT_ALL_GATHER || a.kind == DIRECT_GATHER) {
@@ -969,8 +1110,9 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
         const uint64_t b = min(bytes, per_cta * blockIdx.x), e = min(bytes, b + per_cta);
         const bool vec = cb.out_vec && ((reinterpret_cast<uint64_t>(my_in) | bytes) & 15) == 0;
         if (a.kind == DIRECT_GATHER) {
-            cta_copy(cb.out[a.root] + rank * bytes + b, my_in + b, e - b);
-        } else if (NVLS && cb.out_sym && vec) {
+            cta_copy(g, cb.out[a.root] + rank * bytes + b, my_in + b, e - b);
+        } else if (NVLS && cb.out_sym && vec && GUARD_OK(g, my_out + rank * bytes + b, e - b) &&
+                   GUARD_OK(g, my_in + b, e - b)) {
             char* dst = a.mc_base + cb.out_off + rank * bytes;
             const uint64_t nv = (e - b) / 16;
             for (uint64_t i = threadIdx.x; i < nv; i += blockDim.x)
@@ -980,7 +1122,7 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
 #pragma unroll
             for (int j = 0; j < kMaxRanks; ++j)
                 dst[j] = j < n ? cb.out[(rank + 1 + j) % n] + rank * bytes + b : nullptr;
-            cta_fanout(dst, n, my_in + b, e - b, vec);
+            cta_fanout(g, dst, n, my_in + b, e - b, vec);
         }
     } else if (a.kind == DIRECT_ALL_TO_ALL || a.kind == DIRECT_SCATTER) {
         // chunk q of the input into slot `rank` of rank q's output (all_to_all) or into rank q's
@@ -999,7 +1141,7 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                 dst[j] = j < n ? cb.out[q] + slot + b : nullptr;
                 src[j] = j < n ? my_in + q * bytes + b : nullptr;
             }
-            cta_pairs(dst, src, n, e - b, vec);
+            cta_pairs(g, dst, src, n, e - b, vec);
         }
     } else if (a.kind == DIRECT_BROADCAST) {
         const uint64_t S = a.len * sizeof(Tin);
@@ -1010,9 +1152,9 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
             const uint64_t b = min(S, per_cta * blockIdx.x), e = min(S, b + per_cta);
             if (rank == root) {
                 if (n == 2)
-                    cta_copy(cb.out[1 - rank] + b, my_in + b, e - b);
+                    cta_copy(g, cb.out[1 - rank] + b, my_in + b, e - b);
                 if (my_out != my_in)
-                    cta_copy(my_out + b, my_in + b, e - b);
+                    cta_copy(g, my_out + b, my_in + b, e - b);
             }
         } else {
             const BcastPlan pl = bcast_plan(S, n, gridDim.x, a.chunk_bytes);
@@ -1025,29 +1167,53 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                 *hi = min(L, min(sb + pl.per_cta, sb + static_cast<uint64_t>(k + 1) * a.chunk_bytes));
             };
             if (rank == root) {
+                // The last warp only announces: the other warps store chunk after chunk without
+                // ever waiting for a store to be acknowledged.  After each (chunk, slice) they
+                // arrive on one of eight named barriers in turn; the announcing warp waits on it
+                // and then publishes the chunk counter with a releasing store, which is what takes
+                // a round trip.  (The copying warps would have to get eight pieces ahead of the
+                // announcing warp to arrive twice on one barrier; a piece takes several round trips.)
+                constexpr int kSigBarriers = 8;
+                const unsigned ncopy = blockDim.x - 32;
+                const bool announcer = threadIdx.x >= ncopy;
+                uint32_t piece = 0;
                 for (uint32_t k = 0; k < pl.chunks; ++k) {
-                    for (int v = 0; v < n - 1; ++v) {
+                    // slice by slice, starting with a different one in every round; each forwarder
+                    // learns of its chunk as soon as that chunk (not the whole round) has been stored
+                    for (int vv = 0; vv < n - 1; ++vv) {
+                        const int v = (vv + static_cast<int>(k)) % (n - 1);
                         const int j = (root + 1 + v) % n;
+                        const int bar_id = 1 + static_cast<int>(piece % kSigBarriers);
                         uint64_t lo, hi;
                         chunk_range(v, k, &lo, &hi);
-                        if (hi > lo)
-                            cta_copy(cb.out[j] + v * pl.slice + lo, my_in + v * pl.slice + lo, hi - lo);
-                    }
-                    __syncthreads();
-                    if (threadIdx.x < static_cast<unsigned>(n - 1)) {
-                        const int j = (root + 1 + threadIdx.x) % n;
-                        __threadfence_system();
-                        st_release_sys(reinterpret_cast<uint32_t*>(c.peers.heap[j] + kChunkFlagOff) + blockIdx.x,
-                                       a.chunk_base + k + 1);
+                        if (hi <= lo)
+                            continue;  // nothing of this slice in this chunk: the forwarder does not wait for it
+                        if (!announcer) {
+                            cta_copy_part(g, cb.out[j] + v * pl.slice + lo, my_in + v * pl.slice + lo, hi - lo,
+                                          threadIdx.x, ncopy);
+                            // every eighth piece the copying warps wait for the announcing warp, so
+                            // that they can never arrive twice on a barrier it has not passed yet
+                            if (piece % kSigBarriers == kSigBarriers - 1)
+                                named_bar_sync(bar_id, blockDim.x);
+                            else
+                                named_bar_arrive(bar_id, blockDim.x);
+                        } else {
+                            named_bar_sync(bar_id, blockDim.x);
+                            if (threadIdx.x == ncopy)
+                                st_release_sys(reinterpret_cast<uint32_t*>(c.peers.heap[j] + kChunkFlagOff) + blockIdx.x,
+                                               a.chunk_base + k + 1);
+                        }
+                        ++piece;  // (pieces that exist: both roles count alike)
                     }
                 }
+                __syncthreads();
                 if (my_out != my_in) {
                     for (int v = 0; v < n - 1; ++v) {
                         const uint64_t s0 = static_cast<uint64_t>(v) * pl.slice;
                         const uint64_t L = s0 >= S ? 0 : min(pl.slice, S - s0);
                         const uint64_t lo = min(L, sb), hi = min(L, sb + pl.per_cta);
                         if (hi > lo)
-                            cta_copy(my_out + s0 + lo, my_in + s0 + lo, hi - lo);
+                            cta_copy(g, my_out + s0 + lo, my_in + s0 + lo, hi - lo);
                     }
                 }
             } else {
@@ -1055,6 +1221,10 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                 const uint32_t* my_flag =
                         reinterpret_cast<const uint32_t*>(c.peers.heap[rank] + kChunkFlagOff) + blockIdx.x;
                 for (uint32_t k = 0; k < pl.chunks; ++k) {
+                    uint64_t lo, hi;
+                    chunk_range(v, k, &lo, &hi);
+                    if (hi <= lo)
+                        continue;  // (uniform over the CTA) nothing to wait for, nothing to forward
                     if (threadIdx.x == 0) {
                         const uint32_t target = a.chunk_base + k + 1;
                         int ok = 1;
@@ -1078,9 +1248,7 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                     __syncthreads();
                     if (!s_ok)
                         return;
-                    uint64_t lo, hi;
-                    chunk_range(v, k, &lo, &hi);
-                    if (hi > lo && n > 2) {
+                    if (n > 2) {
                         char* dst[kMaxRanks];
                         const char* src = my_out + v * pl.slice + lo;
                         bool vec = (reinterpret_cast<uint64_t>(src) & 15) == 0;
@@ -1091,19 +1259,31 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                             if (dst[j] != nullptr && (reinterpret_cast<uint64_t>(dst[j]) & 15))
                                 vec = false;
                         }
-                        cta_fanout(dst, n - 1, src, hi - lo, vec);
+                        cta_fanout(g, dst, n - 1, src, hi - lo, vec);
                     }
                     __syncthreads();  // s_ok is rewritten in the next round
                 }
             }
         }
     } else {
-        // all_reduce / reduce: len is cut into n slices of se elements and this rank reduces
-        // slice `rank`; reduce_scatter: its slice is the rank-th block of len elements
+        // all_reduce: len is cut into n slices of se elements and this rank reduces slice `rank`;
+        // reduce_scatter: its slice is the rank-th block of len elements; reduce: n - 1 slices, one
+        // per non-root rank, so that the root's links carry only its input (out) and the result
+        // (in), not a slice's operands as well
         uint64_t se, elem0, L;
         if (a.kind == DIRECT_REDUCE_SCATTER) {
             elem0 = a.len * rank;
             L = a.len;
+        } else if (a.kind == DIRECT_REDUCE && n > 1) {
+            if (rank == a.root) {
+                elem0 = 0;
+                L = 0;
+            } else {
+                const int v = (rank - a.root - 1 + n) % n;
+                se = round_up_u64((a.len + n - 2) / (n - 1), V);
+                elem0 = min(a.len, se * v);
+                L = min(a.len, elem0 + se) - elem0;
+            }
         } else {
             se = round_up_u64((a.len + n - 1) / n, V);
             elem0 = min(a.len, se * rank);
@@ -1128,20 +1308,22 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
         const bool mc_out = NVLS && cb.out_sym && vec && single == nullptr;
         switch (a.op) {
             case MegRay::MEGRAY_SUM:
-                direct_reduce_range<Tin, Tout, MegRay::MEGRAY_SUM, NVLS>(a, cb, in_byte0, out_byte0, e - b, single, vec,
+                direct_reduce_range<Tin, Tout, MegRay::MEGRAY_SUM, NVLS>(g, a, cb, in_byte0, out_byte0, e - b, single, vec,
                                                                          mc_in, mc_out);
                 break;
             case MegRay::MEGRAY_MAX:
-                direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MAX, NVLS>(a, cb, in_byte0, out_byte0, e - b, single, vec,
+                direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MAX, NVLS>(g, a, cb, in_byte0, out_byte0, e - b, single, vec,
                                                                          mc_in, mc_out);
                 break;
             default:
-                direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MIN, NVLS>(a, cb, in_byte0, out_byte0, e - b, single, vec,
+                direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MIN, NVLS>(g, a, cb, in_byte0, out_byte0, e - b, single, vec,
                                                                          mc_in, mc_out);
         }
     }
+    stamp(c, 2);
     // all transfers are complete before any rank uses its output or overwrites its input
     cta_barrier(c, ++epoch);
+    stamp(c, 3);
 }
 
 // ------------------------------------------------------------------ stand-alone reduce_n

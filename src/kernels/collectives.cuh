@@ -49,6 +49,11 @@ constexpr uint64_t kBarrierFlagOff = 0;      // [kMaxCtas][kMaxRanks] u32: per-C
 constexpr uint64_t kChunkFlagOff = 4096;     // [kMaxCtas] u32: chunk counters of the pipelined broadcast
 constexpr uint64_t kExchangeOff = 8192;      // [2][kMaxRanks] x 16 bytes: the buffers of the current call
 constexpr uint64_t kTokenOff = 8192 + 512;   // [2][kMaxRanks] x 8 bytes: tokens of the small-message kernel
+constexpr uint64_t kDebugOff = 8192 + 1024;  // bounds-checked build: the first access it refused
+                                             // {u64 address, u64 bytes, u32 source line, u32 rank}
+constexpr uint64_t kPhaseOff = 8192 + 2048;  // kMaxPhases x u64: %globaltimer stamps of CTA 0 (phase mode)
+constexpr int kMaxPhases = 8;
+constexpr int kStatusOutOfBounds = 14;       // MegRay::MEGRAY_OUT_OF_BOUNDS
 // Small-message (flagged word) slots follow the pad: [2 parities][kMaxRanks sources] slots, each
 // holding kLLMaxBytes of payload as 8-byte {data, flag} words.
 constexpr uint64_t kLLMaxBytes = 1024 * 1024;
@@ -68,6 +73,18 @@ struct CommonArgs {
     uint64_t timeout_ns;   // limit of one wait
     int* status;           // device-visible status word (0 = ok)
     uint64_t flag_off;     // byte offset of the flag rows inside the heap
+    uint64_t heap_bytes;   // size of every rank's heap
+    int phases;            // 1: CTA 0 stamps %globaltimer at every phase boundary (pad, kPhaseOff)
+    // Extents of this call's buffers, for builds with MEGRAY_DEBUG_BOUNDS: every CTA-level copy or
+    // reduction first checks that the range it is about to touch lies in some rank's heap or in
+    // one of these buffers; a range that does not is skipped and recorded (pad, kDebugOff) and
+    // the status word becomes MEGRAY_OUT_OF_BOUNDS.  0 = extent unknown (nothing may touch it).
+    const void* guard_in;
+    const void* guard_out;
+    uint64_t guard_in_bytes;
+    uint64_t guard_out_bytes;
+    uint64_t guard_peer_in_bytes;   // exchanged buffers: what a peer's input / output holds
+    uint64_t guard_peer_out_bytes;
 };
 
 struct ReduceArgs {

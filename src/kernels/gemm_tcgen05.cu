@@ -518,7 +518,16 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
         const int ok = p.N - col;
         const bool lane_ok = row_ok && ok > 0;
         uint32_t pk[16], pk2[16];
-        if (EPI == EPI_STORE) {
+        if (EPI == EPI_STORE_F32) {
+            // the accumulator's own bits: two boxes of 16 float columns per 32-column chunk
+            if (!zero_tile)
+                tmem_ld_wait(r);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                pk[i] = lane_ok || row_ok ? r[i] : 0u;
+                pk2[i] = lane_ok || row_ok ? r[16 + i] : 0u;
+            }
+        } else if (EPI == EPI_STORE) {
             if (!zero_tile)
                 tmem_ld_wait(r);
 #pragma unroll
@@ -587,6 +596,8 @@ __device__ __forceinline__ void epilogue_tile(const KParams& p, const Tile& tl, 
             emit_box32(out.map_d, out, lane, col, box_row, pk);
             if (EPI == EPI_DSWIGLU)
                 emit_box32(out.map_du, out, lane, col, box_row, pk2);
+            if (EPI == EPI_STORE_F32 && ok > 16)
+                emit_box32(out.map_d, out, lane, col + 16, box_row, pk2);
         }
     }
 }
@@ -1129,16 +1140,17 @@ bool make_map(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer,
     return r == CUDA_SUCCESS;
 }
 
-// Output matrix for the TMA-store epilogues: box = 32 columns (64 B, the swizzle span) x 32 rows.
-bool make_out_map(CUtensorMap* map, const void* ptr, uint64_t cols, uint64_t rows, uint64_t ld) {
+// Output matrix for the TMA-store epilogues: box = 32 columns (64 B, the swizzle span) x 32 rows;
+// for a float32 matrix 16 columns x 32 rows (the same 64-byte rows).
+bool make_out_map(CUtensorMap* map, const void* ptr, uint64_t cols, uint64_t rows, uint64_t ld, bool f32 = false) {
     auto fn = get_encode_fn();
     if (fn == nullptr)
         return false;
     cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {ld * 2};
-    cuuint32_t box[2] = {32, 32};
+    cuuint64_t strides[1] = {ld * (f32 ? 4u : 2u)};
+    cuuint32_t box[2] = {f32 ? 16u : 32u, 32};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+    CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
                     CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
@@ -1230,6 +1242,8 @@ cudaError_t launch_e(int epi, const Maps& maps, const KParams& kp, int workers, 
             return launch_t<MODE, A_MN, B_MN, EPI_PUSH>(maps, kp, workers, stream);
         case EPI_STORE_ROWS:
             return launch_t<MODE, A_MN, B_MN, EPI_STORE_ROWS>(maps, kp, workers, stream);
+        case EPI_STORE_F32:
+            return launch_t<MODE, A_MN, B_MN, EPI_STORE_F32>(maps, kp, workers, stream);
         case EPI_DSWIGLU:
             return launch_t<MODE, A_MN, B_MN, EPI_DSWIGLU>(maps, kp, workers, stream);
         case EPI_SWIGLU:
@@ -1453,7 +1467,7 @@ cudaError_t launch_gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     } else {
         if (grouped_k && (a.M % tile_m))
             return cudaErrorInvalidValue;
-        ok = make_out_map(&maps.d, a.D, a.N, out_rows, a.ldd);
+        ok = make_out_map(&maps.d, a.D, a.N, out_rows, a.ldd, epi == EPI_STORE_F32);
         maps.du = maps.d2 = maps.d;
         if (ok && (epi == EPI_SWIGLU || epi == EPI_DSWIGLU)) {
             if (a.aux_off % 8)

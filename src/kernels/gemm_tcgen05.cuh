@@ -21,6 +21,8 @@ enum Epilogue : int {
     EPI_ACCUM = 3,    // D = acc + D (bf16 read-modify-write; used for gradient accumulation)
     EPI_PUSH = 4,     // D row blocks live on different GPUs: row r goes to peer_out[r / rows_per_peer]
     EPI_STORE_ROWS = 5,  // D = acc, written as whole 128-byte row segments through shared memory
+    EPI_STORE_F32 = 6,   // D = acc as float32 (D is a float matrix, ldd in float elements): the partial
+                         // products of a K split, which are summed before anything is rounded to bf16
 };
 
 // One m-block of a grouped (per-expert) problem.

@@ -97,15 +97,13 @@ __global__ void __launch_bounds__(256) route_bwd_kernel(const int* __restrict__ 
 }
 
 // ---------------------------------------------------------------- plan: one block
-__global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ counts_all, int nranks, int rank,
-                                                   int experts, int capacity_rows, PlanOut out) {
-    __shared__ int seg_size[kMaxExperts];   // rows of expert e over all source ranks
-    __shared__ int seg_start[kMaxExperts];  // first row of expert e inside its owner's buffer
-    __shared__ int before_me[kMaxExperts];  // rows of expert e from ranks below this one
-    __shared__ int overflow;
+// counts_all[r * experts + e]: pairs rank r routes to expert e (global or shared memory).
+__device__ __forceinline__ void plan_body(const int* counts_all, int nranks, int rank, int experts, int capacity_rows,
+                                          const PlanOut& out, int* seg_size, int* seg_start, int* before_me,
+                                          int* overflow) {
     const int el = experts / nranks;
     if (threadIdx.x == 0)
-        overflow = 0;
+        *overflow = 0;
     for (int e = threadIdx.x; e < experts; e += blockDim.x) {
         int tot = 0, before = 0;
         for (int r = 0; r < nranks; ++r) {
@@ -128,7 +126,7 @@ __global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ count
             row += (seg_size[e] + kBlockRows - 1) / kBlockRows * kBlockRows;
         }
         if (row > capacity_rows)
-            atomicExch(&overflow, 1);
+            atomicExch(overflow, 1);
         if (d == rank)
             out.total[0] = row;
     }
@@ -156,7 +154,70 @@ __global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ count
     }
     __syncthreads();
     if (threadIdx.x == 0)
-        out.total[1] = overflow;
+        out.total[1] = *overflow;
+}
+
+__global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ counts_all, int nranks, int rank,
+                                                   int experts, int capacity_rows, PlanOut out) {
+    __shared__ int seg_size[kMaxExperts];   // rows of expert e over all source ranks
+    __shared__ int seg_start[kMaxExperts];  // first row of expert e inside its owner's buffer
+    __shared__ int before_me[kMaxExperts];  // rows of expert e from ranks below this one
+    __shared__ int overflow;
+    plan_body(counts_all, nranks, rank, experts, capacity_rows, out, seg_size, seg_start, before_me, &overflow);
+}
+
+// The same plan with the exchange of the counts inside the launch: every rank stores its counts
+// into the peers' small-message slots as 8-byte {count, sequence number} words and polls its own
+// slots until every word carries this call's sequence number (no barrier, no separate all_gather).
+__global__ void __launch_bounds__(256) plan_exchange_kernel(const int* __restrict__ counts, PlanExchange x, int nranks,
+                                                            int rank, int experts, int capacity_rows, PlanOut out) {
+    __shared__ int seg_size[kMaxExperts];
+    __shared__ int seg_start[kMaxExperts];
+    __shared__ int before_me[kMaxExperts];
+    __shared__ int overflow;
+    __shared__ int all[kMaxRanks * kMaxExperts];
+    __shared__ int failed;
+    if (threadIdx.x == 0)
+        failed = 0;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        const int c = counts[e];
+        all[rank * experts + e] = c;
+        for (int qq = 1; qq < nranks; ++qq) {
+            const int q = (rank + qq) % nranks;
+            char* slot = x.heap[q] + x.slot_off + static_cast<uint64_t>(rank) * x.slot_stride + static_cast<uint64_t>(e) * 8;
+            asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(slot), "r"(static_cast<uint32_t>(c)), "r"(x.seq)
+                         : "memory");
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < (nranks - 1) * experts; i += blockDim.x) {
+        const int q = (rank + 1 + i / experts) % nranks, e = i % experts;
+        const char* slot = x.heap[rank] + x.slot_off + static_cast<uint64_t>(q) * x.slot_stride + static_cast<uint64_t>(e) * 8;
+        uint32_t v = 0, f = 0, spins = 0;
+        unsigned long long t0 = 0;
+        for (;;) {
+            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(f) : "l"(slot) : "memory");
+            if (f == x.seq)
+                break;
+            if ((++spins & 255) == 0) {
+                unsigned long long now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (t0 == 0)
+                    t0 = now;
+                else if (now - t0 > x.timeout_ns) {
+                    if (x.status != nullptr)
+                        atomicCAS(x.status, 0, 12);  // MEGRAY_TIMEOUT
+                    failed = 1;
+                    break;
+                }
+            }
+        }
+        all[q * experts + e] = static_cast<int>(v);
+    }
+    __syncthreads();
+    if (failed)
+        return;
+    plan_body(all, nranks, rank, experts, capacity_rows, out, seg_size, seg_start, before_me, &overflow);
 }
 
 __global__ void __launch_bounds__(256) zero_pads_kernel(uint4* __restrict__ buf, int row_vecs,
@@ -189,6 +250,15 @@ __global__ void __launch_bounds__(256) dispatch_kernel(const uint4* __restrict__
         // an expert id that no rank owns names no cursor and no buffer: the (token, slot) is dropped
         const bool in0 = static_cast<unsigned>(e0) < static_cast<unsigned>(experts);
         const bool in1 = static_cast<unsigned>(e1) < static_cast<unsigned>(experts);
+        // The first vectors of the row are requested before the row positions are known: taking a
+        // position is an atomic whose round trip would otherwise sit in front of every row's loads.
+        constexpr int U = 8;
+        const uint4* s = src + static_cast<size_t>(t) * row_vecs;
+        uint4 x[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (lane + 32 * u < row_vecs)
+                x[u] = __ldg(s + lane + 32 * u);
         int row0, row1;
         if (pos_in != nullptr) {
             row0 = pos_in[i0];
@@ -211,7 +281,6 @@ __global__ void __launch_bounds__(256) dispatch_kernel(const uint4* __restrict__
         if (!ok0 && !ok1)
             continue;
         const float s0 = w != nullptr ? w[i0] : 1.f, s1 = w != nullptr ? w[i0 + 1] : 1.f;
-        const uint4* s = src + static_cast<size_t>(t) * row_vecs;
         uint4* d0 = ok0 ? static_cast<uint4*>(dst.p[e0 / local_experts]) + static_cast<size_t>(row0) * row_vecs : nullptr;
         uint4* d1 = ok1 ? static_cast<uint4*>(dst.p[e1 / local_experts]) + static_cast<size_t>(row1) * row_vecs : nullptr;
         auto scaled = [](const uint4& x, float f) {
@@ -222,13 +291,13 @@ __global__ void __launch_bounds__(256) dispatch_kernel(const uint4* __restrict__
             y.w = pack(lo(x.w) * f, hi(x.w) * f);
             return y;
         };
-        constexpr int U = 8;
         for (int v0 = lane; v0 < row_vecs; v0 += 32 * U) {
-            uint4 x[U];
+            if (v0 != lane) {  // (the first batch is already in registers)
 #pragma unroll
-            for (int u = 0; u < U; ++u)
-                if (v0 + 32 * u < row_vecs)
-                    x[u] = __ldg(s + v0 + 32 * u);
+                for (int u = 0; u < U; ++u)
+                    if (v0 + 32 * u < row_vecs)
+                        x[u] = __ldg(s + v0 + 32 * u);
+            }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int v = v0 + 32 * u;
@@ -353,6 +422,16 @@ cudaError_t launch_plan(const int* counts_all, int nranks, int rank, int experts
         capacity_rows % kBlockRows)
         return cudaErrorInvalidValue;
     plan_kernel<<<1, 256, 0, stream>>>(counts_all, nranks, rank, experts, capacity_rows, out);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_plan_exchange(const int* counts, const PlanExchange& x, int nranks, int rank, int experts,
+                                 int capacity_rows, PlanOut out, cudaStream_t stream) {
+    if (nranks < 1 || nranks > kMaxRanks || experts % nranks || experts > kMaxExperts || capacity_rows % kBlockRows ||
+        x.seq == 0 || static_cast<uint64_t>(experts) * 8 > x.slot_stride)
+        return cudaErrorInvalidValue;
+    plan_exchange_kernel<<<1, 256, 0, stream>>>(counts, x, nranks, rank, experts, capacity_rows, out);
     count_launch();
     return cudaGetLastError();
 }

@@ -44,6 +44,20 @@ struct PlanOut {
 cudaError_t launch_plan(const int* counts_all, int nranks, int rank, int experts, int capacity_rows,
                         PlanOut out, cudaStream_t stream);
 
+// The plan with the count exchange inside the launch.  `counts` are this rank's counts; they
+// travel to the peers as flagged 8-byte words through small-message slots of the communicator
+// (heap[q] + slot_off + source rank * slot_stride, reserved for this call together with `seq`).
+struct PlanExchange {
+    char* heap[kMaxRanks];  // every rank's heap as mapped here
+    uint64_t slot_off;
+    uint64_t slot_stride;
+    uint32_t seq;           // this call's flag value (never 0)
+    uint64_t timeout_ns;
+    int* status;            // communicator status word: MEGRAY_TIMEOUT when a wait runs out
+};
+cudaError_t launch_plan_exchange(const int* counts, const PlanExchange& x, int nranks, int rank, int experts,
+                                 int capacity_rows, PlanOut out, cudaStream_t stream);
+
 // Zero the padding rows [seg_begin+seg_rows, seg_end) of every local expert in `buf`.
 cudaError_t launch_zero_pads(void* buf, int row_elems, const int* seg_begin, const int* seg_rows,
                              const int* seg_end, int local_experts, cudaStream_t stream);

@@ -114,6 +114,7 @@ NvlCommunicator::NvlCommunicator(uint32_t nranks, uint32_t rank) : Communicator(
     }
     if (m_cta_bytes < 1024)
         m_cta_bytes = 1024;
+    int64_t bcast_chunk_tuned = -1;
     // small-message limits (payload bytes per source / destination pair), per operation
     static const char* const kKindNames[8] = {"all_reduce", "reduce_scatter", "all_gather", "all_to_all",
                                               "broadcast",  "reduce",         "gather",     "scatter"};
@@ -127,7 +128,17 @@ NvlCommunicator::NvlCommunicator(uint32_t nranks, uint32_t rank) : Communicator(
             v = ll_all;
         m_ll_bytes[k] = std::min<size_t>(static_cast<size_t>(std::max<int64_t>(v, 0)), mgk::coll::kLLMaxBytes);
     }
-    m_bcast_chunk = static_cast<uint32_t>(round_up(static_cast<size_t>(env_i64("MEGRAY_BCAST_CHUNK", 128 * 1024)), 16));
+    m_direct_cta_bytes = static_cast<size_t>(env_i64("MEGRAY_DIRECT_CTA_BYTES", 32 * 1024));
+    if (!tune_text.empty() && getenv("MEGRAY_DIRECT_CTA_BYTES") == nullptr)
+        m_direct_cta_bytes = static_cast<size_t>(json_i64(tune_text, "direct_cta_bytes", static_cast<int64_t>(m_direct_cta_bytes)));
+    if (m_direct_cta_bytes < 4096)
+        m_direct_cta_bytes = 4096;
+    if (!tune_text.empty() && getenv("MEGRAY_BCAST_CHUNK") == nullptr)
+        bcast_chunk_tuned = json_i64(tune_text, "bcast_chunk_bytes", -1);
+    m_phases = env_i64("MEGRAY_PHASES", 0) != 0;
+    m_guard_shrink = env_i64("MEGRAY_DEBUG_BOUNDS_SELFTEST", 0) != 0;
+    m_bcast_chunk = static_cast<uint32_t>(round_up(
+            static_cast<size_t>(bcast_chunk_tuned > 0 ? bcast_chunk_tuned : env_i64("MEGRAY_BCAST_CHUNK", 64 * 1024)), 16));
     if (m_bcast_chunk < 4096)
         m_bcast_chunk = 4096;
     if (o.algo == "oneshot")
@@ -142,6 +153,12 @@ NvlCommunicator::~NvlCommunicator() {
         cudaDeviceSynchronize();
     }
     m_p2p.reset();
+    m_p2p_ctx.reset();
+    if (m_p2p_stream != nullptr) {
+        cudaStreamDestroy(m_p2p_stream);
+        cudaEventDestroy(m_p2p_fork);
+        cudaEventDestroy(m_p2p_done);
+    }
     for (void*& b : m_bounce) {
         if (b != nullptr)
             cudaFree(b);
@@ -217,7 +234,8 @@ Status NvlCommunicator::do_init() {
     if (m_ws_bytes == 0)
         m_ws_bytes = std::min<size_t>(192ull << 20, m_heap.bytes() / 8);
     m_ws_bytes = round_down(m_ws_bytes, 4096);
-    m_user_off = round_up(kWorkspaceOff + 2 * m_ws_bytes, 1 << 20);
+    // canary zones before, between and after the two workspaces
+    m_user_off = round_up(kWorkspaceOff + 3 * kCanaryBytes + 2 * m_ws_bytes, 1 << 20);
     if (m_user_off >= m_heap.bytes()) {
         MEGRAY_ERROR("heap of %zu bytes is too small for two %zu-byte workspaces", m_heap.bytes(),
                      m_ws_bytes);
@@ -225,6 +243,9 @@ Status NvlCommunicator::do_init() {
     }
     m_user_top = m_user_off;
 
+    for (int z = 0; z < 3; ++z)
+        CUDA_CHECK(cudaMemset(m_heap.local() + canary_off(z), kCanaryByte, kCanaryBytes));
+    CUDA_CHECK(cudaDeviceSynchronize());
     CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&m_status_host), 64, cudaHostAllocMapped));
     memset(m_status_host, 0, 64);
     CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&m_status_dev), m_status_host, 0));
@@ -321,12 +342,33 @@ CommonArgs NvlCommunicator::common_args(uint32_t epochs) {
     c.timeout_ns = m_timeout_ns;
     c.status = m_status_dev;
     c.flag_off = kFlagOff;
+    c.heap_bytes = m_heap.bytes();
+    c.phases = m_phases ? 1 : 0;
+    c.guard_in = m_guard.in;
+    c.guard_in_bytes = m_guard.in_bytes;
+    c.guard_out = m_guard.out;
+    c.guard_out_bytes = m_guard.out_bytes;
+    c.guard_peer_in_bytes = m_guard.in_bytes;
+    c.guard_peer_out_bytes = m_guard.out_bytes;
     return c;
 }
 
 Status NvlCommunicator::fused_begin(void* stream) { return begin_on(static_cast<cudaStream_t>(stream)); }
 
 void NvlCommunicator::fused_end(void* stream) { after_launch(static_cast<cudaStream_t>(stream)); }
+
+void NvlCommunicator::set_guard(const void* in, size_t in_bytes, void* out, size_t out_bytes) {
+    m_guard.in = in;
+    m_guard.in_bytes = in != nullptr ? in_bytes : 0;
+    m_guard.out = out;
+    m_guard.out_bytes = out != nullptr ? out_bytes : 0;
+    if (m_guard_shrink) {
+        // self-test of the bounds-checked build: claim that the buffers are half as long as they
+        // are, so that the guard must refuse (and skip) accesses that are in fact harmless
+        m_guard.in_bytes /= 2;
+        m_guard.out_bytes /= 2;
+    }
+}
 
 uint32_t NvlCommunicator::fused_call_count(const void* flags) {
     if (!in_heap(flags, 1))
@@ -341,8 +383,48 @@ uint32_t NvlCommunicator::reserve_epochs(uint32_t count) {
     return e;
 }
 
+size_t NvlCommunicator::canary_off(int zone) const {
+    return kWorkspaceOff + static_cast<size_t>(zone) * (kCanaryBytes + m_ws_bytes);
+}
+
+Status NvlCommunicator::check_canaries() {
+    if (!m_ready)
+        return MEGRAY_INVALID_USAGE;
+    CUDA_CHECK(cudaDeviceSynchronize());
+    std::vector<unsigned char> host(kCanaryBytes);
+    for (int z = 0; z < 3; ++z) {
+        CUDA_CHECK(cudaMemcpy(host.data(), m_heap.local() + canary_off(z), kCanaryBytes, cudaMemcpyDeviceToHost));
+        for (size_t i = 0; i < kCanaryBytes; ++i) {
+            if (host[i] != kCanaryByte) {
+                MEGRAY_ERROR("rank %u: canary zone %d around the staging workspaces was overwritten at byte %zu", m_rank,
+                             z, i);
+                if (m_error == MEGRAY_OK)
+                    m_error = MEGRAY_OUT_OF_BOUNDS;
+                return MEGRAY_OUT_OF_BOUNDS;
+            }
+        }
+    }
+    return MEGRAY_OK;
+}
+
+int NvlCommunicator::read_phase_stamps(uint64_t* out, int max) {
+    if (!m_ready || !m_phases || out == nullptr)
+        return 0;
+    cudaDeviceSynchronize();
+    uint64_t all[mgk::coll::kMaxPhases] = {};
+    if (cudaMemcpy(all, m_heap.local() + mgk::coll::kPhaseOff, sizeof(all), cudaMemcpyDeviceToHost) != cudaSuccess)
+        return 0;
+    // stamps of one kernel increase; a smaller value belongs to an earlier kernel with more phases
+    int n = 0;
+    while (n < mgk::coll::kMaxPhases && n < max && all[n] != 0 && (n == 0 || all[n] >= all[n - 1])) {
+        out[n] = all[n];
+        ++n;
+    }
+    return n;
+}
+
 size_t NvlCommunicator::workspace_off() {
-    const size_t off = kWorkspaceOff + static_cast<size_t>(m_parity) * m_ws_bytes;
+    const size_t off = kWorkspaceOff + kCanaryBytes + static_cast<size_t>(m_parity) * (m_ws_bytes + kCanaryBytes);
     m_parity ^= 1;
     return off;
 }
@@ -408,7 +490,7 @@ Status NvlCommunicator::direct_launch(int kind, const void* in, void* out, size_
     a.mc_base = nvls ? m_heap.multicast() : nullptr;
     a.heap_bytes = m_heap.bytes();
     // single-pass kernels are latency-bound per CTA: smaller shares, more CTAs
-    const int ctas = static_cast<int>(std::min<size_t>(std::max<size_t>(1, bytes / (32u << 10)),
+    const int ctas = static_cast<int>(std::min<size_t>(std::max<size_t>(1, bytes / m_direct_cta_bytes),
                                                        static_cast<size_t>(2 * m_max_ctas > kMaxCtas ? kMaxCtas : 2 * m_max_ctas)));
     MEGRAY_CHECK(check_cuda(mgk::coll::launch_direct(a, ctas, 512, stream)));
     after_launch(stream);
@@ -422,14 +504,21 @@ Status NvlCommunicator::direct_launch(int kind, const void* in, void* out, size_
 
 // ------------------------------------------------------------------ small messages (flagged words)
 
-Status NvlCommunicator::ll_launch(mgk::coll::LLArgs& a, cudaStream_t stream) {
-    a.c = common_args(0);  // no barrier: no epochs
+void NvlCommunicator::ll_ticket(uint32_t* seq, size_t* slot_off, size_t* slot_stride) {
     if (++m_ll_seq == 0)
         m_ll_seq = 1;
-    a.seq = m_ll_seq;
-    const int parity = m_ll_parity;
+    *seq = m_ll_seq;
+    *slot_off = kLLOff + static_cast<size_t>(m_ll_parity) * kMaxRanks * mgk::coll::kLLSlotBytes;
+    *slot_stride = mgk::coll::kLLSlotBytes;
     m_ll_parity ^= 1;
-    a.slot_off = kLLOff + static_cast<size_t>(parity) * kMaxRanks * mgk::coll::kLLSlotBytes;
+}
+
+Status NvlCommunicator::ll_launch(mgk::coll::LLArgs& a, cudaStream_t stream) {
+    a.c = common_args(0);  // no barrier: no epochs
+    const int parity = m_ll_parity;
+    size_t slot_off = 0, slot_stride = 0;
+    ll_ticket(&a.seq, &slot_off, &slot_stride);
+    a.slot_off = slot_off;
     a.token_off = mgk::coll::kTokenOff + static_cast<size_t>(parity) * kMaxRanks * 8;
     const size_t units = (a.bytes + 15) / 16;
     const size_t fan = std::max<size_t>(
@@ -511,6 +600,7 @@ Status NvlCommunicator::exchange_launch(int kind, const void* in, size_t in_byte
         out_use = b;
         copy_back = true;
     }
+    set_guard(in_use, in_bytes, out_use, out_bytes);
     DirectArgs a;
     memset(&a, 0, sizeof(a));
     a.c = common_args();
@@ -540,11 +630,11 @@ Status NvlCommunicator::exchange_launch(int kind, const void* in, size_t in_byte
                        (reducing && mgk::coll::nvls_supports(in_dtype, out_dtype, op)));
     a.mc_base = nvls ? m_heap.multicast() : nullptr;
     const int max_ctas = 2 * m_max_ctas > kMaxCtas ? kMaxCtas : 2 * m_max_ctas;
-    int ctas = static_cast<int>(std::min<size_t>(std::max<size_t>(1, work / (32u << 10)), static_cast<size_t>(max_ctas)));
+    int ctas = static_cast<int>(std::min<size_t>(std::max<size_t>(1, work / m_direct_cta_bytes), static_cast<size_t>(max_ctas)));
     if (kind == mgk::coll::DIRECT_BROADCAST) {
         // a CTA moves its share of every slice in chunks; small shares are not worth a CTA
         const size_t slice = m_nranks > 1 ? (work + m_nranks - 2) / (m_nranks - 1) : work;
-        ctas = static_cast<int>(std::min<size_t>(std::max<size_t>(1, slice / (16u << 10)), static_cast<size_t>(max_ctas)));
+        ctas = static_cast<int>(std::min<size_t>(std::max<size_t>(1, slice / (m_direct_cta_bytes / 2)), static_cast<size_t>(max_ctas)));
         a.chunk_bytes = m_bcast_chunk;
         a.chunk_base = m_chunk_seq;
         m_chunk_seq += mgk::coll::bcast_plan(work, static_cast<int>(m_nranks), ctas, a.chunk_bytes).chunks;
@@ -572,6 +662,7 @@ Status NvlCommunicator::reduce_impl(ReduceKind kind, const void* in, void* out, 
     const bool wants_out = kind != ReduceKind::Reduce || m_rank == root;
     if (in == nullptr || (wants_out && out == nullptr))
         return MEGRAY_INVALID_ARGUMENT;
+    set_guard(in, len * ein * (kind == ReduceKind::ReduceScatter ? n : 1), wants_out ? out : nullptr, len * eout);
 
     // Largest slice (elements) whose n staging slots plus reduced slice fit one workspace.
     const size_t se_max = round_down((m_ws_bytes - 16 * (n + 1)) / (n * ein + eout), 16);
@@ -775,6 +866,7 @@ Status NvlCommunicator::all_gather(const void* sendbuff, void* recvbuff, size_t 
         return MEGRAY_OK;
     if (sendbuff == nullptr || recvbuff == nullptr)
         return MEGRAY_INVALID_ARGUMENT;
+    set_guard(sendbuff, bytes, recvbuff, bytes * m_nranks);
     if (bytes <= ll_limit(mgk::coll::DIRECT_ALL_GATHER)) {
         mgk::coll::LLArgs l;
         memset(&l, 0, sizeof(l));
@@ -835,6 +927,7 @@ Status NvlCommunicator::all_to_all(const void* sendbuff, void* recvbuff, size_t 
         return MEGRAY_OK;
     if (sendbuff == nullptr || recvbuff == nullptr)
         return MEGRAY_INVALID_ARGUMENT;
+    set_guard(sendbuff, bytes * m_nranks, recvbuff, bytes * m_nranks);
     if (bytes <= ll_limit(mgk::coll::DIRECT_ALL_TO_ALL)) {
         mgk::coll::LLArgs l;
         memset(&l, 0, sizeof(l));
@@ -896,6 +989,7 @@ Status NvlCommunicator::broadcast(const void* sendbuff, void* recvbuff, size_t l
         return MEGRAY_OK;
     if (recvbuff == nullptr || (m_rank == root && sendbuff == nullptr))
         return MEGRAY_INVALID_ARGUMENT;
+    set_guard(m_rank == root ? sendbuff : nullptr, bytes, recvbuff, bytes);
     if (bytes <= ll_limit(mgk::coll::DIRECT_BROADCAST)) {
         mgk::coll::LLArgs l;
         memset(&l, 0, sizeof(l));
@@ -970,6 +1064,7 @@ Status NvlCommunicator::gather(const void* sendbuff, void* recvbuff, size_t send
         return MEGRAY_OK;
     if (sendbuff == nullptr || (m_rank == root && recvbuff == nullptr))
         return MEGRAY_INVALID_ARGUMENT;
+    set_guard(sendbuff, bytes, m_rank == root ? recvbuff : nullptr, bytes * m_nranks);
     if (bytes <= ll_limit(mgk::coll::DIRECT_GATHER)) {
         mgk::coll::LLArgs l;
         memset(&l, 0, sizeof(l));
@@ -1031,6 +1126,7 @@ Status NvlCommunicator::scatter(const void* sendbuff, void* recvbuff, size_t rec
         return MEGRAY_OK;
     if (recvbuff == nullptr || (m_rank == root && sendbuff == nullptr))
         return MEGRAY_INVALID_ARGUMENT;
+    set_guard(m_rank == root ? sendbuff : nullptr, bytes * m_nranks, recvbuff, bytes);
     if (bytes <= ll_limit(mgk::coll::DIRECT_SCATTER)) {
         mgk::coll::LLArgs l;
         memset(&l, 0, sizeof(l));
@@ -1080,6 +1176,7 @@ Status NvlCommunicator::scatter(const void* sendbuff, void* recvbuff, size_t rec
 Status NvlCommunicator::stream_barrier(std::shared_ptr<Context> ctx) {
     cudaStream_t stream;
     MEGRAY_CHECK(begin(ctx, &stream));
+    set_guard(nullptr, 0, nullptr, 0);
     ExchangeArgs a;
     memset(&a, 0, sizeof(a));
     a.c = common_args();
@@ -1091,48 +1188,110 @@ Status NvlCommunicator::stream_barrier(std::shared_ptr<Context> ctx) {
 }
 
 // ------------------------------------------------------------------ point to point (NCCL)
+// send / recv run as NCCL point-to-point calls on a stream of the communicator's own.  That
+// stream first waits for the work already on the caller's stream (the data to send is final, the
+// buffer to receive into is free) and the caller's stream then waits for the transfer, so the
+// calls keep the interface's meaning: enqueued on the context's stream, complete in stream order.
+// With set_p2p_async(true) the second wait is left out until p2p_join(): kernels enqueued on the
+// caller's stream in between (native collectives included) run at the same time as the transfer.
 
-Status NvlCommunicator::_send(const void* sendbuff, size_t size, uint32_t rank,
-                              std::shared_ptr<Context> ctx) {
+Status NvlCommunicator::p2p_fork(cudaStream_t user) {
+    if (m_p2p_stream == nullptr) {
+        CUDA_CHECK(cudaStreamCreateWithFlags(&m_p2p_stream, cudaStreamNonBlocking));
+        CUDA_CHECK(cudaEventCreateWithFlags(&m_p2p_fork, cudaEventDisableTiming));
+        CUDA_CHECK(cudaEventCreateWithFlags(&m_p2p_done, cudaEventDisableTiming));
+    }
+    for (cudaStream_t s : m_p2p_users)
+        if (s == user)
+            return MEGRAY_OK;  // this group already waits for that stream
+    CUDA_CHECK(cudaEventRecord(m_p2p_fork, user));
+    CUDA_CHECK(cudaStreamWaitEvent(m_p2p_stream, m_p2p_fork, 0));
+    m_p2p_users.push_back(user);
+    return MEGRAY_OK;
+}
+
+Status NvlCommunicator::p2p_finish() {
+    CUDA_CHECK(cudaEventRecord(m_p2p_done, m_p2p_stream));
+    if (m_p2p_async) {
+        m_p2p_pending = true;
+    } else {
+        for (cudaStream_t s : m_p2p_users)
+            CUDA_CHECK(cudaStreamWaitEvent(s, m_p2p_done, 0));
+    }
+    m_p2p_users.clear();
+    return MEGRAY_OK;
+}
+
+Status NvlCommunicator::p2p_join(std::shared_ptr<Context> ctx) {
+    if (!ctx || ctx->type() != MEGRAY_CTX_CUDA)
+        return MEGRAY_INVALID_ARGUMENT;
+    if (m_p2p_pending) {
+        CUDA_CHECK(cudaStreamWaitEvent(static_cast<CudaContext*>(ctx.get())->get_stream(), m_p2p_done, 0));
+        m_p2p_pending = false;
+    }
+    return MEGRAY_OK;
+}
+
+Status NvlCommunicator::p2p_call(bool is_send, void* buf, size_t size, uint32_t rank,
+                                 const std::shared_ptr<Context>& ctx) {
 #ifdef MEGRAY_WITH_NCCL
     if (!m_p2p)
         return MEGRAY_NOT_IMPLEMENTED;
+    if (!ctx || ctx->type() != MEGRAY_CTX_CUDA)
+        return MEGRAY_INVALID_ARGUMENT;
+    if (m_aborted.load())
+        return MEGRAY_ABORTED;
     m_stats.calls++;
     m_stats.bytes += size;
-    return m_p2p->send(sendbuff, size, MEGRAY_CHAR, rank, ctx);
+    MEGRAY_CHECK(p2p_fork(static_cast<CudaContext*>(ctx.get())->get_stream()));
+    if (!m_p2p_ctx)
+        m_p2p_ctx = CudaContext::make(m_p2p_stream);
+    const Status s = is_send ? m_p2p->send(buf, size, MEGRAY_CHAR, rank, m_p2p_ctx)
+                             : m_p2p->recv(buf, size, MEGRAY_CHAR, rank, m_p2p_ctx);
+    if (s != MEGRAY_OK) {
+        m_p2p_users.clear();
+        return s;
+    }
+    return m_p2p_grouping ? MEGRAY_OK : p2p_finish();
 #else
     return MEGRAY_NOT_IMPLEMENTED;
 #endif
 }
 
+Status NvlCommunicator::_send(const void* sendbuff, size_t size, uint32_t rank,
+                              std::shared_ptr<Context> ctx) {
+    return p2p_call(true, const_cast<void*>(sendbuff), size, rank, ctx);
+}
+
 Status NvlCommunicator::_recv(void* recvbuf, size_t size, uint32_t rank,
                               std::shared_ptr<Context> ctx) {
-#ifdef MEGRAY_WITH_NCCL
-    if (!m_p2p)
-        return MEGRAY_NOT_IMPLEMENTED;
-    m_stats.calls++;
-    m_stats.bytes += size;
-    return m_p2p->recv(recvbuf, size, MEGRAY_CHAR, rank, ctx);
-#else
-    return MEGRAY_NOT_IMPLEMENTED;
-#endif
+    return p2p_call(false, recvbuf, size, rank, ctx);
 }
 
 Status NvlCommunicator::group_start() {
 #ifdef MEGRAY_WITH_NCCL
     // native collectives are single launches and ignore grouping; p2p is batched by NCCL
-    return m_p2p ? m_p2p->group_start() : MEGRAY_OK;
-#else
-    return MEGRAY_OK;
+    if (m_p2p) {
+        m_p2p_grouping = true;
+        return m_p2p->group_start();
+    }
 #endif
+    return MEGRAY_OK;
 }
 
 Status NvlCommunicator::group_end() {
 #ifdef MEGRAY_WITH_NCCL
-    return m_p2p ? m_p2p->group_end() : MEGRAY_OK;
-#else
-    return MEGRAY_OK;
+    if (m_p2p) {
+        m_p2p_grouping = false;
+        const Status s = m_p2p->group_end();
+        if (s != MEGRAY_OK) {
+            m_p2p_users.clear();
+            return s;
+        }
+        return m_p2p_users.empty() ? MEGRAY_OK : p2p_finish();
+    }
 #endif
+    return MEGRAY_OK;
 }
 
 // ------------------------------------------------------------------ state

@@ -72,9 +72,14 @@ public:
                              DType out_dtype, float scale, ReduceOp op,
                              std::shared_ptr<Context> ctx) override;
     Status stream_barrier(std::shared_ptr<Context> ctx) override;
+    Status check_canaries() override;
+    int read_phase_stamps(uint64_t* out, int max) override;
+    void set_p2p_async(bool on) override { m_p2p_async = on; }
+    Status p2p_join(std::shared_ptr<Context> ctx) override;
     Status fused_begin(void* stream) override;
     void fused_end(void* stream) override;
     uint32_t fused_call_count(const void* flags) override;
+    void ll_ticket(uint32_t* seq, size_t* slot_off, size_t* slot_stride) override;
     uint32_t reserve_epochs(uint32_t count) override;
     size_t fused_flag_offset() override { return kFusedFlagOff; }
     int* status_word() override { return m_status_dev; }
@@ -101,6 +106,11 @@ private:
                        cudaStream_t stream);
     mgk::coll::CommonArgs common_args(uint32_t epochs = 2);
     size_t workspace_off();  // offset of the workspace this launch uses; flips the parity
+    // Guard zones of kCanaryBytes, filled with kCanaryByte at init, lie before, between and after
+    // the two staging workspaces; nothing ever writes there, and check_canaries() verifies it.
+    static constexpr size_t kCanaryBytes = 4096;
+    static constexpr unsigned char kCanaryByte = 0xC5;
+    size_t canary_off(int zone) const;
     void after_launch(cudaStream_t stream);
     int pick_ctas(size_t bytes) const;
     bool aligned_heap(const void* p, size_t bytes);
@@ -127,7 +137,12 @@ private:
                            uint32_t root, cudaStream_t stream);
     // Small-message kernel; `a` comes filled with the operation's send / receive pattern.
     Status ll_launch(mgk::coll::LLArgs& a, cudaStream_t stream);
+    Status p2p_call(bool is_send, void* buf, size_t size, uint32_t rank, const std::shared_ptr<Context>& ctx);
+    Status p2p_fork(cudaStream_t user);
+    Status p2p_finish();
     bool peer_addressable(const void* p, size_t bytes);
+    // extents of the current call's buffers, handed to the kernels (see CommonArgs::guard_in)
+    void set_guard(const void* in, size_t in_bytes, void* out, size_t out_bytes);
     void* bounce(int which, size_t bytes);
     size_t ll_limit(int kind) const { return m_ll_bytes[kind]; }
     Status check_cuda(cudaError_t e);
@@ -135,6 +150,14 @@ private:
     SymmetricHeap m_heap;
     std::unique_ptr<Server> m_own_server;  // init(BcastCallback): private rendezvous
     std::unique_ptr<NcclCommunicator> m_p2p;
+    // send / recv: a stream of the communicator's own, forked from and joined to the caller's
+    cudaStream_t m_p2p_stream = nullptr;
+    cudaEvent_t m_p2p_fork = nullptr, m_p2p_done = nullptr;
+    std::shared_ptr<Context> m_p2p_ctx;
+    std::vector<cudaStream_t> m_p2p_users;  // callers' streams of the open group
+    bool m_p2p_grouping = false;
+    bool m_p2p_async = false;
+    bool m_p2p_pending = false;
     bool m_ready = false;
     size_t m_ws_bytes = 0;   // bytes of one staging workspace
     size_t m_user_off = 0;   // first byte of the symmetric allocator's area
@@ -149,10 +172,19 @@ private:
     size_t m_oneshot_bytes;
     size_t m_nvls_min_bytes = 0;
     size_t m_cta_bytes = 128 * 1024;  // message bytes per CTA when sizing a collective's grid
+    size_t m_direct_cta_bytes = 32 * 1024;  // the same for the single-pass kernels
     bool m_direct = true;
     // Ranks that are threads of one process, with peer access enabled between all their devices:
     // every collective above the small-message limit runs the single-pass kernels on the user's
     // buffers (MEGRAY_EXCHANGE=0 turns it off).
+    struct {
+        const void* in = nullptr;
+        size_t in_bytes = 0;
+        void* out = nullptr;
+        size_t out_bytes = 0;
+    } m_guard;
+    bool m_guard_shrink = false;
+    bool m_phases = false;  // MEGRAY_PHASES=1: kernels stamp %globaltimer at their phase boundaries
     bool m_xchg = false;
     int m_xchg_parity = 0;
     uint32_t m_ll_seq = 0;      // small-message calls so far

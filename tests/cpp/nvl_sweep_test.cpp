@@ -9,6 +9,7 @@
 // the order of the additions: results must match bit for bit.
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <functional>
@@ -237,6 +238,9 @@ void sweep_rank(int n, int rank, int port, const std::vector<size_t>& lens, size
     if (comm->status() != MEGRAY_OK)
         fails.add("communicator status " + std::to_string(comm->status()) + " on rank " + std::to_string(rank));
     const CommStats st = comm->stats();
+    NvlInterface* nvl = as_nvl(comm.get());
+    if (nvl == nullptr || nvl->check_canaries() != MEGRAY_OK)
+        fails.add("a guard zone around the staging workspaces was overwritten on rank " + std::to_string(rank));
     if (st.algo_ll == 0 || st.algo_direct == 0)
         fails.add("expected both the flagged-word and the single-pass kernels to run: ll " + std::to_string(st.algo_ll) +
                   " direct " + std::to_string(st.algo_direct));
@@ -282,4 +286,42 @@ TEST(Nvl_AllOperationsOnPlainBuffersAgainstHostValues) {
     run_sweep(n);
     if (n > 3)
         run_sweep(3);  // an odd group: slices and chunk shares that do not divide evenly
+}
+
+// The range guard of a build with MEGRAY_DEBUG_BOUNDS, exercised without any access that is really
+// out of bounds: with MEGRAY_DEBUG_BOUNDS_SELFTEST=1 the communicator tells its kernels that the
+// call's buffers are half as long as they are, so the guard must refuse the ranges that reach into
+// the second half (skipping them), record the first one and report MEGRAY_OUT_OF_BOUNDS.  Runs
+// only when the environment says that this binary is such a build.
+TEST(Nvl_RangeGuardRefusesWhatLiesOutsideTheDeclaredBuffers) {
+    if (getenv("MEGRAY_EXPECT_BOUNDS_BUILD") == nullptr || getenv("MEGRAY_DEBUG_BOUNDS_SELFTEST") == nullptr)
+        SKIP("needs the bounds-checked build and its self-test mode");
+    if (device_count() < 1) SKIP("needs a GPU");
+    for (size_t len : {size_t(1000), size_t(1) << 20}) {  // flagged-word kernel, single-pass kernel
+        Server server(1);
+        cudaSetDevice(0);
+        cudaStream_t stream;
+        cudaStreamCreate(&stream);
+        auto ctx = CudaContext::make(stream);
+        auto comm = get_communicator(1, 0, MEGRAY_NVL);
+        ASSERT_TRUE(comm->init("127.0.0.1", server.port()) == MEGRAY_OK);
+        float *in = nullptr, *out = nullptr;
+        cudaMalloc(&in, len * 4);
+        cudaMalloc(&out, len * 4);
+        std::vector<float> h(len, 3.0f);
+        cudaMemcpy(in, h.data(), len * 4, cudaMemcpyHostToDevice);
+        cudaMemset(out, 0, len * 4);
+        EXPECT_EQ(comm->all_reduce(in, out, len, MEGRAY_FLOAT32, MEGRAY_SUM, ctx), MEGRAY_OK);
+        cudaStreamSynchronize(stream);
+        EXPECT_EQ(comm->status(), MEGRAY_OUT_OF_BOUNDS);
+        cudaMemcpy(h.data(), out, len * 4, cudaMemcpyDeviceToHost);
+        EXPECT_EQ(h[len - 1], 0.0f);  // the refused range was not written
+        // the context is intact and a later call is refused with the recorded status
+        EXPECT_EQ(comm->all_reduce(in, out, len, MEGRAY_FLOAT32, MEGRAY_SUM, ctx), MEGRAY_OUT_OF_BOUNDS);
+        EXPECT_EQ(cudaDeviceSynchronize(), cudaSuccess);
+        comm.reset();
+        cudaFree(in);
+        cudaFree(out);
+        cudaStreamDestroy(stream);
+    }
 }

@@ -74,6 +74,7 @@ def test_split_k_choice_follows_the_wave_arithmetic():
     assert pick_split_k(d, F, T) == 1 and pick_split_k(2 * F, d, T) == 1
     # 8-way shard: 224 tiles on 74 CTA pairs would take 4 waves for the work of 3.03
     assert pick_split_k(d, F // 8, T) > 1
-    assert pick_split_k(2 * F // 8, d, T) > 1
+    # 448 tiles lose half a wave in seven: not worth writing and re-reading float32 partial products
+    assert pick_split_k(2 * F // 8, d, T) == 1
     # short K or ragged M: never
     assert pick_split_k(d, F // 8, 2048) == 1 and pick_split_k(d + 8, F // 8, T) == 1

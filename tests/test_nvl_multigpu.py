@@ -96,3 +96,9 @@ def test_fused_call_wait_limit_reports_timeout_and_keeps_the_gpu_usable():
 def test_fused_reduce_scatter_on_a_recreated_communicator():
     out = torchrun("recreate.py", env={"MEGRAY_HEAP_MB": "512"})
     assert out.count("RANK_OK") == NPROC, out[-3000:]
+
+
+def test_send_recv_overlaps_a_native_collective_when_its_join_is_postponed():
+    out = torchrun("p2p_overlap.py", nproc=2)
+    print("\n".join(l for l in out.splitlines() if l.startswith("RANK_OK")))
+    assert out.count("RANK_OK") == 2, out[-3000:]
