@@ -8,7 +8,9 @@ ranks, float32) over the small and middle sizes with each algorithm forced in tu
 operation, the largest size up to which the flagged-word kernel is the fastest; for all_reduce
 also the size up to which the one-shot kernel beats the single-pass one; and, when the NVSwitch
 multicast object can be set up (``--nvls``: MEGRAY_NVLS=1 in the benchmark processes only), the
-size from which the multimem kernels beat plain peer loads and stores on heap buffers.
+size from which the multimem kernels beat plain peer loads and stores on heap buffers.  It also
+picks the grid size, the bytes per CTA of the single-pass kernels, the chunk of the pipelined
+broadcast and the pause of long waits by the summed time over a few sizes.
 
     python bench/tune.py --devices 8 --out megray_b200/tune/tune_b200_n8.json
 """
@@ -87,6 +89,26 @@ def main():
         if t is not None and (best_t is None or t < best_t):
             best_ctas, best_t = ctas, t
     table["max_ctas"] = best_ctas
+
+    def pick(key, values, funcs, sizes, env_name):
+        """The value of one knob with the smallest summed time over `funcs` x `sizes`."""
+        best_v, best_sum = None, None
+        for v in values:
+            r = run(a.devices, funcs, sizes, {env_name: str(v), "MEGRAY_TUNE_DEFAULT": "0", "MEGRAY_MAX_CTAS": str(best_ctas)})
+            t = sum(x[0] for x in r.values()) if len(r) == len(funcs) * len(sizes) else None
+            table["measured"][f"us_sum_{key}_{v}"] = t
+            if t is not None and (best_sum is None or t < best_sum):
+                best_v, best_sum = v, t
+        if best_v is not None:
+            table[key] = best_v
+
+    # bytes per CTA of the single-pass kernels in the middle sizes (more CTAs: more bytes in
+    # flight, but a longer barrier), chunk of the pipelined broadcast, pause of long waits
+    pick("direct_cta_bytes", (16 << 10, 32 << 10, 128 << 10), KINDS, [1 << 20, 4 << 20, 16 << 20], "MEGRAY_DIRECT_CTA_BYTES")
+    if a.devices > 2:
+        pick("bcast_chunk_bytes", (32 << 10, 64 << 10, 256 << 10, 1 << 20), ["broadcast"], [4 << 20, 64 << 20, 1 << 30],
+             "MEGRAY_BCAST_CHUNK")
+    pick("spin_sleep_ns", (0, 200, 1000), ["broadcast", "reduce", "all_reduce"], [1 << 20, 256 << 20], "MEGRAY_SPIN_SLEEP_NS")
 
     if a.nvls:
         sizes = [1 << k for k in range(18, 29, 2)]  # 256 KiB .. 256 MiB

@@ -73,6 +73,37 @@ __device__ __forceinline__ Guard make_guard(const CommonArgs& c) {
 }
 #define GUARD_OK(g, p, n) (g).ok((p), (n), __LINE__)
 
+// ------------------------------------------------------------------ waits
+// A wait that has lasted a while pauses between polls (when spin_sleep_ns is set): a rank that
+// waits for long, such as the root of a reduce or CTAs that finished early, then keeps its L2
+// free for the peers that read and write this GPU's memory.  The first polls go back to back,
+// which is all that ranks running in step ever need.
+__device__ __forceinline__ void poll_backoff(const CommonArgs& c, uint32_t spins) {
+    if (c.spin_sleep_ns != 0 && spins > 32)
+        __nanosleep(c.spin_sleep_ns);
+}
+
+// Wait until *flag has reached `target` (wrap-safe).  False when the wait ran out, in which case
+// the status word says so.
+__device__ __forceinline__ bool wait_flag_reached(const CommonArgs& c, const uint32_t* flag, uint32_t target) {
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    while (static_cast<int32_t>(ld_acquire_sys(flag) - target) < 0) {
+        if ((++spins & 63) == 0) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0)
+                t0 = now;
+            else if (now - t0 > c.timeout_ns) {
+                if (c.status != nullptr)
+                    atomicCAS(c.status, 0, kStatusTimeout);
+                return false;
+            }
+        }
+        poll_backoff(c, spins);
+    }
+    return true;
+}
+
 // ------------------------------------------------------------------ barrier
 // One flag word per (CTA, peer) in every rank's pad.  Returns false when a wait ran out.
 __device__ __forceinline__ bool cta_barrier(const CommonArgs& c, uint32_t target) {
@@ -85,21 +116,7 @@ __device__ __forceinline__ bool cta_barrier(const CommonArgs& c, uint32_t target
         st_release_sys(at_peer, target);
         const uint32_t* mine = reinterpret_cast<const uint32_t*>(c.peers.heap[c.rank] + c.flag_off) +
                                blockIdx.x * kMaxRanks + q;
-        uint32_t spins = 0;
-        uint64_t t0 = 0;
-        while (static_cast<int32_t>(ld_acquire_sys(mine) - target) < 0) {
-            if ((++spins & 63) == 0) {
-                const uint64_t now = globaltimer_ns();
-                if (t0 == 0)
-                    t0 = now;
-                else if (now - t0 > c.timeout_ns) {
-                    ok = 0;
-                    if (c.status != nullptr)
-                        atomicCAS(c.status, 0, kStatusTimeout);
-                    break;
-                }
-            }
-        }
+        ok = wait_flag_reached(c, mine, target) ? 1 : 0;
     }
     return __syncthreads_and(ok) != 0;
 }
@@ -782,12 +799,14 @@ struct CallBufs {
     int in_vec, out_vec;       // every rank's buffer is 16-byte aligned
 };
 
-__device__ __forceinline__ uint64_t ld_cg_u64(const uint64_t* p) { return __ldcg(reinterpret_cast<const unsigned long long*>(p)); }
-
-// The first barrier of a single-pass kernel.  With `exchange` it also carries this call's buffer
-// addresses: thread q stores this rank's pair into slot [parity][rank] of rank q's pad before the
-// releasing flag store, and reads rank q's pair from its own pad after the acquiring flag load.
-// (Every CTA stores the same pair; any CTA's flag orders its own copy.)
+// The first barrier of a single-pass kernel: every rank has started this call, so whatever ran
+// before it on that rank's stream is complete.  With `exchange` it is the buffer addresses
+// themselves that say so: thread q stores this rank's pair into slot [parity][rank] of rank q's
+// pad as four flagged words (32 payload bits + the epoch, each word written atomically), and
+// polls slot [parity][q] of its own pad until all four carry this call's epoch.  No fence and no
+// separate flag: nothing written by this kernel has to be visible yet.  (Every CTA stores the
+// same words.  A slot was last used two calls ago, and the end barrier of the call in between
+// keeps any rank from running that far ahead.)
 __device__ __forceinline__ bool first_barrier(const DirectArgs& a, uint32_t target, CallBufs* cb) {
     const CommonArgs& c = a.c;
     const int n = c.nranks;
@@ -796,36 +815,41 @@ __device__ __forceinline__ bool first_barrier(const DirectArgs& a, uint32_t targ
     if (threadIdx.x < static_cast<unsigned>(n)) {
         const int q = threadIdx.x;
         if (a.exchange) {
-            uint64_t* theirs = reinterpret_cast<uint64_t*>(c.peers.heap[q] + kExchangeOff) +
-                               (a.parity * kMaxRanks + c.rank) * 2;
-            theirs[0] = reinterpret_cast<uint64_t>(a.in_local);
-            theirs[1] = reinterpret_cast<uint64_t>(a.out_local);
-        }
-        uint32_t* at_peer = reinterpret_cast<uint32_t*>(c.peers.heap[q] + c.flag_off) + blockIdx.x * kMaxRanks + c.rank;
-        st_release_sys(at_peer, target);
-        const uint32_t* mine = reinterpret_cast<const uint32_t*>(c.peers.heap[c.rank] + c.flag_off) +
-                               blockIdx.x * kMaxRanks + q;
-        uint32_t spins = 0;
-        uint64_t t0 = 0;
-        while (static_cast<int32_t>(ld_acquire_sys(mine) - target) < 0) {
-            if ((++spins & 63) == 0) {
-                const uint64_t now = globaltimer_ns();
-                if (t0 == 0)
-                    t0 = now;
-                else if (now - t0 > c.timeout_ns) {
-                    ok = 0;
-                    if (c.status != nullptr)
-                        atomicCAS(c.status, 0, kStatusTimeout);
+            char* theirs = c.peers.heap[q] + kExchangeOff + (a.parity * kMaxRanks + c.rank) * 32;
+            const uint64_t pi = reinterpret_cast<uint64_t>(a.in_local), po = reinterpret_cast<uint64_t>(a.out_local);
+            st_ll_v4(theirs, static_cast<uint32_t>(pi), static_cast<uint32_t>(pi >> 32), target);
+            st_ll_v4(theirs + 16, static_cast<uint32_t>(po), static_cast<uint32_t>(po >> 32), target);
+            const char* got = c.peers.heap[c.rank] + kExchangeOff + (a.parity * kMaxRanks + q) * 32;
+            uint32_t spins = 0;
+            uint64_t t0 = 0;
+            cb->in[q] = nullptr;
+            cb->out[q] = nullptr;
+            for (;;) {
+                const uint4 x = ld_ll_v4(got), y = ld_ll_v4(got + 16);
+                if (x.y == target && x.w == target && y.y == target && y.w == target) {
+                    cb->in[q] = reinterpret_cast<const char*>(static_cast<uint64_t>(x.x) | (static_cast<uint64_t>(x.z) << 32));
+                    cb->out[q] = reinterpret_cast<char*>(static_cast<uint64_t>(y.x) | (static_cast<uint64_t>(y.z) << 32));
                     break;
                 }
+                if ((++spins & 63) == 0) {
+                    const uint64_t now = globaltimer_ns();
+                    if (t0 == 0)
+                        t0 = now;
+                    else if (now - t0 > c.timeout_ns) {
+                        ok = 0;
+                        if (c.status != nullptr)
+                            atomicCAS(c.status, 0, kStatusTimeout);
+                        break;
+                    }
+                }
+                poll_backoff(c, spins);
             }
-        }
-        if (a.exchange) {
-            const uint64_t* got = reinterpret_cast<const uint64_t*>(c.peers.heap[c.rank] + kExchangeOff) +
-                                  (a.parity * kMaxRanks + q) * 2;
-            cb->in[q] = ok ? reinterpret_cast<const char*>(ld_cg_u64(got)) : nullptr;
-            cb->out[q] = ok ? reinterpret_cast<char*>(ld_cg_u64(got + 1)) : nullptr;
         } else {
+            uint32_t* at_peer = reinterpret_cast<uint32_t*>(c.peers.heap[q] + c.flag_off) + blockIdx.x * kMaxRanks + c.rank;
+            st_release_sys(at_peer, target);
+            const uint32_t* mine = reinterpret_cast<const uint32_t*>(c.peers.heap[c.rank] + c.flag_off) +
+                                   blockIdx.x * kMaxRanks + q;
+            ok = wait_flag_reached(c, mine, target) ? 1 : 0;
             cb->in[q] = a.in_base[q];
             cb->out[q] = a.out_base[q];
             if (q == c.rank) {  // buffers that only this rank touches need not be peer-addressable
@@ -1167,43 +1191,41 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                 *hi = min(L, min(sb + pl.per_cta, sb + static_cast<uint64_t>(k + 1) * a.chunk_bytes));
             };
             if (rank == root) {
-                // The last warp only announces: the other warps store chunk after chunk without
-                // ever waiting for a store to be acknowledged.  After each (chunk, slice) they
-                // arrive on one of eight named barriers in turn; the announcing warp waits on it
-                // and then publishes the chunk counter with a releasing store, which is what takes
-                // a round trip.  (The copying warps would have to get eight pieces ahead of the
-                // announcing warp to arrive twice on one barrier; a piece takes several round trips.)
+                // The last warp only announces: the other warps store round after round (chunk k
+                // of every slice) without ever waiting for a store to be acknowledged.  After
+                // each round they arrive on one of eight named barriers in turn; the announcing
+                // warp waits on it and then publishes the chunk counter to all forwarders with one
+                // warp-wide releasing store (lane v to the forwarder of slice v), which is what
+                // takes a round trip.  Every eighth round the storing warps wait for the announcing
+                // warp, so that they can never arrive twice on a barrier it has not passed yet.
                 constexpr int kSigBarriers = 8;
                 const unsigned ncopy = blockDim.x - 32;
                 const bool announcer = threadIdx.x >= ncopy;
-                uint32_t piece = 0;
                 for (uint32_t k = 0; k < pl.chunks; ++k) {
-                    // slice by slice, starting with a different one in every round; each forwarder
-                    // learns of its chunk as soon as that chunk (not the whole round) has been stored
-                    for (int vv = 0; vv < n - 1; ++vv) {
-                        const int v = (vv + static_cast<int>(k)) % (n - 1);
-                        const int j = (root + 1 + v) % n;
-                        const int bar_id = 1 + static_cast<int>(piece % kSigBarriers);
-                        uint64_t lo, hi;
-                        chunk_range(v, k, &lo, &hi);
-                        if (hi <= lo)
-                            continue;  // nothing of this slice in this chunk: the forwarder does not wait for it
-                        if (!announcer) {
-                            cta_copy_part(g, cb.out[j] + v * pl.slice + lo, my_in + v * pl.slice + lo, hi - lo,
-                                          threadIdx.x, ncopy);
-                            // every eighth piece the copying warps wait for the announcing warp, so
-                            // that they can never arrive twice on a barrier it has not passed yet
-                            if (piece % kSigBarriers == kSigBarriers - 1)
-                                named_bar_sync(bar_id, blockDim.x);
-                            else
-                                named_bar_arrive(bar_id, blockDim.x);
-                        } else {
-                            named_bar_sync(bar_id, blockDim.x);
-                            if (threadIdx.x == ncopy)
-                                st_release_sys(reinterpret_cast<uint32_t*>(c.peers.heap[j] + kChunkFlagOff) + blockIdx.x,
-                                               a.chunk_base + k + 1);
+                    const int bar_id = 1 + static_cast<int>(k % kSigBarriers);
+                    if (!announcer) {
+                        // slice by slice, starting with a different one in every round
+                        for (int vv = 0; vv < n - 1; ++vv) {
+                            const int v = (vv + static_cast<int>(k)) % (n - 1);
+                            const int j = (root + 1 + v) % n;
+                            uint64_t lo, hi;
+                            chunk_range(v, k, &lo, &hi);
+                            if (hi > lo)
+                                cta_copy_part(g, cb.out[j] + v * pl.slice + lo, my_in + v * pl.slice + lo, hi - lo,
+                                              threadIdx.x, ncopy);
                         }
-                        ++piece;  // (pieces that exist: both roles count alike)
+                        if (k % kSigBarriers == kSigBarriers - 1)
+                            named_bar_sync(bar_id, blockDim.x);
+                        else
+                            named_bar_arrive(bar_id, blockDim.x);
+                    } else {
+                        named_bar_sync(bar_id, blockDim.x);
+                        const int v = static_cast<int>(threadIdx.x - ncopy);
+                        if (v < n - 1) {
+                            const int j = (root + 1 + v) % n;
+                            st_release_sys(reinterpret_cast<uint32_t*>(c.peers.heap[j] + kChunkFlagOff) + blockIdx.x,
+                                           a.chunk_base + k + 1);
+                        }
                     }
                 }
                 __syncthreads();
@@ -1225,26 +1247,8 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                     chunk_range(v, k, &lo, &hi);
                     if (hi <= lo)
                         continue;  // (uniform over the CTA) nothing to wait for, nothing to forward
-                    if (threadIdx.x == 0) {
-                        const uint32_t target = a.chunk_base + k + 1;
-                        int ok = 1;
-                        uint32_t spins = 0;
-                        uint64_t t0 = 0;
-                        while (static_cast<int32_t>(ld_acquire_sys(my_flag) - target) < 0) {
-                            if ((++spins & 63) == 0) {
-                                const uint64_t now = globaltimer_ns();
-                                if (t0 == 0)
-                                    t0 = now;
-                                else if (now - t0 > c.timeout_ns) {
-                                    ok = 0;
-                                    if (c.status != nullptr)
-                                        atomicCAS(c.status, 0, kStatusTimeout);
-                                    break;
-                                }
-                            }
-                        }
-                        s_ok = ok;
-                    }
+                    if (threadIdx.x == 0)
+                        s_ok = wait_flag_reached(c, my_flag, a.chunk_base + k + 1) ? 1 : 0;
                     __syncthreads();
                     if (!s_ok)
                         return;

@@ -75,6 +75,7 @@ struct CommonArgs {
     uint64_t flag_off;     // byte offset of the flag rows inside the heap
     uint64_t heap_bytes;   // size of every rank's heap
     int phases;            // 1: CTA 0 stamps %globaltimer at every phase boundary (pad, kPhaseOff)
+    uint32_t spin_sleep_ns;  // pause between the polls of a wait that has lasted a while (0: none)
     // Extents of this call's buffers, for builds with MEGRAY_DEBUG_BOUNDS: every CTA-level copy or
     // reduction first checks that the range it is about to touch lies in some rank's heap or in
     // one of these buffers; a range that does not is skipped and recorded (pad, kDebugOff) and

@@ -79,7 +79,8 @@ NvlInterface* as_nvl(Communicator* comm) { return dynamic_cast<NvlInterface*>(co
 NvlCommunicator::NvlCommunicator(uint32_t nranks, uint32_t rank) : Communicator(nranks, rank) {
     const Options& o = global_options();
     m_timeout_ns = static_cast<uint64_t>(o.device_timeout_ms) * 1000000ull;
-    m_max_ctas = o.max_ctas > 0 ? std::min(o.max_ctas, kMaxCtas) : 64;
+    m_max_ctas = o.max_ctas > 0 ? std::min(o.max_ctas, kMaxCtas)
+                                : static_cast<int>(std::min<int64_t>(kMaxCtas, std::max<int64_t>(1, env_i64("MEGRAY_MAX_CTAS", 64))));
     m_oneshot_bytes = static_cast<size_t>(env_i64("MEGRAY_ONESHOT_BYTES", 256 * 1024));
     m_direct = env_i64("MEGRAY_DIRECT", 1) != 0;
     m_push_exchange = env_i64("MEGRAY_PUSH_EXCHANGE", 1) != 0;
@@ -106,7 +107,7 @@ NvlCommunicator::NvlCommunicator(uint32_t nranks, uint32_t rank) : Communicator(
         const std::string& t = tune_text;
         if (getenv("MEGRAY_ONESHOT_BYTES") == nullptr)
             m_oneshot_bytes = static_cast<size_t>(json_i64(t, "oneshot_bytes", static_cast<int64_t>(m_oneshot_bytes)));
-        if (o.max_ctas <= 0)
+        if (o.max_ctas <= 0 && getenv("MEGRAY_MAX_CTAS") == nullptr)
             m_max_ctas = std::min<int>(kMaxCtas, static_cast<int>(json_i64(t, "max_ctas", m_max_ctas)));
         if (getenv("MEGRAY_CTA_BYTES") == nullptr)
             m_cta_bytes = static_cast<size_t>(json_i64(t, "cta_bytes", static_cast<int64_t>(m_cta_bytes)));
@@ -136,6 +137,9 @@ NvlCommunicator::NvlCommunicator(uint32_t nranks, uint32_t rank) : Communicator(
     if (!tune_text.empty() && getenv("MEGRAY_BCAST_CHUNK") == nullptr)
         bcast_chunk_tuned = json_i64(tune_text, "bcast_chunk_bytes", -1);
     m_phases = env_i64("MEGRAY_PHASES", 0) != 0;
+    m_spin_sleep_ns = static_cast<uint32_t>(env_i64("MEGRAY_SPIN_SLEEP_NS", 0));
+    if (!tune_text.empty() && getenv("MEGRAY_SPIN_SLEEP_NS") == nullptr)
+        m_spin_sleep_ns = static_cast<uint32_t>(json_i64(tune_text, "spin_sleep_ns", m_spin_sleep_ns));
     m_guard_shrink = env_i64("MEGRAY_DEBUG_BOUNDS_SELFTEST", 0) != 0;
     m_bcast_chunk = static_cast<uint32_t>(round_up(
             static_cast<size_t>(bcast_chunk_tuned > 0 ? bcast_chunk_tuned : env_i64("MEGRAY_BCAST_CHUNK", 64 * 1024)), 16));
@@ -306,10 +310,7 @@ Status NvlCommunicator::begin_on(cudaStream_t s) {
     if (m_aborted.load())
         return MEGRAY_ABORTED;
     if (*m_status_host != 0) {  // an earlier kernel gave up waiting
-        if (m_error == MEGRAY_OK) {
-            m_error = static_cast<Status>(*m_status_host);
-            m_stats.timeouts++;
-        }
+        adopt_device_status();
         return m_error;
     }
     if (m_error != MEGRAY_OK)
@@ -322,6 +323,26 @@ Status NvlCommunicator::begin_on(cudaStream_t s) {
     }
     m_stats.calls++;
     return MEGRAY_OK;
+}
+
+// A kernel reported a failure: make it the communicator's error, once.  For a refused access
+// (bounds-checked build) say which one it was.
+void NvlCommunicator::adopt_device_status() {
+    if (m_error != MEGRAY_OK)
+        return;
+    m_error = static_cast<Status>(*m_status_host);
+    m_stats.timeouts++;
+    if (m_error == MEGRAY_OUT_OF_BOUNDS) {
+        uint64_t rec[3] = {0, 0, 0};
+        (void)cudaDeviceSynchronize();  // (the record is written right after the status)
+        if (cudaMemcpy(rec, m_heap.local() + mgk::coll::kDebugOff, sizeof(rec), cudaMemcpyDeviceToHost) == cudaSuccess)
+            MEGRAY_ERROR("rank %u: the range guard refused an access of %llu bytes at %p (collectives.cu line %u); "
+                         "declared buffers: in %p + %zu, out %p + %zu, peers' in %zu, out %zu",
+                         m_rank, static_cast<unsigned long long>(rec[1]), reinterpret_cast<void*>(rec[0]),
+                         static_cast<unsigned>(rec[2] & 0xffffffffu), m_guard.in, m_guard.in_bytes, m_guard.out,
+                         m_guard.out_bytes, m_guard.peer_in_bytes, m_guard.peer_out_bytes);
+        (void)cudaGetLastError();
+    }
 }
 
 void NvlCommunicator::after_launch(cudaStream_t stream) {
@@ -344,12 +365,13 @@ CommonArgs NvlCommunicator::common_args(uint32_t epochs) {
     c.flag_off = kFlagOff;
     c.heap_bytes = m_heap.bytes();
     c.phases = m_phases ? 1 : 0;
+    c.spin_sleep_ns = m_spin_sleep_ns;
     c.guard_in = m_guard.in;
     c.guard_in_bytes = m_guard.in_bytes;
     c.guard_out = m_guard.out;
     c.guard_out_bytes = m_guard.out_bytes;
-    c.guard_peer_in_bytes = m_guard.in_bytes;
-    c.guard_peer_out_bytes = m_guard.out_bytes;
+    c.guard_peer_in_bytes = m_guard.peer_in_bytes;
+    c.guard_peer_out_bytes = m_guard.peer_out_bytes;
     return c;
 }
 
@@ -362,11 +384,15 @@ void NvlCommunicator::set_guard(const void* in, size_t in_bytes, void* out, size
     m_guard.in_bytes = in != nullptr ? in_bytes : 0;
     m_guard.out = out;
     m_guard.out_bytes = out != nullptr ? out_bytes : 0;
+    m_guard.peer_in_bytes = in_bytes;
+    m_guard.peer_out_bytes = out_bytes;
     if (m_guard_shrink) {
         // self-test of the bounds-checked build: claim that the buffers are half as long as they
         // are, so that the guard must refuse (and skip) accesses that are in fact harmless
         m_guard.in_bytes /= 2;
         m_guard.out_bytes /= 2;
+        m_guard.peer_in_bytes /= 2;
+        m_guard.peer_out_bytes /= 2;
     }
 }
 
@@ -1307,10 +1333,8 @@ void NvlCommunicator::abort() {
 Status NvlCommunicator::status() {
     if (m_aborted.load())
         return MEGRAY_ABORTED;
-    if (m_status_host != nullptr && *m_status_host != 0 && m_error == MEGRAY_OK) {
-        m_error = static_cast<Status>(*m_status_host);
-        m_stats.timeouts++;
-    }
+    if (m_status_host != nullptr && *m_status_host != 0)
+        adopt_device_status();
     return m_error;
 }
 

@@ -112,6 +112,7 @@ private:
     static constexpr unsigned char kCanaryByte = 0xC5;
     size_t canary_off(int zone) const;
     void after_launch(cudaStream_t stream);
+    void adopt_device_status();
     int pick_ctas(size_t bytes) const;
     bool aligned_heap(const void* p, size_t bytes);
     // A user buffer registered with register_buffer(): this rank's range and every rank's twin.
@@ -182,6 +183,10 @@ private:
         size_t in_bytes = 0;
         void* out = nullptr;
         size_t out_bytes = 0;
+        // extents of the peers' buffers of the same call: the declared sizes, also on a rank
+        // that passes no buffer of its own (the non-root ranks of a rooted operation)
+        size_t peer_in_bytes = 0;
+        size_t peer_out_bytes = 0;
     } m_guard;
     bool m_guard_shrink = false;
     bool m_phases = false;  // MEGRAY_PHASES=1: kernels stamp %globaltimer at their phase boundaries
@@ -194,6 +199,7 @@ private:
     bool m_oneshot_first = true;
     uint32_t m_chunk_seq = 0;   // chunks announced by pipelined broadcasts so far
     uint32_t m_bcast_chunk = 128 * 1024;
+    uint32_t m_spin_sleep_ns = 0;  // MEGRAY_SPIN_SLEEP_NS / tune table "spin_sleep_ns"
     // largest payload per (source, destination) pair that goes as flagged words, per DirectKind
     size_t m_ll_bytes[8] = {};
     void* m_bounce[2] = {nullptr, nullptr};

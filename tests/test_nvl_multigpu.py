@@ -102,3 +102,9 @@ def test_send_recv_overlaps_a_native_collective_when_its_join_is_postponed():
     out = torchrun("p2p_overlap.py", nproc=2)
     print("\n".join(l for l in out.splitlines() if l.startswith("RANK_OK")))
     assert out.count("RANK_OK") == 2, out[-3000:]
+
+
+def test_full_size_fused_step_matches_the_unfused_step_elementwise():
+    out = torchrun("tp_fullsize_fused_vs_unfused.py", env={"MEGRAY_HEAP_MB": "6144"}, timeout=900)
+    print("\n".join(l for l in out.splitlines() if "differ" in l))
+    assert out.count("RANK_OK") == NPROC, out[-3000:]
