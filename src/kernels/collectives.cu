@@ -799,6 +799,54 @@ struct CallBufs {
     int in_vec, out_vec;       // every rank's buffer is 16-byte aligned
 };
 
+// Ranks in separate processes name a buffer as (entry of the allocation in the owner's export
+// log, offset).  The helper thread of this rank maps every entry that appears in a peer's log
+// and stores the address in the import table; an entry that is not there yet is waited for.
+__device__ __forceinline__ bool imported_address(const DirectArgs& a, int q, uint64_t word, char** out) {
+    const CommonArgs& c = a.c;
+    const uint32_t entry = static_cast<uint32_t>(word >> 48);
+    const uint64_t off = word & ((1ull << 48) - 1);
+    *out = nullptr;
+    if (entry == kWordEntryNull)
+        return true;
+    if (entry == kWordEntryHeap) {
+        *out = c.peers.heap[q] + off;
+        return true;
+    }
+    if (entry >= kImportEntries || a.import_table == nullptr) {
+        if (c.status != nullptr)
+            atomicCAS(c.status, 0, static_cast<int>(MegRay::MEGRAY_INVALID_ARGUMENT));
+        return false;
+    }
+    const uint64_t* slot = a.import_table + static_cast<uint64_t>(q) * kImportEntries + entry;
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    for (;;) {
+        uint64_t base;
+        asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(base) : "l"(slot) : "memory");
+        if (base > 1) {
+            *out = reinterpret_cast<char*>(base) + off;
+            return true;
+        }
+        if (base == 1) {  // the owner's memory could not be mapped into this process
+            if (c.status != nullptr)
+                atomicCAS(c.status, 0, static_cast<int>(MegRay::MEGRAY_CUDA_ERR));
+            return false;
+        }
+        if ((++spins & 63) == 0) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0)
+                t0 = now;
+            else if (now - t0 > c.timeout_ns) {
+                if (c.status != nullptr)
+                    atomicCAS(c.status, 0, kStatusTimeout);
+                return false;
+            }
+        }
+        __nanosleep(200);
+    }
+}
+
 // The first barrier of a single-pass kernel: every rank has started this call, so whatever ran
 // before it on that rank's stream is complete.  With `exchange` it is the buffer addresses
 // themselves that say so: thread q stores this rank's pair into slot [parity][rank] of rank q's
@@ -816,7 +864,7 @@ __device__ __forceinline__ bool first_barrier(const DirectArgs& a, uint32_t targ
         const int q = threadIdx.x;
         if (a.exchange) {
             char* theirs = c.peers.heap[q] + kExchangeOff + (a.parity * kMaxRanks + c.rank) * 32;
-            const uint64_t pi = reinterpret_cast<uint64_t>(a.in_local), po = reinterpret_cast<uint64_t>(a.out_local);
+            const uint64_t pi = a.in_word, po = a.out_word;
             st_ll_v4(theirs, static_cast<uint32_t>(pi), static_cast<uint32_t>(pi >> 32), target);
             st_ll_v4(theirs + 16, static_cast<uint32_t>(po), static_cast<uint32_t>(po >> 32), target);
             const char* got = c.peers.heap[c.rank] + kExchangeOff + (a.parity * kMaxRanks + q) * 32;
@@ -827,8 +875,22 @@ __device__ __forceinline__ bool first_barrier(const DirectArgs& a, uint32_t targ
             for (;;) {
                 const uint4 x = ld_ll_v4(got), y = ld_ll_v4(got + 16);
                 if (x.y == target && x.w == target && y.y == target && y.w == target) {
-                    cb->in[q] = reinterpret_cast<const char*>(static_cast<uint64_t>(x.x) | (static_cast<uint64_t>(x.z) << 32));
-                    cb->out[q] = reinterpret_cast<char*>(static_cast<uint64_t>(y.x) | (static_cast<uint64_t>(y.z) << 32));
+                    const uint64_t wi = static_cast<uint64_t>(x.x) | (static_cast<uint64_t>(x.z) << 32);
+                    const uint64_t wo = static_cast<uint64_t>(y.x) | (static_cast<uint64_t>(y.z) << 32);
+                    if (q == c.rank) {
+                        cb->in[q] = static_cast<const char*>(a.in_local);
+                        cb->out[q] = static_cast<char*>(a.out_local);
+                    } else if (a.exchange == 2) {
+                        char* pin = nullptr;
+                        char* pout = nullptr;
+                        if (!imported_address(a, q, wi, &pin) || !imported_address(a, q, wo, &pout))
+                            ok = 0;
+                        cb->in[q] = pin;
+                        cb->out[q] = pout;
+                    } else {
+                        cb->in[q] = reinterpret_cast<const char*>(wi);
+                        cb->out[q] = reinterpret_cast<char*>(wo);
+                    }
                     break;
                 }
                 if ((++spins & 63) == 0) {
@@ -1204,9 +1266,11 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                 for (uint32_t k = 0; k < pl.chunks; ++k) {
                     const int bar_id = 1 + static_cast<int>(k % kSigBarriers);
                     if (!announcer) {
-                        // slice by slice, starting with a different one in every round
+                        // slice by slice, starting with a different one in every round and in every
+                        // CTA: at any moment the CTAs store to all destinations alike (all of them
+                        // storing to one destination at a time would be limited by that GPU's link)
                         for (int vv = 0; vv < n - 1; ++vv) {
-                            const int v = (vv + static_cast<int>(k)) % (n - 1);
+                            const int v = (vv + static_cast<int>(k) + static_cast<int>(blockIdx.x)) % (n - 1);
                             const int j = (root + 1 + v) % n;
                             uint64_t lo, hi;
                             chunk_range(v, k, &lo, &hi);
@@ -1267,6 +1331,113 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                     }
                     __syncthreads();  // s_ok is rewritten in the next round
                 }
+            }
+        }
+    } else if (a.kind == DIRECT_REDUCE && a.stage_slots > 0 && n > 1) {
+        // Reduce with the root's input pushed.  One slice per non-root rank, as below, but the
+        // reducer of a slice does not load the root's part over NVLink: the root stores it, chunk
+        // by chunk, into staging slots in the reducer's heap (the root has nothing else to do).
+        // Every GPU then issues about one message's worth of transfers (the root its input, a
+        // reducer the other non-root inputs of its slice plus its result) instead of the reducers
+        // issuing all of them.  CTA b of the root feeds CTA b of every reducer; a slot is written
+        // again only after its reader has reported the chunk that was in it as consumed.
+        const int root = a.root;
+        const ReducePlan pl = reduce_plan(a.len, n, gridDim.x, a.chunk_bytes, sizeof(Tin));
+        const uint64_t sb = pl.per_cta * blockIdx.x;  // this CTA's share of every slice (elements)
+        // elements [lo, hi) of slice v that chunk k of this CTA covers (relative to the slice)
+        auto chunk_range = [&](int v, uint32_t k, uint64_t* lo, uint64_t* hi) {
+            const uint64_t s0 = static_cast<uint64_t>(v) * pl.slice;
+            const uint64_t L = s0 >= a.len ? 0 : min(pl.slice, a.len - s0);
+            *lo = min(L, sb + static_cast<uint64_t>(k) * pl.chunk_el);
+            *hi = min(L, min(sb + pl.per_cta, sb + static_cast<uint64_t>(k + 1) * pl.chunk_el));
+        };
+        auto slot_off = [&](uint32_t k) {
+            return a.stage_off + (static_cast<uint64_t>(blockIdx.x) * a.stage_slots + k % a.stage_slots) * a.chunk_bytes;
+        };
+        if (rank == root) {
+            constexpr int kSigBarriers = 8;
+            const unsigned ncopy = blockDim.x - 32;
+            const bool announcer = threadIdx.x >= ncopy;
+            if (threadIdx.x == 0)
+                s_ok = 1;
+            __syncthreads();
+            for (uint32_t k = 0; k < pl.chunks; ++k) {
+                const int bar_id = 1 + static_cast<int>(k % kSigBarriers);
+                if (!announcer) {
+                    if (k >= a.stage_slots) {
+                        // the slot still holds chunk k - stage_slots until every reducer has consumed it
+                        if (threadIdx.x < static_cast<unsigned>(n - 1) && s_ok) {
+                            const int j = (root + 1 + static_cast<int>(threadIdx.x)) % n;
+                            const uint32_t* credit = reinterpret_cast<const uint32_t*>(c.peers.heap[rank] + kCreditOff) +
+                                                     blockIdx.x * kMaxRanks + j;
+                            uint64_t lo, hi;
+                            chunk_range(static_cast<int>(threadIdx.x), k - a.stage_slots, &lo, &hi);
+                            // (a reducer reports only chunks that held something)
+                            if (hi > lo && !wait_flag_reached(c, credit, a.chunk_base + (k - a.stage_slots) + 1))
+                                s_ok = 0;  // (status says why; the loop runs on without waiting so that every barrier completes)
+                        }
+                        named_bar_sync(9, ncopy);
+                    }
+                    for (int vv = 0; vv < n - 1; ++vv) {
+                        const int v = (vv + static_cast<int>(k) + static_cast<int>(blockIdx.x)) % (n - 1);
+                        const int j = (root + 1 + v) % n;
+                        uint64_t lo, hi;
+                        chunk_range(v, k, &lo, &hi);
+                        if (hi > lo)
+                            cta_copy_part(g, c.peers.heap[j] + slot_off(k), my_in + (v * pl.slice + lo) * sizeof(Tin),
+                                          (hi - lo) * sizeof(Tin), threadIdx.x, ncopy);
+                    }
+                    if (k % kSigBarriers == kSigBarriers - 1)
+                        named_bar_sync(bar_id, blockDim.x);
+                    else
+                        named_bar_arrive(bar_id, blockDim.x);
+                } else {
+                    named_bar_sync(bar_id, blockDim.x);
+                    const int v = static_cast<int>(threadIdx.x - ncopy);
+                    if (v < n - 1) {
+                        const int j = (root + 1 + v) % n;
+                        st_release_sys(reinterpret_cast<uint32_t*>(c.peers.heap[j] + kChunkFlagOff) + blockIdx.x,
+                                       a.chunk_base + k + 1);
+                    }
+                }
+            }
+        } else {
+            const int v = (rank - root - 1 + n) % n;  // the slice this rank reduces
+            const uint32_t* my_flag = reinterpret_cast<const uint32_t*>(c.peers.heap[rank] + kChunkFlagOff) + blockIdx.x;
+            uint32_t* credit = reinterpret_cast<uint32_t*>(c.peers.heap[root] + kCreditOff) + blockIdx.x * kMaxRanks + rank;
+            for (uint32_t k = 0; k < pl.chunks; ++k) {
+                uint64_t lo, hi;
+                chunk_range(v, k, &lo, &hi);
+                if (hi <= lo)
+                    continue;  // (uniform over the CTA) the root stores nothing for it either
+                const uint64_t in_byte0 = (v * pl.slice + lo) * sizeof(Tin);
+                const uint64_t out_byte0 = (v * pl.slice + lo) * sizeof(Tout);
+                if (threadIdx.x == 0) {
+                    s_ok = wait_flag_reached(c, my_flag, a.chunk_base + k + 1) ? 1 : 0;
+                    // the root's part of this chunk: in the slot, addressed like the other inputs
+                    cb.in[root] = c.peers.heap[rank] + slot_off(k) - in_byte0;
+                }
+                __syncthreads();
+                if (!s_ok)
+                    return;
+                char* single = cb.out[root] + out_byte0;
+                const bool vec = cb.in_vec && (in_byte0 & 15) == 0 && (reinterpret_cast<uint64_t>(single) & 15) == 0;
+                switch (a.op) {
+                    case MegRay::MEGRAY_SUM:
+                        direct_reduce_range<Tin, Tout, MegRay::MEGRAY_SUM, false>(g, a, cb, in_byte0, out_byte0, hi - lo, single,
+                                                                                  vec, false, false);
+                        break;
+                    case MegRay::MEGRAY_MAX:
+                        direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MAX, false>(g, a, cb, in_byte0, out_byte0, hi - lo, single,
+                                                                                  vec, false, false);
+                        break;
+                    default:
+                        direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MIN, false>(g, a, cb, in_byte0, out_byte0, hi - lo, single,
+                                                                                  vec, false, false);
+                }
+                __syncthreads();  // every thread has loaded its part of the slot
+                if (threadIdx.x == 0)
+                    asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(credit), "r"(a.chunk_base + k + 1) : "memory");
             }
         }
     } else {

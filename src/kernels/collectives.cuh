@@ -53,6 +53,10 @@ constexpr uint64_t kDebugOff = 8192 + 1024;  // bounds-checked build: the first 
                                              // {u64 address, u64 bytes, u32 source line, u32 rank}
 constexpr uint64_t kPhaseOff = 8192 + 2048;  // kMaxPhases x u64: %globaltimer stamps of CTA 0 (phase mode)
 constexpr int kMaxPhases = 8;
+constexpr uint32_t kImportEntries = 512;     // allocations one rank can export to processes that are its peers
+constexpr uint32_t kWordEntryNull = 0xFFFF;  // exchange == 2: no buffer
+constexpr uint32_t kWordEntryHeap = 0xFFFE;  // exchange == 2: the offset is one into the rank's heap
+constexpr uint64_t kCreditOff = 12288;       // [kMaxCtas][kMaxRanks] u32: chunks a reducer has consumed (staged reduce)
 constexpr int kStatusOutOfBounds = 14;       // MegRay::MEGRAY_OUT_OF_BOUNDS
 // Small-message (flagged word) slots follow the pad: [2 parities][kMaxRanks sources] slots, each
 // holding kLLMaxBytes of payload as 8-byte {data, flag} words.
@@ -182,12 +186,21 @@ struct DirectArgs {
     MegRay::DType out_dtype;
     MegRay::ReduceOp op;
     char* mc_base;         // non-null: multicast (NVLS) mapping of the heap, use multimem
-    int exchange;          // 1: in_local / out_local are published to the peers and theirs are read
+    int exchange;          // 1: in_word / out_word (this rank's buffer addresses) are published to the peers
+                           // and theirs are read; 2: the words are (allocation entry << 48 | offset)
+                           // and import_table maps (rank, entry) to the allocation's address here
+    uint64_t in_word, out_word;
+    const uint64_t* import_table;  // [kMaxRanks ranks][kImportEntries]; 0: not mapped yet, 1: cannot be mapped
     int parity;            // exchange: which of the two address slots this launch uses (alternates)
     int root;              // broadcast, reduce, gather, scatter
     uint64_t heap_bytes;   // size of every rank's heap (NVLS needs both buffers inside it, same offset)
     uint32_t chunk_base;   // broadcast: chunk k is announced as chunk_base + k + 1
     uint32_t chunk_bytes;  // broadcast: bytes of one chunk of a CTA's share of a slice (multiple of 16)
+    // reduce with the root's input pushed (stage_slots > 0): CTA b of the root stores chunk k of
+    // every slice into slot (b * stage_slots + k % stage_slots) of chunk_bytes at stage_off in the
+    // heap of the rank that reduces the slice
+    uint64_t stage_off;
+    uint32_t stage_slots;
 };
 
 // Small messages: flagged words ("LL").  A sender stores every 4 bytes of payload together with
@@ -236,6 +249,27 @@ __host__ __device__ inline BcastPlan bcast_plan(uint64_t bytes, int n, int ctas,
     p.slice = ((bytes + ns - 1) / ns + 15) / 16 * 16;
     p.per_cta = ((p.slice + ctas - 1) / ctas + 15) / 16 * 16;
     p.chunks = static_cast<uint32_t>((p.per_cta + chunk_bytes - 1) / chunk_bytes);
+    if (p.chunks == 0)
+        p.chunks = 1;
+    return p;
+}
+
+// The staged reduce: n - 1 slices of `slice` elements (one per non-root rank), of which every
+// CTA takes `per_cta` elements in `chunks` chunks of `chunk_el` elements.
+struct ReducePlan {
+    uint64_t slice;
+    uint64_t per_cta;
+    uint64_t chunk_el;
+    uint32_t chunks;
+};
+__host__ __device__ inline ReducePlan reduce_plan(uint64_t len, int n, int ctas, uint32_t chunk_bytes, uint32_t elem_bytes) {
+    ReducePlan p;
+    const uint64_t ns = n > 1 ? static_cast<uint64_t>(n - 1) : 1;
+    const uint64_t v = 16 / elem_bytes;  // elements per 16-byte vector
+    p.slice = ((len + ns - 1) / ns + v - 1) / v * v;
+    p.per_cta = ((p.slice + ctas - 1) / ctas + v - 1) / v * v;
+    p.chunk_el = chunk_bytes / elem_bytes;
+    p.chunks = static_cast<uint32_t>((p.per_cta + p.chunk_el - 1) / p.chunk_el);
     if (p.chunks == 0)
         p.chunks = 1;
     return p;

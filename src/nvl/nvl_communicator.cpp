@@ -1,4 +1,5 @@
 #include "nvl/nvl_communicator.h"
+#include "nvl/ipc_cache.h"
 
 #include <dlfcn.h>
 #include <string.h>
@@ -138,6 +139,9 @@ NvlCommunicator::NvlCommunicator(uint32_t nranks, uint32_t rank) : Communicator(
         bcast_chunk_tuned = json_i64(tune_text, "bcast_chunk_bytes", -1);
     m_phases = env_i64("MEGRAY_PHASES", 0) != 0;
     m_spin_sleep_ns = static_cast<uint32_t>(env_i64("MEGRAY_SPIN_SLEEP_NS", 0));
+    m_reduce_staged_min = static_cast<size_t>(env_i64("MEGRAY_REDUCE_STAGED_MIN", 8 << 20));
+    if (!tune_text.empty() && getenv("MEGRAY_REDUCE_STAGED_MIN") == nullptr)
+        m_reduce_staged_min = static_cast<size_t>(json_i64(tune_text, "reduce_staged_min_bytes", static_cast<int64_t>(m_reduce_staged_min)));
     if (!tune_text.empty() && getenv("MEGRAY_SPIN_SLEEP_NS") == nullptr)
         m_spin_sleep_ns = static_cast<uint32_t>(json_i64(tune_text, "spin_sleep_ns", m_spin_sleep_ns));
     m_guard_shrink = env_i64("MEGRAY_DEBUG_BOUNDS_SELFTEST", 0) != 0;
@@ -175,6 +179,7 @@ NvlCommunicator::~NvlCommunicator() {
     // peers may still be inside their last kernel reading this rank's heap: meet first
     if (m_ready && m_client && m_client->connected() && !m_aborted.load())
         m_client->barrier();
+    m_ipc.reset();  // stops the helper thread and closes the mappings of the peers' allocations
     for (Registration& r : m_regs)
         drop_registration(r);
     m_regs.clear();
@@ -274,6 +279,20 @@ Status NvlCommunicator::do_init() {
         m_xchg = true;
         for (uint32_t q = 0; q < m_nranks; ++q)
             m_xchg = m_xchg && all[q] != 0;
+    }
+    // Ranks in separate processes: allocations are exported and mapped on first use, after which
+    // the same kernels run on them (MEGRAY_IPC_CACHE=0 keeps ordinary buffers on the staged paths).
+    if (!m_xchg && m_nranks > 1 && env_i64("MEGRAY_IPC_CACHE", 1) != 0 && env_i64("MEGRAY_EXCHANGE", 1) != 0) {
+        static_assert(IpcCache::kMaxExports == mgk::coll::kImportEntries, "table geometry");
+        static_assert(IpcCache::kEntryNull == mgk::coll::kWordEntryNull && IpcCache::kEntryHeap == mgk::coll::kWordEntryHeap,
+                      "word encoding");
+        m_ipc.reset(new IpcCache());
+        if (m_ipc->init(*m_client, m_nranks, m_rank, m_heap.device())) {
+            m_xchg = true;
+        } else {
+            m_ipc.reset();
+            MEGRAY_INFO("NVL backend: no shared export logs; ordinary buffers take the staged paths");
+        }
     }
 
 #ifdef MEGRAY_WITH_NCCL
@@ -612,16 +631,39 @@ Status NvlCommunicator::exchange_launch(int kind, const void* in, size_t in_byte
     const void* in_use = in;
     void* out_use = out;
     bool copy_back = false;
-    if (in != nullptr && in_shared && !peer_addressable(in, in_bytes)) {
+    // what this rank tells its peers about the two buffers: the address (ranks of one process),
+    // or the allocation's export entry and the offset inside it (ranks in separate processes)
+    uint64_t in_word = 0, out_word = 0;
+    auto describe = [&](const void* p, size_t bytes, uint64_t* word) {
+        if (m_ipc == nullptr) {
+            *word = reinterpret_cast<uint64_t>(p);
+            return peer_addressable(p, bytes);
+        }
+        if (p == nullptr) {
+            *word = IpcCache::encode(IpcCache::kEntryNull, 0);
+            return true;
+        }
+        if (in_heap(p, bytes)) {
+            *word = IpcCache::encode(IpcCache::kEntryHeap, static_cast<uint64_t>(static_cast<const char*>(p) - m_heap.local()));
+            return true;
+        }
+        return m_ipc->resolve(p, bytes, word);
+    };
+    if (in == nullptr || !in_shared) {
+        // (peers never touch it: nothing to describe)
+        in_word = m_ipc ? IpcCache::encode(IpcCache::kEntryNull, 0) : reinterpret_cast<uint64_t>(in);
+    } else if (!describe(in, in_bytes, &in_word)) {
         void* b = bounce(0, in_bytes);
-        if (b == nullptr)
+        if (b == nullptr || !describe(b, in_bytes, &in_word))
             return MEGRAY_CUDA_ERR;
         MEGRAY_CHECK(check_cuda(cudaMemcpyAsync(b, in, in_bytes, cudaMemcpyDefault, stream)));
         in_use = b;
     }
-    if (out != nullptr && out_shared && !peer_addressable(out, out_bytes)) {
+    if (out == nullptr || !out_shared) {
+        out_word = m_ipc ? IpcCache::encode(IpcCache::kEntryNull, 0) : reinterpret_cast<uint64_t>(out);
+    } else if (!describe(out, out_bytes, &out_word)) {
         void* b = bounce(1, out_bytes);
-        if (b == nullptr)
+        if (b == nullptr || !describe(b, out_bytes, &out_word))
             return MEGRAY_CUDA_ERR;
         out_use = b;
         copy_back = true;
@@ -637,7 +679,10 @@ Status NvlCommunicator::exchange_launch(int kind, const void* in, size_t in_byte
     a.out_dtype = out_dtype;
     a.op = op;
     a.root = static_cast<int>(root);
-    a.exchange = 1;
+    a.exchange = m_ipc ? 2 : 1;
+    a.in_word = in_word;
+    a.out_word = out_word;
+    a.import_table = m_ipc ? m_ipc->table() : nullptr;
     a.parity = m_xchg_parity;
     m_xchg_parity ^= 1;
     a.in_local = in_use;
@@ -664,6 +709,21 @@ Status NvlCommunicator::exchange_launch(int kind, const void* in, size_t in_byte
         a.chunk_bytes = m_bcast_chunk;
         a.chunk_base = m_chunk_seq;
         m_chunk_seq += mgk::coll::bcast_plan(work, static_cast<int>(m_nranks), ctas, a.chunk_bytes).chunks;
+    }
+    if (kind == mgk::coll::DIRECT_REDUCE && m_nranks > 1 && work >= m_reduce_staged_min && !nvls) {
+        // large messages: the root pushes its input into staging slots of the reducing ranks
+        const size_t slice = (work + m_nranks - 2) / (m_nranks - 1);
+        const int want = static_cast<int>(std::min<size_t>(std::max<size_t>(1, slice / (m_direct_cta_bytes / 2)), static_cast<size_t>(max_ctas)));
+        const size_t slots = std::min<size_t>(8, m_ws_bytes / (static_cast<size_t>(want) * m_bcast_chunk));
+        if (slots >= 2) {
+            ctas = want;
+            a.chunk_bytes = m_bcast_chunk;
+            a.chunk_base = m_chunk_seq;
+            m_chunk_seq += mgk::coll::reduce_plan(len, static_cast<int>(m_nranks), ctas, a.chunk_bytes,
+                                                  static_cast<uint32_t>(ein)).chunks;
+            a.stage_off = workspace_off();
+            a.stage_slots = static_cast<uint32_t>(slots);
+        }
     }
     MEGRAY_CHECK(check_cuda(mgk::coll::launch_direct(a, ctas, 512, stream)));
     after_launch(stream);
@@ -1441,6 +1501,14 @@ Status NvlCommunicator::register_buffer(void* ptr, size_t bytes) {
     // A bad argument on one rank must not leave the others waiting in the exchange below: it is
     // reported to them as "this rank could not export its buffer", and every rank falls back.
     const bool bad_arg = ptr == nullptr || bytes == 0;
+    if (m_ipc != nullptr) {
+        // Ranks in separate processes export allocations on first use anyway; registering one
+        // only does it ahead of time, so that the first collective on it finds it mapped.
+        uint64_t word = 0;
+        if (bad_arg)
+            return MEGRAY_INVALID_ARGUMENT;
+        return in_heap(ptr, bytes) || m_ipc->resolve(ptr, bytes, &word) ? MEGRAY_OK : MEGRAY_NOT_IMPLEMENTED;
+    }
     const drv::Api* api = drv::api();
     std::vector<RegInfo> all(m_nranks);
     RegInfo mine;
@@ -1524,6 +1592,8 @@ Status NvlCommunicator::deregister_buffer(void* ptr) {
     // peers may still be reading or writing this buffer from their last kernel
     cudaDeviceSynchronize();
     MEGRAY_CHECK(m_client->barrier());
+    if (m_ipc != nullptr)
+        return MEGRAY_OK;  // (exports stay: the memory may be used again)
     for (size_t i = 0; i < m_regs.size(); ++i) {
         if (m_regs[i].local == static_cast<char*>(ptr)) {
             drop_registration(m_regs[i]);

@@ -25,6 +25,8 @@
 
 namespace MegRay {
 
+class IpcCache;
+
 class NcclCommunicator;
 
 class NvlCommunicator : public Communicator, public NvlInterface {
@@ -191,6 +193,7 @@ private:
     bool m_guard_shrink = false;
     bool m_phases = false;  // MEGRAY_PHASES=1: kernels stamp %globaltimer at their phase boundaries
     bool m_xchg = false;
+    std::unique_ptr<IpcCache> m_ipc;  // ranks in separate processes: export logs and import table
     int m_xchg_parity = 0;
     uint32_t m_ll_seq = 0;      // small-message calls so far
     int m_ll_parity = 0;
@@ -199,6 +202,9 @@ private:
     bool m_oneshot_first = true;
     uint32_t m_chunk_seq = 0;   // chunks announced by pipelined broadcasts so far
     uint32_t m_bcast_chunk = 128 * 1024;
+    // reduce of at least this many bytes: the root pushes its input (MEGRAY_REDUCE_STAGED_MIN / tune
+    // table "reduce_staged_min_bytes")
+    size_t m_reduce_staged_min = 8u << 20;
     uint32_t m_spin_sleep_ns = 0;  // MEGRAY_SPIN_SLEEP_NS / tune table "spin_sleep_ns"
     // largest payload per (source, destination) pair that goes as flagged words, per DirectKind
     size_t m_ll_bytes[8] = {};

@@ -71,8 +71,11 @@ def test_single_pass_collectives_on_heap_tensors():
     assert "nvls_calls=0" in out
 
 
-def test_single_pass_collectives_on_registered_user_buffers():
-    out = torchrun("registered.py")
+@pytest.mark.parametrize("ipc_cache", ["0", "1"])
+def test_single_pass_collectives_on_registered_user_buffers(ipc_cache):
+    # "0": explicit registration maps the buffers (one host exchange per buffer); "1": allocations
+    # are exported on first use and registering only does that ahead of time
+    out = torchrun("registered.py", env={"MEGRAY_IPC_CACHE": ipc_cache})
     assert out.count("RANK_OK") == NPROC, out[-3000:]
 
 
@@ -107,4 +110,16 @@ def test_send_recv_overlaps_a_native_collective_when_its_join_is_postponed():
 def test_full_size_fused_step_matches_the_unfused_step_elementwise():
     out = torchrun("tp_fullsize_fused_vs_unfused.py", env={"MEGRAY_HEAP_MB": "6144"}, timeout=900)
     print("\n".join(l for l in out.splitlines() if "differ" in l))
+    assert out.count("RANK_OK") == NPROC, out[-3000:]
+
+
+def test_ordinary_tensors_of_separate_processes_take_the_single_pass_kernels():
+    # allocations are exported and mapped on first use (asymmetric first use, freed and
+    # re-allocated memory, views at odd offsets)
+    out = torchrun("ipc_cache.py")
+    assert out.count("RANK_OK") == NPROC, out[-3000:]
+
+
+def test_collectives_on_the_staged_paths_when_nothing_is_exported():
+    out = torchrun("collectives.py", env={"MEGRAY_IPC_CACHE": "0"})
     assert out.count("RANK_OK") == NPROC, out[-3000:]
