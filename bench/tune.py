@@ -108,7 +108,21 @@ def main():
     if a.devices > 2:
         pick("bcast_chunk_bytes", (32 << 10, 64 << 10, 256 << 10, 1 << 20), ["broadcast"], [4 << 20, 64 << 20, 1 << 30],
              "MEGRAY_BCAST_CHUNK")
-    pick("spin_sleep_ns", (0, 200, 1000), ["broadcast", "reduce", "all_reduce"], [1 << 20, 256 << 20], "MEGRAY_SPIN_SLEEP_NS")
+
+    # reduce: from which size on the form in which the root pushes its input wins at every larger size
+    rsizes = [1 << k for k in range(18, 29, 2)]  # 256 KiB .. 256 MiB
+    base_env = {"MEGRAY_TUNE_DEFAULT": "0", "MEGRAY_LL_BYTES": "0", "MEGRAY_MAX_CTAS": str(best_ctas)}
+    pushed = run(a.devices, ["reduce"], rsizes, dict(base_env, MEGRAY_REDUCE_STAGED_MIN="0"))
+    pulled = run(a.devices, ["reduce"], rsizes, dict(base_env, MEGRAY_REDUCE_STAGED_MIN=str(1 << 62)))
+    first = 1 << 62
+    for sz in reversed(rsizes):
+        tp, tl = pushed.get(("reduce", sz)), pulled.get(("reduce", sz))
+        if tp is None or tl is None or tp[0] > tl[0]:
+            break
+        first = sz
+    table["reduce_staged_min_bytes"] = first
+    table["measured"]["us_reduce_pushed_vs_pulled"] = {str(sz): [pushed.get(("reduce", sz), [None])[0],
+                                                                 pulled.get(("reduce", sz), [None])[0]] for sz in rsizes}
 
     if a.nvls:
         sizes = [1 << k for k in range(18, 29, 2)]  # 256 KiB .. 256 MiB

@@ -28,6 +28,19 @@ __device__ __forceinline__ void stamp(const CommonArgs& c, int i) {
         reinterpret_cast<uint64_t*>(c.peers.heap[c.rank] + kPhaseOff)[i] = globaltimer_ns();
 }
 
+// ------------------------------------------------------------------ failure record
+// The first wait that runs out (or lookup that fails) sets the status word and leaves, in the
+// pad at kDebugOff + 32, what it was: {source line, detail (peer, entry, target, ...), rank}.
+__device__ __forceinline__ void fail_with(const CommonArgs& c, int code, int line, uint64_t detail) {
+    if (c.status != nullptr && atomicCAS(c.status, 0, code) == 0) {
+        uint64_t* rec = reinterpret_cast<uint64_t*>(c.peers.heap[c.rank] + kDebugOff + 32);
+        rec[0] = static_cast<uint64_t>(static_cast<uint32_t>(line));
+        rec[1] = detail;
+        rec[2] = static_cast<uint64_t>(c.rank);
+    }
+}
+#define FAIL_WITH(c, code, detail) fail_with((c), (code), __LINE__, (detail))
+
 // ------------------------------------------------------------------ range guard
 // In a build with MEGRAY_DEBUG_BOUNDS every CTA-level primitive asks the guard before it touches
 // a range.  Allowed: any rank's heap, this call's local buffers, and (single-pass kernels on
@@ -85,7 +98,8 @@ __device__ __forceinline__ void poll_backoff(const CommonArgs& c, uint32_t spins
 
 // Wait until *flag has reached `target` (wrap-safe).  False when the wait ran out, in which case
 // the status word says so.
-__device__ __forceinline__ bool wait_flag_reached(const CommonArgs& c, const uint32_t* flag, uint32_t target) {
+// `what` goes into the failure record: 1 barrier, 2 chunk announcement, 3 consumed-chunk counter.
+__device__ __forceinline__ bool wait_flag_reached(const CommonArgs& c, const uint32_t* flag, uint32_t target, int what = 1) {
     uint32_t spins = 0;
     uint64_t t0 = 0;
     while (static_cast<int32_t>(ld_acquire_sys(flag) - target) < 0) {
@@ -94,8 +108,7 @@ __device__ __forceinline__ bool wait_flag_reached(const CommonArgs& c, const uin
             if (t0 == 0)
                 t0 = now;
             else if (now - t0 > c.timeout_ns) {
-                if (c.status != nullptr)
-                    atomicCAS(c.status, 0, kStatusTimeout);
+                FAIL_WITH(c, kStatusTimeout, (static_cast<uint64_t>(what) << 32) | target);
                 return false;
             }
         }
@@ -196,6 +209,25 @@ __device__ __forceinline__ void named_bar_arrive(int id, int count) {
 }
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// Progress of the storing warps of a root CTA, for its announcing warp.  A warp that has issued
+// all its stores of round k - 1 writes k into its word (release at CTA scope, after the warp has
+// converged); the announcing warp reads all words (acquire) and takes the minimum.  Its releasing
+// store at system scope then also covers the storing warps' stores.
+__device__ __forceinline__ void warp_round_done(uint32_t* s_round, uint32_t rounds) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) {
+        __threadfence_block();
+        reinterpret_cast<volatile uint32_t*>(s_round)[threadIdx.x >> 5] = rounds;
+    }
+}
+__device__ __forceinline__ uint32_t rounds_done_by_all(const uint32_t* s_round, unsigned warps) {
+    const unsigned lane = threadIdx.x & 31;
+    uint32_t m = lane < warps ? reinterpret_cast<const volatile uint32_t*>(s_round)[lane] : 0xffffffffu;
+    m = __reduce_min_sync(0xffffffffu, m);
+    __threadfence_block();
+    return m;
 }
 
 // ------------------------------------------------------------------ arithmetic
@@ -566,8 +598,7 @@ __device__ __forceinline__ bool ll_wait_unit(const char* slot, uint64_t u, uint3
             if (t0 == 0)
                 t0 = now;
             else if (now - t0 > c.timeout_ns) {
-                if (c.status != nullptr)
-                    atomicCAS(c.status, 0, kStatusTimeout);
+                FAIL_WITH(c, kStatusTimeout, 0);
                 return false;
             }
         }
@@ -742,8 +773,7 @@ __global__ void __launch_bounds__(512) ll_family_kernel(const LLArgs a) {
                 if (t0 == 0)
                     t0 = now;
                 else if (now - t0 > c.timeout_ns) {
-                    if (c.status != nullptr)
-                        atomicCAS(c.status, 0, kStatusTimeout);
+                    FAIL_WITH(c, kStatusTimeout, 0);
                     break;
                 }
             }
@@ -814,8 +844,7 @@ __device__ __forceinline__ bool imported_address(const DirectArgs& a, int q, uin
         return true;
     }
     if (entry >= kImportEntries || a.import_table == nullptr) {
-        if (c.status != nullptr)
-            atomicCAS(c.status, 0, static_cast<int>(MegRay::MEGRAY_INVALID_ARGUMENT));
+        FAIL_WITH(c, static_cast<int>(MegRay::MEGRAY_INVALID_ARGUMENT), (static_cast<uint64_t>(q) << 32) | entry);
         return false;
     }
     const uint64_t* slot = a.import_table + static_cast<uint64_t>(q) * kImportEntries + entry;
@@ -829,8 +858,7 @@ __device__ __forceinline__ bool imported_address(const DirectArgs& a, int q, uin
             return true;
         }
         if (base == 1) {  // the owner's memory could not be mapped into this process
-            if (c.status != nullptr)
-                atomicCAS(c.status, 0, static_cast<int>(MegRay::MEGRAY_CUDA_ERR));
+            FAIL_WITH(c, static_cast<int>(MegRay::MEGRAY_CUDA_ERR), (static_cast<uint64_t>(q) << 32) | entry);
             return false;
         }
         if ((++spins & 63) == 0) {
@@ -838,8 +866,7 @@ __device__ __forceinline__ bool imported_address(const DirectArgs& a, int q, uin
             if (t0 == 0)
                 t0 = now;
             else if (now - t0 > c.timeout_ns) {
-                if (c.status != nullptr)
-                    atomicCAS(c.status, 0, kStatusTimeout);
+                FAIL_WITH(c, kStatusTimeout, (4ull << 32) | (static_cast<uint64_t>(q) << 16) | entry);  // 4: import table
                 return false;
             }
         }
@@ -899,8 +926,7 @@ __device__ __forceinline__ bool first_barrier(const DirectArgs& a, uint32_t targ
                         t0 = now;
                     else if (now - t0 > c.timeout_ns) {
                         ok = 0;
-                        if (c.status != nullptr)
-                            atomicCAS(c.status, 0, kStatusTimeout);
+                        FAIL_WITH(c, kStatusTimeout, (5ull << 32) | static_cast<uint64_t>(q));  // 5: a peer's buffer words
                         break;
                     }
                 }
@@ -1171,9 +1197,14 @@ template <typename Tin, typename Tout, bool NVLS>
 __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) {
     __shared__ CallBufs cb;
     __shared__ int s_ok;
+    __shared__ uint32_t s_round[16];  // a root's storing warps: rounds issued (see warp_round_done)
     const CommonArgs& c = a.c;
     const int n = c.nranks, rank = c.rank;
     constexpr uint64_t V = 16 / sizeof(Tin);
+    if (threadIdx.x < 16)
+        s_round[threadIdx.x] = 0;
+    if (threadIdx.x == 0)
+        s_ok = 1;
     uint32_t epoch = c.epoch;
     stamp(c, 0);
     // inputs are final / outputs may be overwritten on every rank
@@ -1237,10 +1268,16 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
             const uint64_t per_cta = round_up_u64((S + gridDim.x - 1) / gridDim.x, 16);
             const uint64_t b = min(S, per_cta * blockIdx.x), e = min(S, b + per_cta);
             if (rank == root) {
-                if (n == 2)
-                    cta_copy(g, cb.out[1 - rank] + b, my_in + b, e - b);
-                if (my_out != my_in)
-                    cta_copy(g, my_out + b, my_in + b, e - b);
+                // every vector is loaded once and stored to the other rank and to the root's own output
+                char* dst[kMaxRanks];
+#pragma unroll
+                for (int j = 0; j < kMaxRanks; ++j)
+                    dst[j] = nullptr;
+                dst[0] = n == 2 ? cb.out[1 - rank] + b : nullptr;
+                dst[1] = my_out != my_in ? my_out + b : nullptr;
+                const bool vec = ((reinterpret_cast<uint64_t>(my_in + b) | reinterpret_cast<uint64_t>(dst[0]) |
+                                   reinterpret_cast<uint64_t>(dst[1])) & 15) == 0;
+                cta_fanout(g, dst, 2, my_in + b, e - b, vec);
             }
         } else {
             const BcastPlan pl = bcast_plan(S, n, gridDim.x, a.chunk_bytes);
@@ -1253,19 +1290,18 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                 *hi = min(L, min(sb + pl.per_cta, sb + static_cast<uint64_t>(k + 1) * a.chunk_bytes));
             };
             if (rank == root) {
-                // The last warp only announces: the other warps store round after round (chunk k
-                // of every slice) without ever waiting for a store to be acknowledged.  After
-                // each round they arrive on one of eight named barriers in turn; the announcing
-                // warp waits on it and then publishes the chunk counter to all forwarders with one
-                // warp-wide releasing store (lane v to the forwarder of slice v), which is what
-                // takes a round trip.  Every eighth round the storing warps wait for the announcing
-                // warp, so that they can never arrive twice on a barrier it has not passed yet.
-                constexpr int kSigBarriers = 8;
+                // The last warp only announces; the other warps store round after round (chunk k of
+                // every slice, and the same bytes into the root's own output) without ever waiting
+                // for a store to be acknowledged or for the announcing warp.  Each storing warp
+                // counts the rounds it has issued in shared memory; the announcing warp takes the
+                // minimum and, whenever that has grown, publishes it to all forwarders with one
+                // warp-wide releasing store (lane v to the forwarder of slice v).  The release waits
+                // for the stores issued so far, which under load takes as long as several rounds:
+                // the next announcement then simply covers all of them.
                 const unsigned ncopy = blockDim.x - 32;
                 const bool announcer = threadIdx.x >= ncopy;
-                for (uint32_t k = 0; k < pl.chunks; ++k) {
-                    const int bar_id = 1 + static_cast<int>(k % kSigBarriers);
-                    if (!announcer) {
+                if (!announcer) {
+                    for (uint32_t k = 0; k < pl.chunks; ++k) {
                         // slice by slice, starting with a different one in every round and in every
                         // CTA: at any moment the CTAs store to all destinations alike (all of them
                         // storing to one destination at a time would be limited by that GPU's link)
@@ -1274,32 +1310,31 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                             const int j = (root + 1 + v) % n;
                             uint64_t lo, hi;
                             chunk_range(v, k, &lo, &hi);
-                            if (hi > lo)
+                            if (hi > lo) {
                                 cta_copy_part(g, cb.out[j] + v * pl.slice + lo, my_in + v * pl.slice + lo, hi - lo,
                                               threadIdx.x, ncopy);
+                                if (my_out != my_in)
+                                    cta_copy_part(g, my_out + v * pl.slice + lo, my_in + v * pl.slice + lo, hi - lo,
+                                                  threadIdx.x, ncopy);
+                            }
                         }
-                        if (k % kSigBarriers == kSigBarriers - 1)
-                            named_bar_sync(bar_id, blockDim.x);
-                        else
-                            named_bar_arrive(bar_id, blockDim.x);
-                    } else {
-                        named_bar_sync(bar_id, blockDim.x);
-                        const int v = static_cast<int>(threadIdx.x - ncopy);
-                        if (v < n - 1) {
-                            const int j = (root + 1 + v) % n;
-                            st_release_sys(reinterpret_cast<uint32_t*>(c.peers.heap[j] + kChunkFlagOff) + blockIdx.x,
-                                           a.chunk_base + k + 1);
-                        }
+                        warp_round_done(s_round, k + 1);
                     }
-                }
-                __syncthreads();
-                if (my_out != my_in) {
-                    for (int v = 0; v < n - 1; ++v) {
-                        const uint64_t s0 = static_cast<uint64_t>(v) * pl.slice;
-                        const uint64_t L = s0 >= S ? 0 : min(pl.slice, S - s0);
-                        const uint64_t lo = min(L, sb), hi = min(L, sb + pl.per_cta);
-                        if (hi > lo)
-                            cta_copy(g, my_out + s0 + lo, my_in + s0 + lo, hi - lo);
+                } else {
+                    uint32_t published = 0;
+                    while (published < pl.chunks) {
+                        const uint32_t m = rounds_done_by_all(s_round, ncopy / 32);
+                        if (m > published) {
+                            const int v = static_cast<int>(threadIdx.x - ncopy);
+                            if (v < n - 1) {
+                                const int j = (root + 1 + v) % n;
+                                st_release_sys(reinterpret_cast<uint32_t*>(c.peers.heap[j] + kChunkFlagOff) + blockIdx.x,
+                                               a.chunk_base + m);
+                            }
+                            published = m;
+                        } else {
+                            __nanosleep(100);
+                        }
                     }
                 }
             } else {
@@ -1312,7 +1347,7 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                     if (hi <= lo)
                         continue;  // (uniform over the CTA) nothing to wait for, nothing to forward
                     if (threadIdx.x == 0)
-                        s_ok = wait_flag_reached(c, my_flag, a.chunk_base + k + 1) ? 1 : 0;
+                        s_ok = wait_flag_reached(c, my_flag, a.chunk_base + k + 1, 2) ? 1 : 0;
                     __syncthreads();
                     if (!s_ok)
                         return;
@@ -1355,17 +1390,13 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
             return a.stage_off + (static_cast<uint64_t>(blockIdx.x) * a.stage_slots + k % a.stage_slots) * a.chunk_bytes;
         };
         if (rank == root) {
-            constexpr int kSigBarriers = 8;
+            // (storing warps and announcing warp as in the broadcast above)
             const unsigned ncopy = blockDim.x - 32;
             const bool announcer = threadIdx.x >= ncopy;
-            if (threadIdx.x == 0)
-                s_ok = 1;
-            __syncthreads();
-            for (uint32_t k = 0; k < pl.chunks; ++k) {
-                const int bar_id = 1 + static_cast<int>(k % kSigBarriers);
-                if (!announcer) {
+            if (!announcer) {
+                for (uint32_t k = 0; k < pl.chunks; ++k) {
                     if (k >= a.stage_slots) {
-                        // the slot still holds chunk k - stage_slots until every reducer has consumed it
+                        // the slot still holds chunk k - stage_slots until its reducer has consumed it
                         if (threadIdx.x < static_cast<unsigned>(n - 1) && s_ok) {
                             const int j = (root + 1 + static_cast<int>(threadIdx.x)) % n;
                             const uint32_t* credit = reinterpret_cast<const uint32_t*>(c.peers.heap[rank] + kCreditOff) +
@@ -1373,8 +1404,8 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                             uint64_t lo, hi;
                             chunk_range(static_cast<int>(threadIdx.x), k - a.stage_slots, &lo, &hi);
                             // (a reducer reports only chunks that held something)
-                            if (hi > lo && !wait_flag_reached(c, credit, a.chunk_base + (k - a.stage_slots) + 1))
-                                s_ok = 0;  // (status says why; the loop runs on without waiting so that every barrier completes)
+                            if (hi > lo && !wait_flag_reached(c, credit, a.chunk_base + (k - a.stage_slots) + 1, 3))
+                                s_ok = 0;  // (status says why; the loop runs on without waiting, so the kernel ends)
                         }
                         named_bar_sync(9, ncopy);
                     }
@@ -1387,17 +1418,22 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                             cta_copy_part(g, c.peers.heap[j] + slot_off(k), my_in + (v * pl.slice + lo) * sizeof(Tin),
                                           (hi - lo) * sizeof(Tin), threadIdx.x, ncopy);
                     }
-                    if (k % kSigBarriers == kSigBarriers - 1)
-                        named_bar_sync(bar_id, blockDim.x);
-                    else
-                        named_bar_arrive(bar_id, blockDim.x);
-                } else {
-                    named_bar_sync(bar_id, blockDim.x);
-                    const int v = static_cast<int>(threadIdx.x - ncopy);
-                    if (v < n - 1) {
-                        const int j = (root + 1 + v) % n;
-                        st_release_sys(reinterpret_cast<uint32_t*>(c.peers.heap[j] + kChunkFlagOff) + blockIdx.x,
-                                       a.chunk_base + k + 1);
+                    warp_round_done(s_round, k + 1);
+                }
+            } else {
+                uint32_t published = 0;
+                while (published < pl.chunks) {
+                    const uint32_t m = rounds_done_by_all(s_round, ncopy / 32);
+                    if (m > published) {
+                        const int v = static_cast<int>(threadIdx.x - ncopy);
+                        if (v < n - 1) {
+                            const int j = (root + 1 + v) % n;
+                            st_release_sys(reinterpret_cast<uint32_t*>(c.peers.heap[j] + kChunkFlagOff) + blockIdx.x,
+                                           a.chunk_base + m);
+                        }
+                        published = m;
+                    } else {
+                        __nanosleep(100);
                     }
                 }
             }
@@ -1413,7 +1449,7 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                 const uint64_t in_byte0 = (v * pl.slice + lo) * sizeof(Tin);
                 const uint64_t out_byte0 = (v * pl.slice + lo) * sizeof(Tout);
                 if (threadIdx.x == 0) {
-                    s_ok = wait_flag_reached(c, my_flag, a.chunk_base + k + 1) ? 1 : 0;
+                    s_ok = wait_flag_reached(c, my_flag, a.chunk_base + k + 1, 2) ? 1 : 0;
                     // the root's part of this chunk: in the slot, addressed like the other inputs
                     cb.in[root] = c.peers.heap[rank] + slot_off(k) - in_byte0;
                 }

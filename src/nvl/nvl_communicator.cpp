@@ -361,6 +361,17 @@ void NvlCommunicator::adopt_device_status() {
                          static_cast<unsigned>(rec[2] & 0xffffffffu), m_guard.in, m_guard.in_bytes, m_guard.out,
                          m_guard.out_bytes, m_guard.peer_in_bytes, m_guard.peer_out_bytes);
         (void)cudaGetLastError();
+    } else {
+        uint64_t rec[3] = {0, 0, 0};
+        (void)cudaDeviceSynchronize();
+        if (cudaMemcpy(rec, m_heap.local() + mgk::coll::kDebugOff + 32, sizeof(rec), cudaMemcpyDeviceToHost) == cudaSuccess &&
+            rec[0] != 0)
+            MEGRAY_ERROR("rank %u: a collective kernel gave up with status %d at collectives.cu line %u (what %u, detail 0x%x)",
+                         m_rank, static_cast<int>(m_error), static_cast<unsigned>(rec[0]), static_cast<unsigned>(rec[1] >> 32),
+                         static_cast<unsigned>(rec[1] & 0xffffffffu));
+        else
+            MEGRAY_ERROR("rank %u: a kernel reported status %d", m_rank, static_cast<int>(m_error));
+        (void)cudaGetLastError();
     }
 }
 

@@ -25,7 +25,8 @@ for fused in (True, False):
     dy = (y.float() * 1e-3).to(torch.bfloat16)
     dx = model.backward(dy).clone()
     torch.cuda.synchronize()
-    assert int(gemm_error_flag(dev).item()) == 0 and comm.status == 0
+    flag, status = int(gemm_error_flag(dev).item()), comm.status
+    assert flag == 0 and status == 0, f"fused={fused}: GEMM error flag {flag}, communicator status {status}"
     results[fused] = (y, dx, [l.g_gu.clone() for l in model.layers], [l.g_down.clone() for l in model.layers])
     del model
     torch.cuda.empty_cache()
