@@ -9,8 +9,8 @@ operation, the largest size up to which the flagged-word kernel is the fastest; 
 also the size up to which the one-shot kernel beats the single-pass one; and, when the NVSwitch
 multicast object can be set up (``--nvls``: MEGRAY_NVLS=1 in the benchmark processes only), the
 size from which the multimem kernels beat plain peer loads and stores on heap buffers.  It also
-picks the grid size, the bytes per CTA of the single-pass kernels, the chunk of the pipelined
-broadcast and the pause of long waits by the summed time over a few sizes.
+picks the grid size, the bytes per CTA of the single-pass kernels and the chunk of the pipelined
+broadcast by the summed time over a few sizes, and the size from which a reduce has its root push.
 
     python bench/tune.py --devices 8 --out megray_b200/tune/tune_b200_n8.json
 """
@@ -25,9 +25,9 @@ KINDS = ["all_reduce", "reduce_scatter", "all_gather", "all_to_all", "broadcast"
 
 
 def run(devices, funcs, sizes, env, extra=()):
-    e = dict(os.environ, **env)
+    e = dict(os.environ, MEGRAY_NVL_P2P="0", **env)  # (no send/recv here: skip setting up its engine)
     cmd = [os.path.join(ROOT, "build", "megray_bench"), "-d", str(devices), "-e", "nvl", "-f", ",".join(funcs),
-           "-s", ",".join(str(s) for s in sizes), "-t", "float32", "-w", "10", "-i", "40", "-j", *extra]
+           "-s", ",".join(str(s) for s in sizes), "-t", "float32", "-w", "5", "-i", "25", "-j", *extra]
     out = subprocess.run(cmd, capture_output=True, text=True, env=e, timeout=900)
     res = {}
     for line in out.stdout.splitlines():
@@ -103,7 +103,7 @@ def main():
             table[key] = best_v
 
     # bytes per CTA of the single-pass kernels in the middle sizes (more CTAs: more bytes in
-    # flight, but a longer barrier), chunk of the pipelined broadcast, pause of long waits
+    # flight, but a longer barrier), chunk of the pipelined broadcast
     pick("direct_cta_bytes", (16 << 10, 32 << 10, 128 << 10), KINDS, [1 << 20, 4 << 20, 16 << 20], "MEGRAY_DIRECT_CTA_BYTES")
     if a.devices > 2:
         pick("bcast_chunk_bytes", (32 << 10, 64 << 10, 256 << 10, 1 << 20), ["broadcast"], [4 << 20, 64 << 20, 1 << 30],

@@ -28,6 +28,8 @@ IpcCache::~IpcCache() {
         for (void* base : per_rank)
             if (base != nullptr)
                 cudaIpcCloseMemHandle(base);
+    if (m_probe != nullptr)
+        cudaFree(m_probe);
     if (m_stream != nullptr)
         cudaStreamDestroy(m_stream);
     if (m_table_dev != nullptr)
@@ -81,6 +83,31 @@ bool IpcCache::init(Client& client, uint32_t nranks, uint32_t rank, int device) 
             return false;
     m_imported.assign(nranks, 0);
     m_mappings.assign(nranks, std::vector<void*>());
+    // Every rank exports a small allocation now and maps everybody else's before any collective
+    // runs: the first mapping of a peer's memory switches on peer access to its device, which
+    // touches every allocation of this context and is best done while the devices are idle.
+    {
+        uint64_t word = 0;
+        int32_t probe_ok = cudaMalloc(&m_probe, 2u << 20) == cudaSuccess && resolve(m_probe, 2u << 20, &word) ? 1 : 0;
+        (void)cudaGetLastError();
+        if (client.allgather(&probe_ok, all.data(), sizeof(int32_t)) != MEGRAY_OK)
+            return false;
+        bool fine = true;
+        for (uint32_t q = 0; q < nranks; ++q)
+            fine = fine && all[q] != 0;
+        if (fine) {
+            import_new();  // (everybody's probe is in the logs: the allgather came after the exports)
+            for (uint32_t q = 0; q < nranks; ++q)
+                if (q != rank && m_imported[q] == 0)
+                    fine = false;
+        }
+        probe_ok = fine ? 1 : 0;
+        if (client.allgather(&probe_ok, all.data(), sizeof(int32_t)) != MEGRAY_OK)
+            return false;
+        for (uint32_t q = 0; q < nranks; ++q)
+            if (!all[q])
+                return false;
+    }
     m_helper = std::thread([this] { helper_main(); });
     return true;
 }
@@ -112,6 +139,9 @@ bool IpcCache::resolve(const void* p, size_t bytes, uint64_t* word) {
         *word = encode(it->second.entry, at - start);
         return true;
     }
+    // A new allocation here usually means new ones on the peers at the same point of the program:
+    // map what they have published so far on this thread, before this rank's kernel is launched.
+    import_new();
     RankLog* mine = log(m_rank);
     const uint32_t entry = mine->count.load(std::memory_order_relaxed);
     if (entry >= kMaxExports)
@@ -138,10 +168,19 @@ bool IpcCache::resolve(const void* p, size_t bytes, uint64_t* word) {
     }
     m_cv.notify_all();
     *word = encode(entry, at - start);
+    // Give the peers a moment to publish theirs and map them here, on this thread, while this
+    // rank's kernel is not yet on the device (whatever comes later is the helper thread's).
+    if (m_helper.joinable()) {
+        const auto until = std::chrono::steady_clock::now() + std::chrono::microseconds(300);
+        do {
+            import_new();
+        } while (std::chrono::steady_clock::now() < until);
+    }
     return true;
 }
 
 bool IpcCache::import_new() {
+    std::lock_guard<std::mutex> guard(m_import_mu);
     bool any = false;
     for (uint32_t q = 0; q < m_nranks; ++q) {
         if (q == m_rank)
@@ -153,11 +192,9 @@ bool IpcCache::import_new() {
             const ExportSlot& s = theirs->slots[e];
             uint64_t mapped = kImportFailed;
             void* to_close = nullptr;
-            if (s.supersedes != ~0u && s.supersedes < m_mappings[q].size() && m_mappings[q][s.supersedes] != nullptr) {
-                // the owner freed that allocation and got the same address again
-                cudaIpcCloseMemHandle(m_mappings[q][s.supersedes]);
-                m_mappings[q][s.supersedes] = nullptr;
-            }
+            // (A superseded mapping - the owner freed that allocation and got the same address
+            // again - stays open until this object goes: closing one waits for the device, and
+            // the device may be running a kernel that waits for this very import.)
             if (s.pid == static_cast<int32_t>(getpid())) {
                 // another rank of this very process: its address is valid here once peer access is on
                 cudaError_t pe = cudaDeviceEnablePeerAccess(s.device, 0);

@@ -17,7 +17,9 @@
 //     by the device timeout, like every other wait), so no rank ever waits on the host.
 //
 // An allocation is recognised by its base address and CUDA buffer id: memory that was freed and
-// allocated again at the same address gets a new entry, and the importers close the old mapping.
+// allocated again at the same address gets a new entry (the old mapping stays open until the
+// communicator goes: closing one waits for the device, which may be running a kernel that waits
+// for an import).
 // Memory that cannot be exported (virtual-memory-management allocations, host memory) is not
 // handled here: the caller copies through a buffer of its own, which can.
 #pragma once
@@ -98,6 +100,8 @@ private:
     std::atomic<bool> m_stop{false};
     std::atomic<uint32_t> m_imports_done{0};
     std::mutex m_mu;
+    std::mutex m_import_mu;  // import_new() runs on the helper thread and, before a launch, on the caller's
+    void* m_probe = nullptr;  // exported at init so that peer access is switched on before any collective
     std::condition_variable m_cv;
     bool m_kick = false;
     // exporter side (calling thread)
