@@ -6,8 +6,9 @@ reference's test/performance.cpp does.)  Under torchrun:
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29750 bench/comm_bench_procs.py --backend nvl --sizes 1M,64M,1G
 
-``--backend nvl`` is the native backend (allocations exported and mapped on first use, then the
-single-pass kernels), ``--backend nccl`` this library's wrapper around NCCL, i.e. the calls the
+``--backend nvl`` is the native backend (the two buffers are registered once, so every peer has
+them mapped and calls of any size take the single-pass kernels; with ``--no-register`` allocations
+up to 64 MiB are still exported and mapped on first use, larger calls take the staged kernels), ``--backend nccl`` this library's wrapper around NCCL, i.e. the calls the
 reference's NCCL backend makes (src/nccl/communicator.cpp:170-228).  Device-timed with CUDA
 events, max over ranks; prints the JSON lines of build/megray_bench (bench/sweep_table.py reads
 both).  ``bytes`` is the per-rank unit as in that tool: the whole message for all_reduce /
@@ -40,6 +41,9 @@ def main():
     ap.add_argument("--sizes", default="64K,1M,16M,256M")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-register", action="store_true",
+                    help="nvl: leave the two buffers unregistered (calls above the automatic-export limit, 64 MiB "
+                         "per buffer, then take the staged kernels)")
     a = ap.parse_args()
     rank, n = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -54,6 +58,9 @@ def main():
     dst = torch.zeros(cap * n, device=dev)
     tmax = torch.zeros(1, device=dev)
     tall = torch.zeros(n, device=dev)
+    if a.backend == "nvl" and not a.no_register:
+        # one call per buffer, as a framework does for its communication buffers: every peer maps them
+        assert comm.register(src) and comm.register(dst)
     for _ in range(20):  # clocks up, links trained, first-call work done
         comm.all_reduce(src[:4096], dst[:4096])
     torch.cuda.synchronize()

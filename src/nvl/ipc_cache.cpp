@@ -1,5 +1,6 @@
 #include "nvl/ipc_cache.h"
 
+#include <stdlib.h>
 #include <string.h>
 #include <unistd.h>
 
@@ -41,6 +42,8 @@ bool IpcCache::init(Client& client, uint32_t nranks, uint32_t rank, int device) 
     m_nranks = nranks;
     m_rank = rank;
     m_device = device;
+    if (const char* v = getenv("MEGRAY_IPC_AUTO_MAX_MB"))
+        m_auto_max = static_cast<size_t>(atoll(v)) << 20;
     // rank 0 names and creates the region; the others attach
     char name[64];
     memset(name, 0, sizeof(name));
@@ -53,8 +56,11 @@ bool IpcCache::init(Client& client, uint32_t nranks, uint32_t rank, int device) 
         if (!m_region)
             mine = 0;
         else
-            for (uint32_t q = 0; q < nranks; ++q)
+            for (uint32_t q = 0; q < nranks; ++q) {
                 log(q)->count.store(0, std::memory_order_relaxed);
+                for (auto& a : log(q)->imported_from)
+                    a.store(0, std::memory_order_relaxed);
+            }
     }
     if (client.broadcast(name, name, sizeof(name), 0) != MEGRAY_OK)
         return false;
@@ -112,7 +118,7 @@ bool IpcCache::init(Client& client, uint32_t nranks, uint32_t rank, int device) 
     return true;
 }
 
-bool IpcCache::resolve(const void* p, size_t bytes, uint64_t* word) {
+bool IpcCache::resolve(const void* p, size_t bytes, uint64_t* word, bool any_size) {
     const drv::Api* api = drv::api();
     if (api == nullptr || p == nullptr)
         return false;
@@ -139,6 +145,8 @@ bool IpcCache::resolve(const void* p, size_t bytes, uint64_t* word) {
         *word = encode(it->second.entry, at - start);
         return true;
     }
+    if (size > m_auto_max && !any_size)
+        return false;
     // A new allocation here usually means new ones on the peers at the same point of the program:
     // map what they have published so far on this thread, before this rank's kernel is launched.
     import_new();
@@ -177,6 +185,48 @@ bool IpcCache::resolve(const void* p, size_t bytes, uint64_t* word) {
         } while (std::chrono::steady_clock::now() < until);
     }
     return true;
+}
+
+bool IpcCache::entry_acked(uint32_t entry) {
+    for (uint32_t q = 0; q < m_nranks; ++q)
+        if (q != m_rank && log(q)->imported_from[m_rank].load(std::memory_order_acquire) <= entry)
+            return false;
+    return true;
+}
+
+bool IpcCache::mapped_everywhere(const void* p, size_t bytes) {
+    const drv::Api* api = drv::api();
+    if (api == nullptr || p == nullptr)
+        return false;
+    CUdeviceptr start = 0;
+    size_t size = 0;
+    unsigned long long buffer_id = 0;
+    CUpointer_attribute attrs[3] = {CU_POINTER_ATTRIBUTE_RANGE_START_ADDR, CU_POINTER_ATTRIBUTE_RANGE_SIZE,
+                                    CU_POINTER_ATTRIBUTE_BUFFER_ID};
+    void* vals[3] = {&start, &size, &buffer_id};
+    const CUdeviceptr at = reinterpret_cast<CUdeviceptr>(p);
+    if (api->PointerGetAttributes(3, attrs, vals, at) != CUDA_SUCCESS || at < start || at + bytes > start + size)
+        return false;
+    auto it = m_known.find(start);
+    return it != m_known.end() && it->second.buffer_id == buffer_id && it->second.size == size &&
+           entry_acked(it->second.entry);
+}
+
+Status IpcCache::register_range(const void* p, size_t bytes, int64_t timeout_ms) {
+    uint64_t word = 0;
+    if (!resolve(p, bytes, &word, true))
+        return MEGRAY_NOT_IMPLEMENTED;
+    const uint32_t entry = static_cast<uint32_t>(word >> 48);
+    const auto until = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+    while (!entry_acked(entry)) {
+        if (std::chrono::steady_clock::now() > until)
+            return MEGRAY_TIMEOUT;
+        import_new();  // (the peers register theirs at the same point: map them here meanwhile)
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+    // ... and until this rank has mapped what the peers have published so far (their registrations)
+    import_new();
+    return MEGRAY_OK;
 }
 
 bool IpcCache::import_new() {
@@ -218,6 +268,7 @@ bool IpcCache::import_new() {
             cudaStreamSynchronize(m_stream);
             (void)cudaGetLastError();
             ++m_imported[q];
+            log(m_rank)->imported_from[q].store(m_imported[q], std::memory_order_release);
             m_imports_done.fetch_add(1);
             any = true;
         }

@@ -62,8 +62,21 @@ public:
     bool init(Client& client, uint32_t nranks, uint32_t rank, int device);
 
     /** The (entry, offset) of [p, p + bytes) for the peers, exporting its allocation if this is the
-     *  first time.  False: the memory cannot be exported (or the log is full). */
-    bool resolve(const void* p, size_t bytes, uint64_t* word);
+     *  first time.  False: the memory cannot be exported, the log is full, or the allocation is
+     *  larger than auto_max_bytes() and `any_size` is false (such allocations are only exported
+     *  through registration, which waits for the peers: mapping a large allocation was seen to
+     *  wait for the importing device, which may be running a kernel that waits for the mapping). */
+    bool resolve(const void* p, size_t bytes, uint64_t* word, bool any_size = false);
+
+    /** True when [p, p + bytes) lies in an allocation that is exported and mapped by every peer. */
+    bool mapped_everywhere(const void* p, size_t bytes);
+
+    /** Exports the allocation of [p, p + bytes) whatever its size and waits until every peer has
+     *  mapped it.  Collective by contract: every rank registers its corresponding buffer, at a
+     *  point where no collective on it is in flight. */
+    Status register_range(const void* p, size_t bytes, int64_t timeout_ms);
+
+    size_t auto_max_bytes() const { return m_auto_max; }
 
     /** Device table: [rank q][entry e] -> where export e of rank q is mapped here (0: not yet). */
     const uint64_t* table() const { return m_table_dev; }
@@ -85,6 +98,8 @@ private:
     struct RankLog {
         std::atomic<uint32_t> count;
         uint32_t pad[15];
+        // written by this log's rank as an importer: how many entries of rank q's log it has mapped
+        std::atomic<uint32_t> imported_from[16];
         ExportSlot slots[kMaxExports];
     };
     RankLog* log(uint32_t q) { return reinterpret_cast<RankLog*>(m_region->slot(q)); }
@@ -101,6 +116,8 @@ private:
     std::atomic<uint32_t> m_imports_done{0};
     std::mutex m_mu;
     std::mutex m_import_mu;  // import_new() runs on the helper thread and, before a launch, on the caller's
+    size_t m_auto_max = 64u << 20;  // MEGRAY_IPC_AUTO_MAX_MB
+    bool entry_acked(uint32_t entry);
     void* m_probe = nullptr;  // exported at init so that peer access is switched on before any collective
     std::condition_variable m_cv;
     bool m_kick = false;

@@ -635,6 +635,24 @@ void* NvlCommunicator::bounce(int which, size_t bytes) {
     return m_bounce[which];
 }
 
+// Ranks in separate processes: may this call take the single-pass kernels?  Up to
+// auto_max_bytes() per buffer always (allocations are exported on first use, a large one is
+// replaced by a bounce buffer).  Above, only when every buffer this rank passes lies in the heap
+// or in an allocation that every peer has mapped already (register_buffer sees to that):
+// mapping a large allocation can wait for the importing device, and a kernel that waits for the
+// mapping would then wait for itself.  The rule depends on sizes and on what the program did on
+// every rank alike, so all ranks take the same path.
+bool NvlCommunicator::exchange_fits(const void* in, size_t in_bytes, const void* out, size_t out_bytes) {
+    if (m_ipc == nullptr)
+        return true;
+    if (std::max(in != nullptr ? in_bytes : 0, out != nullptr ? out_bytes : 0) <= m_ipc->auto_max_bytes())
+        return true;
+    auto fine = [&](const void* p, size_t bytes) {
+        return p == nullptr || in_heap(p, bytes) || m_ipc->mapped_everywhere(p, bytes);
+    };
+    return fine(in, in_bytes) && fine(out, out_bytes);
+}
+
 Status NvlCommunicator::exchange_launch(int kind, const void* in, size_t in_bytes, bool in_shared, void* out,
                                         size_t out_bytes, bool out_shared, size_t len, DType in_dtype,
                                         DType out_dtype, float scale, ReduceOp op, uint32_t root,
@@ -658,7 +676,7 @@ Status NvlCommunicator::exchange_launch(int kind, const void* in, size_t in_byte
             *word = IpcCache::encode(IpcCache::kEntryHeap, static_cast<uint64_t>(static_cast<const char*>(p) - m_heap.local()));
             return true;
         }
-        return m_ipc->resolve(p, bytes, word);
+        return m_ipc->resolve(p, bytes, word, p == m_bounce[0] || p == m_bounce[1]);
     };
     if (in == nullptr || !in_shared) {
         // (peers never touch it: nothing to describe)
@@ -816,7 +834,8 @@ Status NvlCommunicator::reduce_impl(ReduceKind kind, const void* in, void* out, 
     }
 
     // Ranks of one process: single pass on the buffers as they are.
-    if (m_xchg && m_direct) {
+    if (m_xchg && m_direct &&
+        exchange_fits(in, len * ein * (kind == ReduceKind::ReduceScatter ? n : 1), wants_out ? out : nullptr, len * eout)) {
         if (kind == ReduceKind::AllReduce && (len * ein > m_oneshot_bytes || !m_oneshot_first))
             return exchange_launch(mgk::coll::DIRECT_ALL_REDUCE, in, len * ein, true, out, len * eout, true, len,
                                    in_dtype, out_dtype, scale, op, 0, stream);
@@ -976,7 +995,7 @@ Status NvlCommunicator::all_gather(const void* sendbuff, void* recvbuff, size_t 
             l.recv_off[q] = static_cast<int64_t>(q * bytes);
         return ll_launch(l, stream);
     }
-    if (m_xchg && m_direct)
+    if (m_xchg && m_direct && exchange_fits(sendbuff, bytes, recvbuff, bytes * m_nranks))
         return exchange_launch(mgk::coll::DIRECT_ALL_GATHER, sendbuff, bytes, false, recvbuff, bytes * m_nranks, true,
                                bytes, MEGRAY_UINT8, MEGRAY_UINT8, 1.0f, MEGRAY_SUM, 0, stream);
     if (m_direct && m_nranks > 1 && bytes > m_oneshot_bytes / m_nranks && aligned_heap(recvbuff, bytes * m_nranks) &&
@@ -1037,7 +1056,7 @@ Status NvlCommunicator::all_to_all(const void* sendbuff, void* recvbuff, size_t 
             l.send_off[q] = l.recv_off[q] = static_cast<int64_t>(q * bytes);
         return ll_launch(l, stream);
     }
-    if (m_xchg && m_direct)
+    if (m_xchg && m_direct && exchange_fits(sendbuff, bytes * m_nranks, recvbuff, bytes * m_nranks))
         return exchange_launch(mgk::coll::DIRECT_ALL_TO_ALL, sendbuff, bytes * m_nranks, false, recvbuff,
                                bytes * m_nranks, true, bytes, MEGRAY_UINT8, MEGRAY_UINT8, 1.0f, MEGRAY_SUM, 0, stream);
     if (m_direct && m_nranks > 1 && bytes > m_oneshot_bytes / m_nranks && aligned_heap(recvbuff, bytes * m_nranks) &&
@@ -1102,7 +1121,7 @@ Status NvlCommunicator::broadcast(const void* sendbuff, void* recvbuff, size_t l
         }
         return ll_launch(l, stream);
     }
-    if (m_xchg && m_direct)
+    if (m_xchg && m_direct && exchange_fits(m_rank == root ? sendbuff : nullptr, bytes, recvbuff, bytes))
         return exchange_launch(mgk::coll::DIRECT_BROADCAST, m_rank == root ? sendbuff : nullptr, bytes, false,
                                recvbuff, bytes, true, bytes, MEGRAY_UINT8, MEGRAY_UINT8, 1.0f, MEGRAY_SUM, root,
                                stream);
@@ -1179,7 +1198,7 @@ Status NvlCommunicator::gather(const void* sendbuff, void* recvbuff, size_t send
         }
         return ll_launch(l, stream);
     }
-    if (m_xchg && m_direct)
+    if (m_xchg && m_direct && exchange_fits(sendbuff, bytes, m_rank == root ? recvbuff : nullptr, bytes * m_nranks))
         return exchange_launch(mgk::coll::DIRECT_GATHER, sendbuff, bytes, false, m_rank == root ? recvbuff : nullptr,
                                bytes * m_nranks, true, bytes, MEGRAY_UINT8, MEGRAY_UINT8, 1.0f, MEGRAY_SUM, root,
                                stream);
@@ -1241,7 +1260,7 @@ Status NvlCommunicator::scatter(const void* sendbuff, void* recvbuff, size_t rec
         }
         return ll_launch(l, stream);
     }
-    if (m_xchg && m_direct)
+    if (m_xchg && m_direct && exchange_fits(m_rank == root ? sendbuff : nullptr, bytes * m_nranks, recvbuff, bytes))
         return exchange_launch(mgk::coll::DIRECT_SCATTER, m_rank == root ? sendbuff : nullptr, bytes * m_nranks, false,
                                recvbuff, bytes, true, bytes, MEGRAY_UINT8, MEGRAY_UINT8, 1.0f, MEGRAY_SUM, root,
                                stream);
@@ -1513,12 +1532,14 @@ Status NvlCommunicator::register_buffer(void* ptr, size_t bytes) {
     // reported to them as "this rank could not export its buffer", and every rank falls back.
     const bool bad_arg = ptr == nullptr || bytes == 0;
     if (m_ipc != nullptr) {
-        // Ranks in separate processes export allocations on first use anyway; registering one
-        // only does it ahead of time, so that the first collective on it finds it mapped.
-        uint64_t word = 0;
+        // Ranks in separate processes export allocations of moderate size on first use anyway;
+        // registering exports one of any size and returns when every peer has mapped it.
         if (bad_arg)
             return MEGRAY_INVALID_ARGUMENT;
-        return in_heap(ptr, bytes) || m_ipc->resolve(ptr, bytes, &word) ? MEGRAY_OK : MEGRAY_NOT_IMPLEMENTED;
+        if (in_heap(ptr, bytes))
+            return MEGRAY_OK;
+        // (waits until every peer has mapped it: afterwards calls of any size on it are single-pass)
+        return m_ipc->register_range(ptr, bytes, global_options().timeout_ms > 0 ? global_options().timeout_ms : 30000);
     }
     const drv::Api* api = drv::api();
     std::vector<RegInfo> all(m_nranks);

@@ -144,6 +144,7 @@ private:
     Status p2p_fork(cudaStream_t user);
     Status p2p_finish();
     bool peer_addressable(const void* p, size_t bytes);
+    bool exchange_fits(const void* in, size_t in_bytes, const void* out, size_t out_bytes);
     // extents of the current call's buffers, handed to the kernels (see CommonArgs::guard_in)
     void set_guard(const void* in, size_t in_bytes, void* out, size_t out_bytes);
     void* bounce(int which, size_t bytes);

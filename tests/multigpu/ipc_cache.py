@@ -77,9 +77,21 @@ comm.reduce(wide, wide_out, 0, "sum")
 if rank == 0:
     expect("reduce 24 MiB", wide_out, torch.full((6 * numel,), float(sum(range(1, n + 1)))))
 
+# 4. a call larger than what is exported automatically: staged until the buffers are registered
+huge = torch.full((20 * numel,), rank + 1.0, device=dev)  # 80 MiB
+huge_out = torch.empty_like(huge)
+before = comm.stats()["direct"]
+comm.all_reduce(huge, huge_out)
+expect("all_reduce 80 MiB, not registered", huge_out, torch.full((20 * numel,), float(sum(range(1, n + 1)))))
+assert comm.stats()["direct"] == before, "a large call on memory no peer has mapped must not wait for mappings in a kernel"
+assert comm.register(huge) and comm.register(huge_out)
+comm.all_reduce(huge, huge_out)
+expect("all_reduce 80 MiB, registered", huge_out, torch.full((20 * numel,), float(sum(range(1, n + 1)))))
+assert comm.stats()["direct"] == before + 1, comm.stats()
+
 st = comm.stats()
 assert st["timeouts"] == 0 and comm.status == 0, (st, comm.status)
-assert st["algo_direct"] >= 10, st  # the single-pass kernels ran, not the staged ones
+assert st["direct"] >= 10, st  # the single-pass kernels ran, not the staged ones
 assert not fails, fails[:10]
-print(f"RANK_OK {rank} direct={st['algo_direct']}", flush=True)
+print(f"RANK_OK {rank} direct={st['direct']}", flush=True)
 comm.close()
