@@ -1485,6 +1485,12 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
         if (a.kind == DIRECT_REDUCE_SCATTER) {
             elem0 = a.len * rank;
             L = a.len;
+        } else if (a.kind == DIRECT_REDUCE && n == 2) {
+            // two ranks: the root loads the other rank's input and reduces into its own output
+            // (loads only, like reduce_scatter; the other rank loading and storing back over the
+            // same link measured a quarter slower)
+            elem0 = 0;
+            L = rank == a.root ? a.len : 0;
         } else if (a.kind == DIRECT_REDUCE && n > 1) {
             if (rank == a.root) {
                 elem0 = 0;

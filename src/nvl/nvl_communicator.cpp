@@ -739,7 +739,7 @@ Status NvlCommunicator::exchange_launch(int kind, const void* in, size_t in_byte
         a.chunk_base = m_chunk_seq;
         m_chunk_seq += mgk::coll::bcast_plan(work, static_cast<int>(m_nranks), ctas, a.chunk_bytes).chunks;
     }
-    if (kind == mgk::coll::DIRECT_REDUCE && m_nranks > 1 && work >= m_reduce_staged_min && !nvls) {
+    if (kind == mgk::coll::DIRECT_REDUCE && m_nranks > 2 && work >= m_reduce_staged_min && !nvls) {
         // large messages: the root pushes its input into staging slots of the reducing ranks
         const size_t slice = (work + m_nranks - 2) / (m_nranks - 1);
         const int want = static_cast<int>(std::min<size_t>(std::max<size_t>(1, slice / (m_direct_cta_bytes / 2)), static_cast<size_t>(max_ctas)));
