@@ -41,13 +41,16 @@ def run(devices, funcs, sizes, env, extra=()):
 
 
 def crossover(sizes, a, b, func, margin=1.0):
-    """Largest size s such that a is at least as fast as b (times `margin`) at every size <= s."""
+    """Largest size s at which a is at least as fast as b (times `margin`), provided a is not
+    slower than b by more than 10 % anywhere below s (one noisy sample at a small size does not
+    switch a off altogether; a real loss does)."""
     best = 0
     for s in sizes:
         ta, tb = a.get((func, s)), b.get((func, s))
-        if ta is None or tb is None or ta[0] > tb[0] * margin:
+        if ta is None or tb is None or ta[0] > tb[0] * 1.10:
             break
-        best = s
+        if ta[0] <= tb[0] * margin:
+            best = s
     return best
 
 
@@ -56,6 +59,8 @@ def main():
     ap.add_argument("--devices", type=int, default=2)
     ap.add_argument("--out", default=None)
     ap.add_argument("--nvls", action="store_true", help="also measure the NVSwitch multimem kernels (heap buffers)")
+    ap.add_argument("--crossovers-only", action="store_true",
+                    help="measure the algorithm crossovers only; keep the default grid and chunk sizes")
     a = ap.parse_args()
     out_path = a.out or os.path.join(ROOT, "megray_b200", "tune", f"tune_b200_n{a.devices}.json")
     table = {"devices": a.devices, "measured": {}}
@@ -82,7 +87,7 @@ def main():
     # grid size of the single-pass kernels at a bandwidth-bound size
     big = [64 << 20]
     best_ctas, best_t = 64, None
-    for ctas in (32, 64):
+    for ctas in (() if a.crossovers_only else (32, 64)):
         r = run(a.devices, ["all_reduce", "all_gather"], big, {"MEGRAY_MAX_CTAS": str(ctas)})
         t = sum(v[0] for v in r.values()) if len(r) == 2 else None
         table["measured"][f"us_sum_at_{ctas}_ctas"] = t
@@ -92,6 +97,8 @@ def main():
 
     def pick(key, values, funcs, sizes, env_name):
         """The value of one knob with the smallest summed time over `funcs` x `sizes`."""
+        if a.crossovers_only:
+            return
         best_v, best_sum = None, None
         for v in values:
             r = run(a.devices, funcs, sizes, {env_name: str(v), "MEGRAY_TUNE_DEFAULT": "0", "MEGRAY_MAX_CTAS": str(best_ctas)})

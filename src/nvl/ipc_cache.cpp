@@ -29,8 +29,9 @@ IpcCache::~IpcCache() {
         for (void* base : per_rank)
             if (base != nullptr)
                 cudaIpcCloseMemHandle(base);
-    if (m_probe != nullptr)
-        cudaFree(m_probe);
+    for (void* b : m_bounce)
+        if (b != nullptr)
+            cudaFree(b);
     if (m_stream != nullptr)
         cudaStreamDestroy(m_stream);
     if (m_table_dev != nullptr)
@@ -89,26 +90,28 @@ bool IpcCache::init(Client& client, uint32_t nranks, uint32_t rank, int device) 
             return false;
     m_imported.assign(nranks, 0);
     m_mappings.assign(nranks, std::vector<void*>());
-    // Every rank exports a small allocation now and maps everybody else's before any collective
-    // runs: the first mapping of a peer's memory switches on peer access to its device, which
-    // touches every allocation of this context and is best done while the devices are idle.
+    // Every rank exports its two bounce buffers now and maps everybody else's before any collective
+    // runs.  A buffer of a call stands in for memory the peers have not mapped (yet); and the
+    // first mapping of a peer's memory switches on peer access to its device, which touches every
+    // allocation of this context and is best done while the devices are idle.
     {
+        m_bounce_bytes = m_auto_max + (2u << 20);
         uint64_t word = 0;
-        int32_t probe_ok = cudaMalloc(&m_probe, 2u << 20) == cudaSuccess && resolve(m_probe, 2u << 20, &word) ? 1 : 0;
+        int32_t fine = 1;
+        for (int i = 0; i < 2 && fine; ++i)
+            fine = cudaMalloc(&m_bounce[i], m_bounce_bytes) == cudaSuccess && resolve(m_bounce[i], m_bounce_bytes, &word, true) ? 1 : 0;
         (void)cudaGetLastError();
-        if (client.allgather(&probe_ok, all.data(), sizeof(int32_t)) != MEGRAY_OK)
+        if (client.allgather(&fine, all.data(), sizeof(int32_t)) != MEGRAY_OK)
             return false;
-        bool fine = true;
         for (uint32_t q = 0; q < nranks; ++q)
             fine = fine && all[q] != 0;
         if (fine) {
-            import_new();  // (everybody's probe is in the logs: the allgather came after the exports)
+            import_new();  // (everybody's two entries are in the logs: the allgather came after the exports)
             for (uint32_t q = 0; q < nranks; ++q)
-                if (q != rank && m_imported[q] == 0)
-                    fine = false;
+                if (q != rank && m_imported[q] < 2)
+                    fine = 0;
         }
-        probe_ok = fine ? 1 : 0;
-        if (client.allgather(&probe_ok, all.data(), sizeof(int32_t)) != MEGRAY_OK)
+        if (client.allgather(&fine, all.data(), sizeof(int32_t)) != MEGRAY_OK)
             return false;
         for (uint32_t q = 0; q < nranks; ++q)
             if (!all[q])
@@ -147,9 +150,6 @@ bool IpcCache::resolve(const void* p, size_t bytes, uint64_t* word, bool any_siz
     }
     if (size > m_auto_max && !any_size)
         return false;
-    // A new allocation here usually means new ones on the peers at the same point of the program:
-    // map what they have published so far on this thread, before this rank's kernel is launched.
-    import_new();
     RankLog* mine = log(m_rank);
     const uint32_t entry = mine->count.load(std::memory_order_relaxed);
     if (entry >= kMaxExports)
@@ -176,14 +176,6 @@ bool IpcCache::resolve(const void* p, size_t bytes, uint64_t* word, bool any_siz
     }
     m_cv.notify_all();
     *word = encode(entry, at - start);
-    // Give the peers a moment to publish theirs and map them here, on this thread, while this
-    // rank's kernel is not yet on the device (whatever comes later is the helper thread's).
-    if (m_helper.joinable()) {
-        const auto until = std::chrono::steady_clock::now() + std::chrono::microseconds(300);
-        do {
-            import_new();
-        } while (std::chrono::steady_clock::now() < until);
-    }
     return true;
 }
 
@@ -210,6 +202,31 @@ bool IpcCache::mapped_everywhere(const void* p, size_t bytes) {
     auto it = m_known.find(start);
     return it != m_known.end() && it->second.buffer_id == buffer_id && it->second.size == size &&
            entry_acked(it->second.entry);
+}
+
+bool IpcCache::resolve_mapped(const void* p, size_t bytes, uint64_t* word) {
+    const drv::Api* api = drv::api();
+    if (api == nullptr || p == nullptr)
+        return false;
+    CUdeviceptr start = 0;
+    size_t size = 0;
+    unsigned long long buffer_id = 0;
+    CUpointer_attribute attrs[3] = {CU_POINTER_ATTRIBUTE_RANGE_START_ADDR, CU_POINTER_ATTRIBUTE_RANGE_SIZE,
+                                    CU_POINTER_ATTRIBUTE_BUFFER_ID};
+    void* vals[3] = {&start, &size, &buffer_id};
+    const CUdeviceptr at = reinterpret_cast<CUdeviceptr>(p);
+    if (api->PointerGetAttributes(3, attrs, vals, at) != CUDA_SUCCESS || at < start || at + bytes > start + size)
+        return false;
+    auto it = m_known.find(start);
+    if (it != m_known.end() && it->second.buffer_id == buffer_id && it->second.size == size) {
+        if (!entry_acked(it->second.entry))
+            return false;  // on its way
+        *word = encode(it->second.entry, at - start);
+        return true;
+    }
+    uint64_t unused = 0;
+    (void)resolve(p, bytes, &unused);  // export it (unless too large or not exportable); usable once acknowledged
+    return false;
 }
 
 Status IpcCache::register_range(const void* p, size_t bytes, int64_t timeout_ms) {

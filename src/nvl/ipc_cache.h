@@ -13,8 +13,11 @@
 //     barrier instead of addresses;
 //   * a helper thread per rank IMPORTS whatever appears in the peers' logs and stores the mapped
 //     base address into a table in device memory, indexed by (rank, entry number);
-//   * a kernel that is handed an entry number its table does not hold yet waits for it (bounded
-//     by the device timeout, like every other wait), so no rank ever waits on the host.
+//   * the importer acknowledges in its own log, and a rank names an entry to its peers only once
+//     every peer has acknowledged it; until then (a few calls) the buffer is replaced by one of two
+//     bounce buffers that every peer mapped at init.  So no rank ever waits on the host for a
+//     peer, and no kernel waits for a mapping (mapping was seen to stall for seconds while the
+//     importing GPU is busy, which a waiting kernel would make worse).
 //
 // An allocation is recognised by its base address and CUDA buffer id: memory that was freed and
 // allocated again at the same address gets a new entry (the old mapping stays open until the
@@ -68,6 +71,16 @@ public:
      *  wait for the importing device, which may be running a kernel that waits for the mapping). */
     bool resolve(const void* p, size_t bytes, uint64_t* word, bool any_size = false);
 
+    /** The (entry, offset) of [p, p + bytes) if its allocation is exported AND every peer has
+     *  acknowledged mapping it.  Otherwise false, after starting the export when that is possible
+     *  (allocation up to auto_max_bytes()): the caller uses a bounce buffer for this call, and a
+     *  later call finds the allocation mapped.  Never waits. */
+    bool resolve_mapped(const void* p, size_t bytes, uint64_t* word);
+
+    /** This rank's two bounce buffers (input, output side), mapped by every peer since init. */
+    void* bounce(int which) const { return m_bounce[which]; }
+    size_t bounce_bytes() const { return m_bounce_bytes; }
+
     /** True when [p, p + bytes) lies in an allocation that is exported and mapped by every peer. */
     bool mapped_everywhere(const void* p, size_t bytes);
 
@@ -118,7 +131,8 @@ private:
     std::mutex m_import_mu;  // import_new() runs on the helper thread and, before a launch, on the caller's
     size_t m_auto_max = 64u << 20;  // MEGRAY_IPC_AUTO_MAX_MB
     bool entry_acked(uint32_t entry);
-    void* m_probe = nullptr;  // exported at init so that peer access is switched on before any collective
+    void* m_bounce[2] = {nullptr, nullptr};  // exported and mapped by every peer at init
+    size_t m_bounce_bytes = 0;
     std::condition_variable m_cv;
     bool m_kick = false;
     // exporter side (calling thread)

@@ -617,6 +617,8 @@ bool NvlCommunicator::peer_addressable(const void* p, size_t bytes) {
 }
 
 void* NvlCommunicator::bounce(int which, size_t bytes) {
+    if (m_ipc != nullptr)  // separate processes: the buffers every peer mapped at init
+        return bytes <= m_ipc->bounce_bytes() ? m_ipc->bounce(which) : nullptr;
     if (m_bounce_cap[which] >= bytes)
         return m_bounce[which];
     // rare: a buffer the peers cannot address (pool or virtual-memory allocations, host memory)
@@ -676,7 +678,9 @@ Status NvlCommunicator::exchange_launch(int kind, const void* in, size_t in_byte
             *word = IpcCache::encode(IpcCache::kEntryHeap, static_cast<uint64_t>(static_cast<const char*>(p) - m_heap.local()));
             return true;
         }
-        return m_ipc->resolve(p, bytes, word, p == m_bounce[0] || p == m_bounce[1]);
+        // (an allocation the peers have not all mapped yet is exported now and replaced by a
+        // bounce buffer for this call: nothing waits for the mapping)
+        return m_ipc->resolve_mapped(p, bytes, word);
     };
     if (in == nullptr || !in_shared) {
         // (peers never touch it: nothing to describe)
