@@ -116,20 +116,26 @@ def main():
         pick("bcast_chunk_bytes", (32 << 10, 64 << 10, 256 << 10, 1 << 20), ["broadcast"], [4 << 20, 64 << 20, 1 << 30],
              "MEGRAY_BCAST_CHUNK")
 
-    # reduce: from which size on the form in which the root pushes its input wins at every larger size
-    rsizes = [1 << k for k in range(18, 29, 2)]  # 256 KiB .. 256 MiB
-    base_env = {"MEGRAY_TUNE_DEFAULT": "0", "MEGRAY_LL_BYTES": "0", "MEGRAY_MAX_CTAS": str(best_ctas)}
-    pushed = run(a.devices, ["reduce"], rsizes, dict(base_env, MEGRAY_REDUCE_STAGED_MIN="0"))
-    pulled = run(a.devices, ["reduce"], rsizes, dict(base_env, MEGRAY_REDUCE_STAGED_MIN=str(1 << 62)))
-    first = 1 << 62
-    for sz in reversed(rsizes):
-        tp, tl = pushed.get(("reduce", sz)), pulled.get(("reduce", sz))
-        if tp is None or tl is None or tp[0] > tl[0]:
-            break
-        first = sz
-    table["reduce_staged_min_bytes"] = first
-    table["measured"]["us_reduce_pushed_vs_pulled"] = {str(sz): [pushed.get(("reduce", sz), [None])[0],
-                                                                 pulled.get(("reduce", sz), [None])[0]] for sz in rsizes}
+    # reduce on more than two ranks: the reducers load everything and store to the root (0), the root
+    # pushes its input into the reducers' slots (1), or loads only, the root loading the reduced
+    # chunks from the reducers' slots (2): the staged form that is fastest at the largest size, and
+    # the size from which it beats form 0 at every larger size
+    if a.devices > 2:
+        rsizes = [1 << k for k in range(20, 31, 2)]  # 1 MiB .. 1 GiB
+        base_env = {"MEGRAY_TUNE_DEFAULT": "0", "MEGRAY_LL_BYTES": "0", "MEGRAY_MAX_CTAS": str(best_ctas)}
+        forms = {0: run(a.devices, ["reduce"], rsizes, dict(base_env, MEGRAY_REDUCE_MODE="0"))}
+        for mode in (1, 2):
+            forms[mode] = run(a.devices, ["reduce"], rsizes, dict(base_env, MEGRAY_REDUCE_MODE=str(mode), MEGRAY_REDUCE_STAGED_MIN="0"))
+        t = lambda mode, sz: forms[mode].get(("reduce", sz), [float("inf")])[0]
+        staged = min((1, 2), key=lambda mode: t(mode, rsizes[-1]))
+        first = 1 << 62
+        for sz in reversed(rsizes):
+            if t(staged, sz) > t(0, sz):
+                break
+            first = sz
+        table["reduce_mode"] = staged if first < (1 << 62) else 0
+        table["reduce_staged_min_bytes"] = first
+        table["measured"]["us_reduce_forms_0_1_2"] = {str(sz): [t(0, sz), t(1, sz), t(2, sz)] for sz in rsizes}
 
     if a.nvls:
         sizes = [1 << k for k in range(18, 29, 2)]  # 256 KiB .. 256 MiB

@@ -1368,6 +1368,101 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                 }
             }
         }
+    } else if (a.kind == DIRECT_REDUCE && a.stage_slots > 0 && n > 1 && a.reduce_mode == 2) {
+        // Reduce by loads alone (the fastest way to move bytes that was measured here: a kernel
+        // that only loads from its peers sustains more than one that loads and stores to them).
+        // One slice per non-root rank.  The reducer of a slice loads it from every rank and stores
+        // the reduced chunk into a slot in its own heap, then raises the chunk counter the root
+        // keeps for (CTA, reducer); the root waits for the counters, loads the chunks into its
+        // output and raises the consumed-chunk counter in the reducer's pad, which frees the slot.
+        // Every link carries one message's worth each way, and nobody stores to a peer but flags.
+        const int root = a.root;
+        const ReducePlan pl = reduce_plan(a.len, n, gridDim.x, a.chunk_bytes, sizeof(Tin));
+        const uint64_t sb = pl.per_cta * blockIdx.x;
+        auto chunk_range = [&](int v, uint32_t k, uint64_t* lo, uint64_t* hi) {
+            const uint64_t s0 = static_cast<uint64_t>(v) * pl.slice;
+            const uint64_t L = s0 >= a.len ? 0 : min(pl.slice, a.len - s0);
+            *lo = min(L, sb + static_cast<uint64_t>(k) * pl.chunk_el);
+            *hi = min(L, min(sb + pl.per_cta, sb + static_cast<uint64_t>(k + 1) * pl.chunk_el));
+        };
+        auto slot_off = [&](uint32_t k) {
+            return a.stage_off + (static_cast<uint64_t>(blockIdx.x) * a.stage_slots + k % a.stage_slots) * a.chunk_bytes;
+        };
+        if (rank == root) {
+            for (uint32_t k = 0; k < pl.chunks; ++k) {
+                // chunk k of every slice is ready?
+                if (threadIdx.x < static_cast<unsigned>(n - 1)) {
+                    const int v = static_cast<int>(threadIdx.x);
+                    const int j = (root + 1 + v) % n;
+                    uint64_t lo, hi;
+                    chunk_range(v, k, &lo, &hi);
+                    const uint32_t* ready = reinterpret_cast<const uint32_t*>(c.peers.heap[rank] + kCreditOff) +
+                                            blockIdx.x * kMaxRanks + j;
+                    if (hi > lo && !wait_flag_reached(c, ready, a.chunk_base + k + 1, 2))
+                        s_ok = 0;
+                }
+                __syncthreads();
+                if (!s_ok)
+                    return;
+                for (int vv = 0; vv < n - 1; ++vv) {
+                    const int v = (vv + static_cast<int>(k) + static_cast<int>(blockIdx.x)) % (n - 1);
+                    const int j = (root + 1 + v) % n;
+                    uint64_t lo, hi;
+                    chunk_range(v, k, &lo, &hi);
+                    if (hi > lo)
+                        cta_copy(g, my_out + (v * pl.slice + lo) * sizeof(Tout), c.peers.heap[j] + slot_off(k),
+                                 (hi - lo) * sizeof(Tout));
+                }
+                __syncthreads();  // every thread has loaded its part of the slots
+                if (threadIdx.x < static_cast<unsigned>(n - 1)) {
+                    const int v = static_cast<int>(threadIdx.x);
+                    const int j = (root + 1 + v) % n;
+                    uint64_t lo, hi;
+                    chunk_range(v, k, &lo, &hi);
+                    if (hi > lo) {
+                        uint32_t* consumed = reinterpret_cast<uint32_t*>(c.peers.heap[j] + kChunkFlagOff) + blockIdx.x;
+                        asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(consumed), "r"(a.chunk_base + k + 1) : "memory");
+                    }
+                }
+            }
+        } else {
+            const int v = (rank - root - 1 + n) % n;  // the slice this rank reduces
+            const uint32_t* consumed = reinterpret_cast<const uint32_t*>(c.peers.heap[rank] + kChunkFlagOff) + blockIdx.x;
+            uint32_t* ready = reinterpret_cast<uint32_t*>(c.peers.heap[root] + kCreditOff) + blockIdx.x * kMaxRanks + rank;
+            for (uint32_t k = 0; k < pl.chunks; ++k) {
+                uint64_t lo, hi;
+                chunk_range(v, k, &lo, &hi);
+                if (hi <= lo)
+                    continue;  // (uniform over the CTA)
+                if (k >= a.stage_slots) {
+                    // the slot still holds chunk k - stage_slots until the root has loaded it
+                    if (threadIdx.x == 0)
+                        s_ok = wait_flag_reached(c, consumed, a.chunk_base + (k - a.stage_slots) + 1, 3) ? 1 : 0;
+                    __syncthreads();
+                    if (!s_ok)
+                        return;
+                }
+                const uint64_t in_byte0 = (v * pl.slice + lo) * sizeof(Tin);
+                char* single = c.peers.heap[rank] + slot_off(k);
+                const bool vec = cb.in_vec && (in_byte0 & 15) == 0;
+                switch (a.op) {
+                    case MegRay::MEGRAY_SUM:
+                        direct_reduce_range<Tin, Tout, MegRay::MEGRAY_SUM, false>(g, a, cb, in_byte0, 0, hi - lo, single, vec, false,
+                                                                                  false);
+                        break;
+                    case MegRay::MEGRAY_MAX:
+                        direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MAX, false>(g, a, cb, in_byte0, 0, hi - lo, single, vec, false,
+                                                                                  false);
+                        break;
+                    default:
+                        direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MIN, false>(g, a, cb, in_byte0, 0, hi - lo, single, vec, false,
+                                                                                  false);
+                }
+                __syncthreads();  // the whole chunk is stored (locally)
+                if (threadIdx.x == 0)
+                    st_release_sys(ready, a.chunk_base + k + 1);
+            }
+        }
     } else if (a.kind == DIRECT_REDUCE && a.stage_slots > 0 && n > 1) {
         // Reduce with the root's input pushed.  One slice per non-root rank, as below, but the
         // reducer of a slice does not load the root's part over NVLink: the root stores it, chunk

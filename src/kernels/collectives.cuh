@@ -201,6 +201,9 @@ struct DirectArgs {
     // heap of the rank that reduces the slice
     uint64_t stage_off;
     uint32_t stage_slots;
+    // 1: as above.  2: loads only - the reducer of a slice loads it from every rank and stores the
+    // reduced chunks into slots in its OWN heap, and the root loads them from there into its output.
+    int reduce_mode;
 };
 
 // Small messages: flagged words ("LL").  A sender stores every 4 bytes of payload together with

@@ -139,6 +139,9 @@ NvlCommunicator::NvlCommunicator(uint32_t nranks, uint32_t rank) : Communicator(
         bcast_chunk_tuned = json_i64(tune_text, "bcast_chunk_bytes", -1);
     m_phases = env_i64("MEGRAY_PHASES", 0) != 0;
     m_spin_sleep_ns = static_cast<uint32_t>(env_i64("MEGRAY_SPIN_SLEEP_NS", 0));
+    m_reduce_mode = static_cast<int>(env_i64("MEGRAY_REDUCE_MODE", 0));
+    if (!tune_text.empty() && getenv("MEGRAY_REDUCE_MODE") == nullptr)
+        m_reduce_mode = static_cast<int>(json_i64(tune_text, "reduce_mode", m_reduce_mode));
     m_reduce_staged_min = static_cast<size_t>(env_i64("MEGRAY_REDUCE_STAGED_MIN", 8 << 20));
     if (!tune_text.empty() && getenv("MEGRAY_REDUCE_STAGED_MIN") == nullptr)
         m_reduce_staged_min = static_cast<size_t>(json_i64(tune_text, "reduce_staged_min_bytes", static_cast<int64_t>(m_reduce_staged_min)));
@@ -743,7 +746,8 @@ Status NvlCommunicator::exchange_launch(int kind, const void* in, size_t in_byte
         a.chunk_base = m_chunk_seq;
         m_chunk_seq += mgk::coll::bcast_plan(work, static_cast<int>(m_nranks), ctas, a.chunk_bytes).chunks;
     }
-    if (kind == mgk::coll::DIRECT_REDUCE && m_nranks > 2 && work >= m_reduce_staged_min && !nvls) {
+    if (kind == mgk::coll::DIRECT_REDUCE && m_nranks > 2 && m_reduce_mode != 0 && work >= m_reduce_staged_min && !nvls &&
+        get_dtype_size(out_dtype) == ein) {
         // large messages: the root pushes its input into staging slots of the reducing ranks
         const size_t slice = (work + m_nranks - 2) / (m_nranks - 1);
         const int want = static_cast<int>(std::min<size_t>(std::max<size_t>(1, slice / (m_direct_cta_bytes / 2)), static_cast<size_t>(max_ctas)));
@@ -756,6 +760,7 @@ Status NvlCommunicator::exchange_launch(int kind, const void* in, size_t in_byte
                                                   static_cast<uint32_t>(ein)).chunks;
             a.stage_off = workspace_off();
             a.stage_slots = static_cast<uint32_t>(slots);
+            a.reduce_mode = m_reduce_mode;
         }
     }
     MEGRAY_CHECK(check_cuda(mgk::coll::launch_direct(a, ctas, 512, stream)));

@@ -206,6 +206,10 @@ private:
     // reduce of at least this many bytes: the root pushes its input (MEGRAY_REDUCE_STAGED_MIN / tune
     // table "reduce_staged_min_bytes")
     size_t m_reduce_staged_min = 8u << 20;
+    // how a large reduce on more than two ranks runs: 0 the reducers load everything and store to
+    // the root, 1 the root pushes its input into the reducers' slots, 2 loads only (the root loads
+    // the reduced chunks from the reducers' slots).  MEGRAY_REDUCE_MODE / tune table "reduce_mode".
+    int m_reduce_mode = 0;
     uint32_t m_spin_sleep_ns = 0;  // MEGRAY_SPIN_SLEEP_NS / tune table "spin_sleep_ns"
     // largest payload per (source, destination) pair that goes as flagged words, per DirectKind
     size_t m_ll_bytes[8] = {};
