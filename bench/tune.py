@@ -137,6 +137,22 @@ def main():
         table["reduce_staged_min_bytes"] = first
         table["measured"]["us_reduce_forms_0_1_2"] = {str(sz): [t(0, sz), t(1, sz), t(2, sz)] for sz in rsizes}
 
+    # broadcast: stores (root and slice owners push) against loads alone (everybody pulls)
+    bsizes = [1 << k for k in range(20, 31, 2)]  # 1 MiB .. 1 GiB
+    benv = {"MEGRAY_TUNE_DEFAULT": "0", "MEGRAY_LL_BYTES": "0", "MEGRAY_MAX_CTAS": str(best_ctas)}
+    pushed = run(a.devices, ["broadcast"], bsizes, dict(benv, MEGRAY_BCAST_PULL="0"))
+    pulled = run(a.devices, ["broadcast"], bsizes, dict(benv, MEGRAY_BCAST_PULL="1"))
+    first = 1 << 62
+    for sz in reversed(bsizes):
+        tl, tp = pulled.get(("broadcast", sz)), pushed.get(("broadcast", sz))
+        if tl is None or tp is None or tl[0] > tp[0]:
+            break
+        first = sz
+    table["bcast_pull"] = 1 if first < (1 << 62) else 0
+    table["bcast_pull_min_bytes"] = first if first < (1 << 62) else 0
+    table["measured"]["us_broadcast_pushed_vs_pulled"] = {str(sz): [pushed.get(("broadcast", sz), [None])[0],
+                                                                   pulled.get(("broadcast", sz), [None])[0]] for sz in bsizes}
+
     if a.nvls:
         sizes = [1 << k for k in range(18, 29, 2)]  # 256 KiB .. 256 MiB
         env = {"MEGRAY_NVLS": "1", "NCCL_NVLS_ENABLE": "1", "MEGRAY_HEAP_MB": "2048"}

@@ -1263,7 +1263,72 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
     } else if (a.kind == DIRECT_BROADCAST) {
         const uint64_t S = a.len * sizeof(Tin);
         const int root = a.root;
-        if (n <= 2) {
+        if (a.bcast_pull && n >= 2) {
+            // Broadcast by loads alone.  The message is cut into n - 1 slices, one per non-root rank.
+            // Chunk by chunk, a rank loads its own slice from the root's input into its output,
+            // raises the chunk counter that every other non-root rank keeps for (CTA, this rank),
+            // and then loads the same chunk of the other slices from their owners' outputs as
+            // their counters arrive.  Nobody stores to a peer but counters; the root only serves
+            // loads (and copies its input to its own output).
+            const BcastPlan pl = bcast_plan(S, n, gridDim.x, a.chunk_bytes);
+            const uint64_t sb = pl.per_cta * blockIdx.x;  // this CTA's share of every slice
+            auto chunk_range = [&](int v, uint32_t k, uint64_t* lo, uint64_t* hi) {
+                const uint64_t s0 = static_cast<uint64_t>(v) * pl.slice;
+                const uint64_t L = s0 >= S ? 0 : min(pl.slice, S - s0);
+                *lo = min(L, sb + static_cast<uint64_t>(k) * a.chunk_bytes);
+                *hi = min(L, min(sb + pl.per_cta, sb + static_cast<uint64_t>(k + 1) * a.chunk_bytes));
+            };
+            if (rank == root) {
+                if (my_out != my_in) {
+                    for (int v = 0; v < n - 1; ++v) {
+                        const uint64_t s0 = static_cast<uint64_t>(v) * pl.slice;
+                        const uint64_t L = s0 >= S ? 0 : min(pl.slice, S - s0);
+                        const uint64_t lo = min(L, sb), hi = min(L, sb + pl.per_cta);
+                        if (hi > lo)
+                            cta_copy(g, my_out + s0 + lo, my_in + s0 + lo, hi - lo);
+                    }
+                }
+            } else {
+                const int v = (rank - root - 1 + n) % n;  // this rank's slice
+                const char* root_in = cb.in[root];
+                for (uint32_t k = 0; k < pl.chunks; ++k) {
+                    uint64_t lo, hi;
+                    chunk_range(v, k, &lo, &hi);
+                    if (hi > lo)
+                        cta_copy(g, my_out + v * pl.slice + lo, root_in + v * pl.slice + lo, hi - lo);
+                    __syncthreads();  // the chunk is stored (locally)
+                    if (threadIdx.x < static_cast<unsigned>(n - 1)) {
+                        const int u = static_cast<int>(threadIdx.x);  // another slice, and its owner
+                        const int m = (root + 1 + u) % n;
+                        if (u != v) {
+                            if (hi > lo)
+                                st_release_sys(reinterpret_cast<uint32_t*>(c.peers.heap[m] + kCreditOff) +
+                                                       blockIdx.x * kMaxRanks + rank,
+                                               a.chunk_base + k + 1);
+                            uint64_t lo2, hi2;
+                            chunk_range(u, k, &lo2, &hi2);
+                            const uint32_t* ready = reinterpret_cast<const uint32_t*>(c.peers.heap[rank] + kCreditOff) +
+                                                    blockIdx.x * kMaxRanks + m;
+                            if (hi2 > lo2 && !wait_flag_reached(c, ready, a.chunk_base + k + 1, 2))
+                                s_ok = 0;
+                        }
+                    }
+                    __syncthreads();
+                    if (!s_ok)
+                        return;
+                    for (int uu = 0; uu < n - 1; ++uu) {
+                        const int u = (uu + static_cast<int>(k) + static_cast<int>(blockIdx.x)) % (n - 1);
+                        if (u == v)
+                            continue;
+                        const int m = (root + 1 + u) % n;
+                        uint64_t lo2, hi2;
+                        chunk_range(u, k, &lo2, &hi2);
+                        if (hi2 > lo2)
+                            cta_copy(g, my_out + u * pl.slice + lo2, cb.out[m] + u * pl.slice + lo2, hi2 - lo2);
+                    }
+                }
+            }
+        } else if (n <= 2) {
             // nobody to forward to: the root stores its share to the other rank (and to itself)
             const uint64_t per_cta = round_up_u64((S + gridDim.x - 1) / gridDim.x, 16);
             const uint64_t b = min(S, per_cta * blockIdx.x), e = min(S, b + per_cta);

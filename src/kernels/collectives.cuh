@@ -196,6 +196,8 @@ struct DirectArgs {
     uint64_t heap_bytes;   // size of every rank's heap (NVLS needs both buffers inside it, same offset)
     uint32_t chunk_base;   // broadcast: chunk k is announced as chunk_base + k + 1
     uint32_t chunk_bytes;  // broadcast: bytes of one chunk of a CTA's share of a slice (multiple of 16)
+    int bcast_pull;        // broadcast by loads alone: every rank loads its slice from the root and the
+                           // other slices from their owners (instead of the root and the owners storing)
     // reduce with the root's input pushed (stage_slots > 0): CTA b of the root stores chunk k of
     // every slice into slot (b * stage_slots + k % stage_slots) of chunk_bytes at stage_off in the
     // heap of the rank that reduces the slice

@@ -139,6 +139,12 @@ NvlCommunicator::NvlCommunicator(uint32_t nranks, uint32_t rank) : Communicator(
         bcast_chunk_tuned = json_i64(tune_text, "bcast_chunk_bytes", -1);
     m_phases = env_i64("MEGRAY_PHASES", 0) != 0;
     m_spin_sleep_ns = static_cast<uint32_t>(env_i64("MEGRAY_SPIN_SLEEP_NS", 0));
+    m_bcast_pull = env_i64("MEGRAY_BCAST_PULL", 0) != 0;
+    if (!tune_text.empty() && getenv("MEGRAY_BCAST_PULL") == nullptr)
+        m_bcast_pull = json_i64(tune_text, "bcast_pull", m_bcast_pull ? 1 : 0) != 0;
+    m_bcast_pull_min = static_cast<size_t>(env_i64("MEGRAY_BCAST_PULL_MIN", 0));
+    if (!tune_text.empty() && getenv("MEGRAY_BCAST_PULL_MIN") == nullptr)
+        m_bcast_pull_min = static_cast<size_t>(json_i64(tune_text, "bcast_pull_min_bytes", static_cast<int64_t>(m_bcast_pull_min)));
     m_reduce_mode = static_cast<int>(env_i64("MEGRAY_REDUCE_MODE", 0));
     if (!tune_text.empty() && getenv("MEGRAY_REDUCE_MODE") == nullptr)
         m_reduce_mode = static_cast<int>(json_i64(tune_text, "reduce_mode", m_reduce_mode));
@@ -744,6 +750,7 @@ Status NvlCommunicator::exchange_launch(int kind, const void* in, size_t in_byte
         ctas = static_cast<int>(std::min<size_t>(std::max<size_t>(1, slice / (m_direct_cta_bytes / 2)), static_cast<size_t>(max_ctas)));
         a.chunk_bytes = m_bcast_chunk;
         a.chunk_base = m_chunk_seq;
+        a.bcast_pull = m_bcast_pull && work >= m_bcast_pull_min ? 1 : 0;
         m_chunk_seq += mgk::coll::bcast_plan(work, static_cast<int>(m_nranks), ctas, a.chunk_bytes).chunks;
     }
     if (kind == mgk::coll::DIRECT_REDUCE && m_nranks > 2 && m_reduce_mode != 0 && work >= m_reduce_staged_min && !nvls &&
@@ -1131,9 +1138,10 @@ Status NvlCommunicator::broadcast(const void* sendbuff, void* recvbuff, size_t l
         return ll_launch(l, stream);
     }
     if (m_xchg && m_direct && exchange_fits(m_rank == root ? sendbuff : nullptr, bytes, recvbuff, bytes))
-        return exchange_launch(mgk::coll::DIRECT_BROADCAST, m_rank == root ? sendbuff : nullptr, bytes, false,
-                               recvbuff, bytes, true, bytes, MEGRAY_UINT8, MEGRAY_UINT8, 1.0f, MEGRAY_SUM, root,
-                               stream);
+        // (in the loads-only form the peers read the root's input themselves)
+        return exchange_launch(mgk::coll::DIRECT_BROADCAST, m_rank == root ? sendbuff : nullptr, bytes,
+                               m_bcast_pull && bytes >= m_bcast_pull_min, recvbuff, bytes, true, bytes, MEGRAY_UINT8,
+                               MEGRAY_UINT8, 1.0f, MEGRAY_SUM, root, stream);
     const uint32_t n = m_nranks;
     const bool two_step = bytes > m_oneshot_bytes && n > 2;
     // one step: everyone loads the whole piece from the root's pub buffer

@@ -210,6 +210,10 @@ private:
     // the root, 1 the root pushes its input into the reducers' slots, 2 loads only (the root loads
     // the reduced chunks from the reducers' slots).  MEGRAY_REDUCE_MODE / tune table "reduce_mode".
     int m_reduce_mode = 0;
+    // broadcast by loads alone from this size on (MEGRAY_BCAST_PULL, MEGRAY_BCAST_PULL_MIN / tune table
+    // "bcast_pull", "bcast_pull_min_bytes")
+    bool m_bcast_pull = false;
+    size_t m_bcast_pull_min = 0;
     uint32_t m_spin_sleep_ns = 0;  // MEGRAY_SPIN_SLEEP_NS / tune table "spin_sleep_ns"
     // largest payload per (source, destination) pair that goes as flagged words, per DirectKind
     size_t m_ll_bytes[8] = {};

@@ -287,13 +287,15 @@ TEST(Nvl_AllOperationsOnPlainBuffersAgainstHostValues) {
     // Once more with few CTAs, small chunks and the staged forms of reduce from 100 KB on: the
     // pipelined broadcast and the staged reduces then run many chunks per CTA, more than a CTA has
     // staging slots, so slots are reused under the consumed-chunk counters.  Form 1: the root
-    // pushes its input; form 2: the root loads the reduced chunks.
+    // pushes its input; form 2: the root loads the reduced chunks (run together with the
+    // broadcast in which every rank loads instead of the root and the slice owners storing).
     setenv("MEGRAY_REDUCE_STAGED_MIN", "100000", 1);
     setenv("MEGRAY_BCAST_CHUNK", "16384", 1);
     setenv("MEGRAY_DIRECT_CTA_BYTES", "262144", 1);
     setenv("MEGRAY_REDUCE_MODE", "1", 1);
     run_sweep(n);
     setenv("MEGRAY_REDUCE_MODE", "2", 1);
+    setenv("MEGRAY_BCAST_PULL", "1", 1);  // and the broadcast by loads alone
     run_sweep(n);
     if (n > 3)
         run_sweep(3);  // an odd group: slices and chunk shares that do not divide evenly
@@ -301,6 +303,7 @@ TEST(Nvl_AllOperationsOnPlainBuffersAgainstHostValues) {
     unsetenv("MEGRAY_BCAST_CHUNK");
     unsetenv("MEGRAY_DIRECT_CTA_BYTES");
     unsetenv("MEGRAY_REDUCE_MODE");
+    unsetenv("MEGRAY_BCAST_PULL");
     if (n > 3)
         run_sweep(3);
 }
