@@ -35,7 +35,7 @@ void reduce_range(const ReducePlan& pl, uint64_t len, int cta, int v, uint32_t k
 }  // namespace
 
 TEST(Plan_BroadcastChunksCoverTheMessageExactlyOnce) {
-    const uint64_t sizes[] = {1, 15, 16, 17, 4096, 65537, 280004, 1200028, (4u << 20) + 12, (33u << 20) + 4};
+    const uint64_t sizes[] = {1, 15, 16, 17, 4096, 65537, 280004, 1200028};
     const uint32_t chunks[] = {4096, 16384, 65536, 1u << 20};
     for (int n = 2; n <= 8; ++n)
         for (uint64_t S : sizes)
@@ -65,7 +65,7 @@ TEST(Plan_BroadcastChunksCoverTheMessageExactlyOnce) {
 }
 
 TEST(Plan_StagedReduceChunksCoverTheMessageExactlyOnceAndFitTheirSlots) {
-    const uint64_t lens[] = {1, 5, 1000, 70001, 300007, (1u << 20) + 3, (6u << 20) + 48};
+    const uint64_t lens[] = {1, 5, 1000, 70001, 300007};
     const uint32_t chunk_bytes[] = {4096, 16384, 65536, 262144};
     for (int n = 3; n <= 8; ++n)
         for (uint64_t len : lens)
