@@ -1321,11 +1321,12 @@ Status NvlCommunicator::stream_barrier(std::shared_ptr<Context> ctx) {
 }
 
 // ------------------------------------------------------------------ point to point (NCCL)
-// send / recv run as NCCL point-to-point calls on a stream of the communicator's own.  That
+// send / recv run as NCCL point-to-point calls.  In the ordinary mode they go straight onto the
+// caller's stream.  With set_p2p_async(true) they run on a stream of the communicator's own.  That
 // stream first waits for the work already on the caller's stream (the data to send is final, the
 // buffer to receive into is free) and the caller's stream then waits for the transfer, so the
-// calls keep the interface's meaning: enqueued on the context's stream, complete in stream order.
-// With set_p2p_async(true) the second wait is left out until p2p_join(): kernels enqueued on the
+// calls keep the interface's meaning: enqueued on the context's stream, complete in stream order;
+// but the second wait is left out until p2p_join(): kernels enqueued on the
 // caller's stream in between (native collectives included) run at the same time as the transfer.
 
 Status NvlCommunicator::p2p_fork(cudaStream_t user) {
@@ -1376,6 +1377,11 @@ Status NvlCommunicator::p2p_call(bool is_send, void* buf, size_t size, uint32_t 
         return MEGRAY_ABORTED;
     m_stats.calls++;
     m_stats.bytes += size;
+    if (!m_p2p_async && !m_p2p_pending && m_p2p_users.empty()) {
+        // Joined at once, the transfer would run in the caller's stream order anyway: enqueue it
+        // there (as the reference does, src/nccl/communicator.cpp:66-88) and save the fork / join events.
+        return is_send ? m_p2p->send(buf, size, MEGRAY_CHAR, rank, ctx) : m_p2p->recv(buf, size, MEGRAY_CHAR, rank, ctx);
+    }
     MEGRAY_CHECK(p2p_fork(static_cast<CudaContext*>(ctx.get())->get_stream()));
     if (!m_p2p_ctx)
         m_p2p_ctx = CudaContext::make(m_p2p_stream);
