@@ -118,16 +118,17 @@ def main():
 
     # reduce on more than two ranks: the reducers load everything and store to the root (0), the root
     # pushes its input into the reducers' slots (1), or loads only, the root loading the reduced
-    # chunks from the reducers' slots (2): the staged form that is fastest at the largest size, and
+    # chunks from the reducers' slots (2), or the same in steps separated by barriers (3): the
+    # staged form that is fastest at the largest size, and
     # the size from which it beats form 0 at every larger size
     if a.devices > 2:
         rsizes = [1 << k for k in range(20, 31, 2)]  # 1 MiB .. 1 GiB
         base_env = {"MEGRAY_TUNE_DEFAULT": "0", "MEGRAY_LL_BYTES": "0", "MEGRAY_MAX_CTAS": str(best_ctas)}
         forms = {0: run(a.devices, ["reduce"], rsizes, dict(base_env, MEGRAY_REDUCE_MODE="0"))}
-        for mode in (1, 2):
+        for mode in (1, 2, 3):
             forms[mode] = run(a.devices, ["reduce"], rsizes, dict(base_env, MEGRAY_REDUCE_MODE=str(mode), MEGRAY_REDUCE_STAGED_MIN="0"))
         t = lambda mode, sz: forms[mode].get(("reduce", sz), [float("inf")])[0]
-        staged = min((1, 2), key=lambda mode: t(mode, rsizes[-1]))
+        staged = min((1, 2, 3), key=lambda mode: t(mode, rsizes[-1]))
         first = 1 << 62
         for sz in reversed(rsizes):
             if t(staged, sz) > t(0, sz):
@@ -135,7 +136,7 @@ def main():
             first = sz
         table["reduce_mode"] = staged if first < (1 << 62) else 0
         table["reduce_staged_min_bytes"] = first
-        table["measured"]["us_reduce_forms_0_1_2"] = {str(sz): [t(0, sz), t(1, sz), t(2, sz)] for sz in rsizes}
+        table["measured"]["us_reduce_forms_0_1_2_3"] = {str(sz): [t(0, sz), t(1, sz), t(2, sz), t(3, sz)] for sz in rsizes}
 
     # broadcast: stores (root and slice owners push) against loads alone (everybody pulls)
     bsizes = [1 << k for k in range(20, 31, 2)]  # 1 MiB .. 1 GiB

@@ -1433,6 +1433,68 @@ __global__ void __launch_bounds__(512) direct_family_kernel(const DirectArgs a) 
                 }
             }
         }
+    } else if (a.kind == DIRECT_REDUCE && a.stage_slots > 0 && n > 2 && a.reduce_mode == 3) {
+        // Reduce in steps, loads only, with nothing but the per-CTA barrier between the steps.  One
+        // slice per non-root rank; a CTA's share of a slice is cut into stage_slots pieces.  In
+        // step t every reducer loads piece t of its slice from every rank and stores the reduced
+        // piece into one of two slots in its own heap, while the root loads piece t - 1 of every
+        // slice from the reducers' other slot into its output; a barrier ends the step.  The
+        // reducers' work of one step and the root's work on the step before run side by side, so
+        // the whole takes (pieces + 1) / pieces of the time of the loads alone.
+        const int root = a.root;
+        const uint32_t pieces = a.stage_slots;
+        const uint64_t se = round_up_u64((a.len + n - 2) / (n - 1), V);
+        const uint64_t per_cta = round_up_u64((se + gridDim.x - 1) / gridDim.x, V);
+        const uint64_t piece_el = a.chunk_bytes / sizeof(Tin);
+        const uint64_t sb = per_cta * blockIdx.x;
+        auto piece_range = [&](int v, uint32_t t, uint64_t* lo, uint64_t* hi) {
+            const uint64_t s0 = static_cast<uint64_t>(v) * se;
+            const uint64_t L = s0 >= a.len ? 0 : min(se, a.len - s0);
+            *lo = min(L, sb + static_cast<uint64_t>(t) * piece_el);
+            *hi = min(L, min(sb + per_cta, sb + static_cast<uint64_t>(t + 1) * piece_el));
+        };
+        auto slot_off = [&](uint32_t t) {
+            return a.stage_off + (static_cast<uint64_t>(blockIdx.x) * 2 + (t & 1)) * a.chunk_bytes;
+        };
+        for (uint32_t t = 0; t <= pieces; ++t) {
+            if (rank != root && t < pieces) {
+                const int v = (rank - root - 1 + n) % n;
+                uint64_t lo, hi;
+                piece_range(v, t, &lo, &hi);
+                if (hi > lo) {
+                    const uint64_t in_byte0 = (v * se + lo) * sizeof(Tin);
+                    char* single = c.peers.heap[rank] + slot_off(t);
+                    const bool vec = cb.in_vec && (in_byte0 & 15) == 0;
+                    switch (a.op) {
+                        case MegRay::MEGRAY_SUM:
+                            direct_reduce_range<Tin, Tout, MegRay::MEGRAY_SUM, false>(g, a, cb, in_byte0, 0, hi - lo, single, vec,
+                                                                                      false, false);
+                            break;
+                        case MegRay::MEGRAY_MAX:
+                            direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MAX, false>(g, a, cb, in_byte0, 0, hi - lo, single, vec,
+                                                                                      false, false);
+                            break;
+                        default:
+                            direct_reduce_range<Tin, Tout, MegRay::MEGRAY_MIN, false>(g, a, cb, in_byte0, 0, hi - lo, single, vec,
+                                                                                      false, false);
+                    }
+                }
+            }
+            if (rank == root && t >= 1) {
+                for (int vv = 0; vv < n - 1; ++vv) {
+                    const int v = (vv + static_cast<int>(blockIdx.x)) % (n - 1);
+                    const int j = (root + 1 + v) % n;
+                    uint64_t lo, hi;
+                    piece_range(v, t - 1, &lo, &hi);
+                    if (hi > lo)
+                        cta_copy(g, my_out + (v * se + lo) * sizeof(Tout), c.peers.heap[j] + slot_off(t - 1),
+                                 (hi - lo) * sizeof(Tout));
+                }
+            }
+            // the reduced pieces of this step are stored / the slots read in this step are free again
+            if (t < pieces && !cta_barrier(c, ++epoch))
+                return;
+        }
     } else if (a.kind == DIRECT_REDUCE && a.stage_slots > 0 && n > 1 && a.reduce_mode == 2) {
         // Reduce by loads alone (the fastest way to move bytes that was measured here: a kernel
         // that only loads from its peers sustains more than one that loads and stores to them).

@@ -759,7 +759,27 @@ Status NvlCommunicator::exchange_launch(int kind, const void* in, size_t in_byte
         const size_t slice = (work + m_nranks - 2) / (m_nranks - 1);
         const int want = static_cast<int>(std::min<size_t>(std::max<size_t>(1, slice / (m_direct_cta_bytes / 2)), static_cast<size_t>(max_ctas)));
         const size_t slots = std::min<size_t>(8, m_ws_bytes / (static_cast<size_t>(want) * m_bcast_chunk));
-        if (slots >= 2) {
+        if (m_reduce_mode == 3) {
+            // in steps: the grid of the plain form; a CTA's share of a slice in `steps` pieces, two
+            // slots of one piece per CTA in every reducer's workspace
+            const size_t v16 = 16 / ein;
+            const size_t se = round_up((len + m_nranks - 2) / (m_nranks - 1), v16);
+            const size_t per_cta = round_up((se + ctas - 1) / ctas, v16);
+            size_t steps = static_cast<size_t>(std::max<int64_t>(2, env_i64("MEGRAY_REDUCE_STEPS", 8)));
+            size_t piece = round_up((per_cta + steps - 1) / steps, v16);
+            while (2 * static_cast<size_t>(ctas) * piece * ein > m_ws_bytes && steps < 256) {
+                steps *= 2;
+                piece = round_up((per_cta + steps - 1) / steps, v16);
+            }
+            steps = (per_cta + piece - 1) / piece;  // (the last pieces may be empty otherwise)
+            if (2 * static_cast<size_t>(ctas) * piece * ein <= m_ws_bytes && steps >= 1) {
+                a.chunk_bytes = static_cast<uint32_t>(piece * ein);
+                a.stage_off = workspace_off();
+                a.stage_slots = static_cast<uint32_t>(steps);
+                a.reduce_mode = 3;
+                m_epoch += static_cast<uint32_t>(steps);  // one barrier per step, beyond the usual two
+            }
+        } else if (slots >= 2) {
             ctas = want;
             a.chunk_bytes = m_bcast_chunk;
             a.chunk_base = m_chunk_seq;

@@ -208,7 +208,8 @@ private:
     size_t m_reduce_staged_min = 8u << 20;
     // how a large reduce on more than two ranks runs: 0 the reducers load everything and store to
     // the root, 1 the root pushes its input into the reducers' slots, 2 loads only (the root loads
-    // the reduced chunks from the reducers' slots).  MEGRAY_REDUCE_MODE / tune table "reduce_mode".
+    // the reduced chunks from the reducers' slots), 3 loads only in steps separated by barriers
+    // (MEGRAY_REDUCE_STEPS pieces).  MEGRAY_REDUCE_MODE / tune table "reduce_mode".
     int m_reduce_mode = 0;
     // broadcast by loads alone from this size on (MEGRAY_BCAST_PULL, MEGRAY_BCAST_PULL_MIN / tune table
     // "bcast_pull", "bcast_pull_min_bytes")

@@ -299,6 +299,12 @@ TEST(Nvl_AllOperationsOnPlainBuffersAgainstHostValues) {
     run_sweep(n);
     if (n > 3)
         run_sweep(3);  // an odd group: slices and chunk shares that do not divide evenly
+    setenv("MEGRAY_REDUCE_MODE", "3", 1);  // form 3: in steps separated by barriers, loads only
+    setenv("MEGRAY_REDUCE_STEPS", "3", 1);
+    run_sweep(n > 3 ? 3 : n);
+    if (n > 3)
+        run_sweep(n);
+    unsetenv("MEGRAY_REDUCE_STEPS");
     unsetenv("MEGRAY_REDUCE_STAGED_MIN");
     unsetenv("MEGRAY_BCAST_CHUNK");
     unsetenv("MEGRAY_DIRECT_CTA_BYTES");
